@@ -1,0 +1,139 @@
+/* tenzo_kernels.h — flat C entry points, one per CUDA kernel of the quantized decode path.
+ *
+ * These are the device-pointer calls that sit underneath the engine ABI (tenzo.h) and the
+ * tenzo::CUDARuntime backend class. Every pointer is a CUDA device pointer unless the name ends
+ * in _host; `stream` is a cudaStream_t passed as void* (NULL = default stream). Calls enqueue
+ * work and return without synchronising. Return value: 0 on success, a negative tenzo_status_t
+ * value (tenzo.h) on bad arguments, or a positive cudaError_t if the launch failed.
+ *
+ * All kernels are sm_100a only; there is no CPU or other-backend fallback.
+ *
+ * Each entry names the reference code it replaces (paths inside catdlia/tenzo).
+ */
+#ifndef TENZO_KERNELS_H
+#define TENZO_KERNELS_H
+#include <stddef.h>
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#ifndef TENZO_API
+#define TENZO_API __attribute__((visibility("default")))
+#endif
+
+/* ---- TL1 ternary GEMV with fused RMSNorm + absmax(31) quantiser ------------------------------
+ * Replaces rms_norm_raw + build_lut + compute_single_block / compute_from_lut
+ * (src/runtime/TenzoEngine.cpp:22-166) and the three call shapes that use them: the fused QKV
+ * loop (:1547-1572), the fused gate/up loop + squared-ReLU GLU (:1593-1620), and the single
+ * projections with residual add (:1585-1590, :1624-1628).
+ *
+ * Weights are the reference's own TL1 layout: [n_blocks][K/2][32 bytes]; byte c of a 32-byte
+ * group carries row 64b+c (low nibble) and row 64b+32+c (high nibble) for columns (2k, 2k+1),
+ * nibble = (w0+1)|((w1+1)<<2). K must be even, the weight pointer 16-byte aligned.
+ *
+ * Per sequence s in [0,batch):
+ *   y   = do_norm ? x*(1/sqrt(mean(x^2)+eps))*norm_w : x                       (fp32)
+ *   m   = max(1e-6, max|y|);  a_k = round(y_k*(31/m));  inv = m/31              (exact)
+ *   acc_r = sum_k w[r][k]*a_k                                                    (int32, exact)
+ *   v_r = (float)acc_r * (inv * scale_of_row_block)
+ *   epilogue 0: out[r] = v_r
+ *   epilogue 1: out[r] = resid[r] + v_r
+ *   epilogue 2: rows [0,N/2) are gate, [N/2,N) up: out[r] = max(0,v_r)^2 * v_{r+N/2}, r < N/2
+ */
+enum { TENZO_EPI_STORE = 0, TENZO_EPI_RESIDUAL = 1, TENZO_EPI_RELU2_GLU = 2 };
+
+typedef struct {
+    const float* x;        /* [batch][x_stride] input activations */
+    const float* norm_w;   /* [K] RMSNorm weight or NULL */
+    int do_norm;
+    float eps;             /* reference uses 1e-5 */
+    const uint8_t* w;      /* TL1-packed weights, n_blocks*K/2*32 bytes */
+    int n_blocks;          /* N/64 */
+    int K;
+    int seg_end[3];        /* row blocks [0,seg_end[0]) use seg_scale[0], [seg_end[0],seg_end[1]) ... */
+    float seg_scale[3];    /* per-tensor weight scales (q/k/v or gate/up packed back to back) */
+    int epilogue;
+    const float* resid;    /* [batch][out_stride], epilogue 1 only */
+    float* out;            /* [batch][out_stride] */
+    int32_t* acc_out;      /* optional [batch][n_blocks*64] raw accumulators (parity checks) */
+    int8_t* a_out;         /* optional [batch][K] quantised activations */
+    float* inv_out;        /* optional [batch] m/31 */
+    int batch;
+    int x_stride, out_stride;
+    /* split-K scratch, zero-initialised once by the caller and left zero by every launch:
+     * splitk_acc >= batch*n_blocks*64 ints, splitk_cnt >= batch*n_blocks uints. May be NULL when
+     * tenzo_cuda_tl1_gemv_ksplit(...) returns 1 for the shape. */
+    int32_t* splitk_acc;
+    uint32_t* splitk_cnt;
+    int use_pdl;           /* launch with programmatic stream serialisation (weights prefetch
+                              overlaps the previous kernel's tail); 0 = ordinary launch */
+} tenzo_tl1_gemv_args;
+
+TENZO_API int tenzo_cuda_tl1_gemv(const tenzo_tl1_gemv_args* args, void* stream);
+/* K-split factor the launcher will pick for this shape (so callers can size the scratch). */
+TENZO_API int tenzo_cuda_tl1_gemv_ksplit(int n_blocks, int K, int epilogue);
+
+/* ---- standalone fused RMSNorm + per-token absmax quantiser ------------------------------------
+ * Replaces rms_norm_raw (:148-166) followed by the quantiser half of build_lut (:27-42,
+ * qmax = 31) or of compute_logits (:1666-1678, qmax = 127: floor 1e-8, scale = amax/127,
+ * q = clamp(round(y*(1/scale)))). y_out / q_out / scale_out are each optional.
+ * scale_out receives m/31 (qmax 31) or amax/127 (qmax 127). */
+TENZO_API int tenzo_cuda_rmsnorm_quant(const float* x, const float* norm_w, int do_norm, float eps, int dim,
+                                       int qmax, int batch, int x_stride, float* y_out, int8_t* q_out,
+                                       float* scale_out, void* stream);
+
+/* ---- fused RoPE + INT8 KV append + GQA decode attention ---------------------------------------
+ * Replaces FusedKVCache::forward_attention_raw in int8_fused mode (:447-533, :657-694, :823-851,
+ * :911-913). Cache layout per sequence is the reference's: K,V int8 [layer][kv_head][max_seq][128],
+ * scales fp32 [layer][kv_head][max_seq]; sequences are seq_stride_* apart. pos[s] is the slot the
+ * new token is written to (= tokens already cached); attention then covers pos[s]+1 keys.
+ * rope_cos/sin: [max_seq][head_dim/2] tables (built on the host with the reference's float
+ * expressions so rotations are bit-identical); NULL skips RoPE. head_dim must be 128.
+ * scratch: split-T partials, tenzo_cuda_attention_scratch_bytes(...) bytes. */
+typedef struct {
+    const float* q;        /* [batch][q_stride]  n_q*128 used, pre-RoPE */
+    const float* k;        /* [batch][kv_stride] n_kv*128 used, pre-RoPE new key */
+    const float* v;        /* [batch][kv_stride] n_kv*128 used, new value */
+    float* out;            /* [batch][n_q*128] */
+    int q_stride, kv_stride; /* floats between sequences; 0 = dense (n_q*128 / n_kv*128) */
+    int8_t* cache_k; int8_t* cache_v; float* scale_k; float* scale_v;
+    size_t seq_stride_kv;  /* elements between sequences in cache_k/v */
+    size_t seq_stride_sc;  /* elements between sequences in scale_k/v */
+    const int* pos;        /* [batch] device */
+    const float* rope_cos; const float* rope_sin;
+    int layer, n_q, n_kv, head_dim, max_seq, batch;
+    int max_len;           /* upper bound on pos[s]+1 for this launch (sizes the grid) */
+    int append;            /* 1: quantise and store the new k,v at pos (normal decode); 0: the
+                              cache already holds pos[s]+1 keys, k/v are ignored */
+    void* scratch;
+    int use_pdl;
+} tenzo_attention_args;
+
+TENZO_API int tenzo_cuda_attention_int8(const tenzo_attention_args* args, void* stream);
+TENZO_API size_t tenzo_cuda_attention_scratch_bytes(int batch, int n_q, int max_len);
+
+/* ---- INT8 LM head GEMV with fused final RMSNorm + absmax(127) quantiser + argmax --------------
+ * Replaces compute_logits' int8 branch (:1634-1638, :1661-1719) and the greedy branch of
+ * sample_top_k_top_p (:1745-1755: first maximum wins). logits/argmax_out/acc_out optional.
+ * scratch: tenzo_cuda_lm_head_scratch_bytes(batch) bytes. */
+TENZO_API int tenzo_cuda_lm_head_i8(const float* x, const float* norm_w, int do_norm, float eps,
+                                    const int8_t* w, const float* row_scales, int vocab, int hidden,
+                                    int batch, int x_stride, float* logits, int32_t* acc_out,
+                                    int* argmax_out, void* scratch, int use_pdl, void* stream);
+TENZO_API size_t tenzo_cuda_lm_head_scratch_bytes(int batch);
+
+/* ---- INT8 embedding row dequantisation ---------------------------------------------------------
+ * Replaces embedding_lookup's int8 branch (:1299-1315): x = (float)W8[tok] * scale[tok]. */
+TENZO_API int tenzo_cuda_embedding_i8(const int8_t* w, const float* row_scales, int hidden,
+                                      const int* tokens, int batch, float* x, int x_stride, void* stream);
+
+/* ---- checkpoint rows -> TL1 layout --------------------------------------------------------------
+ * Replaces pack_ternary_weights_raw (:1842-1884): raw [N/4][K] bytes (row r in bits 2*(r%4)) to
+ * the [N/64][K/2][32] layout above. */
+TENZO_API int tenzo_cuda_tl1_pack_rows2bit(const uint8_t* raw, int N, int K, uint8_t* packed, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TENZO_KERNELS_H */

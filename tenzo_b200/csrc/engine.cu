@@ -1,0 +1,487 @@
+// Resident decode engine behind the tenzo.h ABI (and its additive extension, tenzo_ext.h).
+//
+// Mirrors TenzoEngineImpl of the reference (src/runtime/TenzoEngine.cpp:1215-1838): embedding ->
+// num_layers x forward_layer -> (generate only) logits + sampler, with the sequence length
+// advanced once per token after all layers. The differences are structural: weights, KV cache
+// and every intermediate stay in device memory, a decode step is a fixed kernel sequence replayed
+// as a CUDA graph (token ids and positions are read from device memory so the graph never
+// changes), and `batch` independent sequences advance together.
+//
+// Per layer (reference lines in brackets):
+//   tl1_gemv  in_norm + quant + [q|k|v] rows, store                     [:1542-1572]
+//   attention RoPE, int8 append, softmax(QK)V                           [:1578]
+//   tl1_gemv  attn_sub_norm + quant + out rows, h1 = x + .              [:1582-1590]
+//   tl1_gemv  post_norm + quant + [gate|up] rows, relu(g)^2*u           [:1594-1620]
+//   tl1_gemv  ffn_sub_norm + quant + down rows, x = h1 + .              [:1622-1628]
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <new>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "../../include/tenzo.h"
+#include "../../include/tenzo_ext.h"
+#include "../../include/tenzo_kernels.h"
+#include "engine.h"
+
+namespace tz {
+
+thread_local std::string g_last_error;
+void set_error(const std::string& m) { g_last_error = m; }
+
+struct CudaError : std::runtime_error {
+    cudaError_t code;
+    CudaError(cudaError_t c, const char* what) : std::runtime_error(std::string(what) + ": " + cudaGetErrorString(c)), code(c) {}
+};
+#define TZ_CUDA(expr)                                            \
+    do {                                                         \
+        cudaError_t _e = (expr);                                 \
+        if (_e != cudaSuccess) throw CudaError(_e, #expr);       \
+    } while (0)
+#define TZ_KERNEL(expr)                                                                         \
+    do {                                                                                        \
+        int _r = (expr);                                                                        \
+        if (_r > 0) throw CudaError((cudaError_t)_r, #expr);                                    \
+        if (_r < 0) throw std::runtime_error(std::string(#expr) + " rejected its arguments");   \
+    } while (0)
+
+__global__ void advance_kernel(int* pos, int* tokens, const int* next, int batch, int feed_back) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < batch) {
+        pos[i] += 1;
+        if (feed_back) tokens[i] = next[i];
+    }
+}
+
+__global__ void record_tokens_kernel(const int* next, int* history, int step, int batch) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < batch) history[(size_t)step * batch + i] = next[i];
+}
+
+// Deterministic stand-in KV: int8 rows and positive scales from a counter hash.
+__global__ void kv_fill_kernel(int8_t* k, int8_t* v, float* sk, float* sv, size_t rows_total, int max_seq, int len,
+                               unsigned long long seed) {
+    const size_t n = rows_total * 128;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t row = i >> 7;
+        if ((int)(row % max_seq) >= len) continue;
+        unsigned long long z = (i + 1) * 0x9E3779B97F4A7C15ull + seed;
+        z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+        z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+        z ^= z >> 31;
+        // roughly N(0,1)/amax*127 shaped: sum of four uniform bytes, centred
+        const int a = (int)(z & 255) + (int)((z >> 8) & 255) + (int)((z >> 16) & 255) + (int)((z >> 24) & 255) - 510;
+        const int b = (int)((z >> 32) & 255) + (int)((z >> 40) & 255) + (int)((z >> 48) & 255) + (int)((z >> 56) & 255) - 510;
+        k[i] = (int8_t)max(-127, min(127, a / 4));
+        v[i] = (int8_t)max(-127, min(127, b / 4));
+        if ((i & 127) == 0) {
+            sk[row] = 0.02f + 0.00001f * (float)((z >> 20) & 1023);
+            sv[row] = 0.02f + 0.00001f * (float)((z >> 44) & 1023);
+        }
+    }
+}
+
+static int env_flag(const char* name, int dflt) {
+    const char* s = std::getenv(name);
+    return s ? std::atoi(s) : dflt;
+}
+
+Engine::Engine(const tenzo_config_t& c, const tenzo_ext_options_t& o) : cfg(c) {
+    batch = o.batch > 0 ? o.batch : 1;
+    rope_theta = o.rope_theta > 0.0f ? o.rope_theta : 10000.0f;   // TenzoEngine.cpp:456
+    use_graph = o.use_graph >= 0 ? o.use_graph : env_flag("TENZO_CUDA_GRAPH", 1);
+    use_pdl = o.use_pdl >= 0 ? o.use_pdl : env_flag("TENZO_CUDA_PDL", 1);
+    cfg.kv_mode = "int8_fused";
+    cfg.device = "cuda";
+    h = cfg.hidden_size;
+    qd = cfg.num_q_heads * cfg.head_dim;
+    kvd = cfg.num_kv_heads * cfg.head_dim;
+    ffn = cfg.ffn_dim;
+    L = cfg.num_layers;
+    V = cfg.vocab_size;
+    if (cfg.head_dim != 128) throw std::invalid_argument("head_dim must be 128");
+    if (h <= 0 || ffn <= 0 || L <= 0 || V <= 0 || cfg.max_seq_len <= 0) throw std::invalid_argument("non-positive dimension");
+    if (h % 64 || qd % 64 || kvd % 64 || ffn % 64) throw std::invalid_argument("hidden, q_dim, kv_dim and ffn_dim must be multiples of 64");
+    if (qd != h) throw std::invalid_argument("num_q_heads*head_dim must equal hidden_size (the reference assumes it, TenzoEngine.cpp:1582)");
+    if (cfg.num_q_heads % cfg.num_kv_heads) throw std::invalid_argument("num_q_heads must be a multiple of num_kv_heads");
+    const int g = cfg.num_q_heads / cfg.num_kv_heads;
+    if (g != 1 && g != 2 && g != 4 && g != 8) throw std::invalid_argument("query group size must be 1, 2, 4 or 8");
+    if (h > 16384 || ffn > 16384) throw std::invalid_argument("hidden_size and ffn_dim are limited to 16384");
+
+    TZ_CUDA(cudaGetDevice(&device));
+    TZ_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+    TZ_CUDA(cudaEventCreate(&ev0));
+    TZ_CUDA(cudaEventCreate(&ev1));
+
+    layers.resize(L);
+    const size_t B = batch;
+    auto dalloc = [&](size_t bytes) -> void* {
+        void* p = nullptr;
+        TZ_CUDA(cudaMalloc(&p, bytes ? bytes : 16));
+        TZ_CUDA(cudaMemsetAsync(p, 0, bytes ? bytes : 16, stream));
+        owned.push_back(p);
+        return p;
+    };
+    d_tokens = (int*)dalloc(B * 4);
+    d_pos = (int*)dalloc(B * 4);
+    d_next = (int*)dalloc(B * 4);
+    b_x = (float*)dalloc(B * h * 4);
+    b_qkv = (float*)dalloc(B * (qd + 2 * kvd) * 4);
+    b_attn = (float*)dalloc(B * qd * 4);
+    b_h1 = (float*)dalloc(B * h * 4);
+    b_act = (float*)dalloc(B * ffn * 4);
+    b_logits = (float*)dalloc(B * V * 4);
+
+    kv_rows_per_seq = (size_t)L * cfg.num_kv_heads * cfg.max_seq_len;
+    cache_k = (int8_t*)dalloc(B * kv_rows_per_seq * 128);
+    cache_v = (int8_t*)dalloc(B * kv_rows_per_seq * 128);
+    scale_k = (float*)dalloc(B * kv_rows_per_seq * 4);
+    scale_v = (float*)dalloc(B * kv_rows_per_seq * 4);
+
+    // RoPE tables, computed on the host with the reference's float expressions (:466-469) so the
+    // rotation is bit-identical to a CPU run.
+    {
+        const int half = cfg.head_dim / 2;
+        std::vector<float> cs((size_t)cfg.max_seq_len * half), sn(cs.size());
+        std::vector<float> freq(half);
+        for (int i = 0; i < half; ++i) freq[i] = 1.0f / std::pow(rope_theta, static_cast<float>(2 * i) / cfg.head_dim);
+        for (int p = 0; p < cfg.max_seq_len; ++p)
+            for (int i = 0; i < half; ++i) {
+                const float ang = static_cast<float>(p) * freq[i];
+                cs[(size_t)p * half + i] = std::cos(ang);
+                sn[(size_t)p * half + i] = std::sin(ang);
+            }
+        rope_cos = (float*)dalloc(cs.size() * 4);
+        rope_sin = (float*)dalloc(sn.size() * 4);
+        TZ_CUDA(cudaMemcpyAsync(rope_cos, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice, stream));
+        TZ_CUDA(cudaMemcpyAsync(rope_sin, sn.data(), sn.size() * 4, cudaMemcpyHostToDevice, stream));
+        TZ_CUDA(cudaStreamSynchronize(stream));
+    }
+
+    const int widest_blocks = (qd + 2 * kvd > 2 * ffn ? qd + 2 * kvd : 2 * ffn) / 64;
+    splitk_acc = (int32_t*)dalloc(B * widest_blocks * 64 * 4);
+    splitk_cnt = (uint32_t*)dalloc(B * widest_blocks * 4);
+    attn_scratch = dalloc(tenzo_cuda_attention_scratch_bytes(batch, cfg.num_q_heads, cfg.max_seq_len));
+    lm_scratch = dalloc(tenzo_cuda_lm_head_scratch_bytes(batch));
+
+    TZ_CUDA(cudaMallocHost(&h_pin, (3 * B + 16) * sizeof(int)));
+    h_tokens = h_pin;
+    h_pos = h_pin + B;
+    h_next = h_pin + 2 * B;
+    seq_len.assign(batch, 0);
+    TZ_CUDA(cudaStreamSynchronize(stream));
+}
+
+Engine::~Engine() {
+    cudaStreamSynchronize(stream);
+    for (auto& kv : graphs) cudaGraphExecDestroy(kv.second);
+    for (void* p : owned) cudaFree(p);
+    if (h_pin) cudaFreeHost(h_pin);
+    if (d_history) cudaFree(d_history);
+    cudaEventDestroy(ev0);
+    cudaEventDestroy(ev1);
+    cudaStreamDestroy(stream);
+}
+
+void* Engine::upload(const void* host, size_t bytes) {
+    void* p = nullptr;
+    TZ_CUDA(cudaMalloc(&p, bytes));
+    owned.push_back(p);
+    TZ_CUDA(cudaMemcpy(p, host, bytes, cudaMemcpyHostToDevice));
+    return p;
+}
+
+void Engine::set_layer(int l, const tenzo_layer_weights_t& w) {
+    if (!w.q_w || !w.k_w || !w.v_w || !w.out_w) throw std::invalid_argument("q/k/v/out weights are required");
+    LayerDev& d = layers[l];
+    const size_t kb = (size_t)h / 4;                 // bytes per output row at K = hidden
+    const size_t q_bytes = (size_t)qd * kb, kv_bytes = (size_t)kvd * kb;
+    // q, k, v row blocks are laid back to back: blocks are self-contained in the TL1 layout, so
+    // the concatenation is itself a valid [60 blocks][K/2][32] matrix (one launch, one LUT, :1547).
+    if (!d.qkv) { TZ_CUDA(cudaMalloc((void**)&d.qkv, q_bytes + 2 * kv_bytes)); owned.push_back(d.qkv); }
+    TZ_CUDA(cudaMemcpy(d.qkv, w.q_w, q_bytes, cudaMemcpyHostToDevice));
+    TZ_CUDA(cudaMemcpy(d.qkv + q_bytes, w.k_w, kv_bytes, cudaMemcpyHostToDevice));
+    TZ_CUDA(cudaMemcpy(d.qkv + q_bytes + kv_bytes, w.v_w, kv_bytes, cudaMemcpyHostToDevice));
+    if (!d.o) { TZ_CUDA(cudaMalloc((void**)&d.o, (size_t)h * kb)); owned.push_back(d.o); }
+    TZ_CUDA(cudaMemcpy(d.o, w.out_w, (size_t)h * kb, cudaMemcpyHostToDevice));
+    d.has_mlp = w.gate_w && w.up_w && w.down_w;      // :1593
+    if (d.has_mlp) {
+        const size_t f_bytes = (size_t)ffn * kb, down_bytes = (size_t)h * ffn / 4;
+        if (!d.gateup) { TZ_CUDA(cudaMalloc((void**)&d.gateup, 2 * f_bytes)); owned.push_back(d.gateup); }
+        TZ_CUDA(cudaMemcpy(d.gateup, w.gate_w, f_bytes, cudaMemcpyHostToDevice));
+        TZ_CUDA(cudaMemcpy(d.gateup + f_bytes, w.up_w, f_bytes, cudaMemcpyHostToDevice));
+        if (!d.down) { TZ_CUDA(cudaMalloc((void**)&d.down, down_bytes)); owned.push_back(d.down); }
+        TZ_CUDA(cudaMemcpy(d.down, w.down_w, down_bytes, cudaMemcpyHostToDevice));
+    }
+    d.s_q = w.q_scale; d.s_k = w.k_scale; d.s_v = w.v_scale; d.s_o = w.out_scale;
+    d.s_gate = w.gate_scale; d.s_up = w.up_scale; d.s_down = w.down_scale;
+    auto norm = [&](float*& dst, const float* src, int n) {
+        if (!src) { dst = nullptr; return; }
+        if (!dst) { TZ_CUDA(cudaMalloc((void**)&dst, (size_t)n * 4)); owned.push_back(dst); }
+        TZ_CUDA(cudaMemcpy(dst, src, (size_t)n * 4, cudaMemcpyHostToDevice));
+    };
+    norm(d.in_norm, w.in_norm, h);
+    norm(d.attn_sub_norm, w.attn_sub_norm, h);
+    norm(d.post_norm, w.post_norm, h);
+    norm(d.ffn_sub_norm, w.ffn_sub_norm, ffn);
+    d.set = true;
+    invalidate_graphs();
+}
+
+void Engine::set_final_norm(const float* w) {
+    if (!final_norm) final_norm = (float*)upload(w, (size_t)h * 4);
+    else TZ_CUDA(cudaMemcpy(final_norm, w, (size_t)h * 4, cudaMemcpyHostToDevice));
+    invalidate_graphs();
+}
+
+void Engine::set_lm_head(const int8_t* w, const float* scales) {
+    if (!lm_w) {
+        lm_w = (int8_t*)upload(w, (size_t)V * h);
+        lm_scales = (float*)upload(scales, (size_t)V * 4);
+    } else {
+        TZ_CUDA(cudaMemcpy(lm_w, w, (size_t)V * h, cudaMemcpyHostToDevice));
+        TZ_CUDA(cudaMemcpy(lm_scales, scales, (size_t)V * 4, cudaMemcpyHostToDevice));
+    }
+    invalidate_graphs();
+}
+
+void Engine::invalidate_graphs() {
+    if (graphs.empty()) return;
+    cudaStreamSynchronize(stream);
+    for (auto& kv : graphs) cudaGraphExecDestroy(kv.second);
+    graphs.clear();
+}
+
+void Engine::enqueue_layer(int l, int max_len) {
+    const LayerDev& d = layers[l];
+    if (!d.set) throw std::runtime_error("layer weights were never set");
+    tenzo_tl1_gemv_args g;
+    std::memset(&g, 0, sizeof g);
+    g.eps = 1e-5f;
+    g.do_norm = 1;
+    g.batch = batch;
+    g.splitk_acc = splitk_acc;
+    g.splitk_cnt = splitk_cnt;
+    g.use_pdl = use_pdl;
+
+    // q | k | v
+    g.x = b_x; g.x_stride = h; g.norm_w = d.in_norm; g.w = d.qkv; g.K = h;
+    g.n_blocks = (qd + 2 * kvd) / 64;
+    g.seg_end[0] = qd / 64; g.seg_end[1] = (qd + kvd) / 64; g.seg_end[2] = g.n_blocks;
+    g.seg_scale[0] = d.s_q; g.seg_scale[1] = d.s_k; g.seg_scale[2] = d.s_v;
+    g.epilogue = TENZO_EPI_STORE; g.out = b_qkv; g.out_stride = qd + 2 * kvd;
+    TZ_KERNEL(tenzo_cuda_tl1_gemv(&g, stream));
+    launches += 1;
+
+    tenzo_attention_args a;
+    std::memset(&a, 0, sizeof a);
+    a.q = b_qkv; a.k = b_qkv + qd; a.v = b_qkv + qd + kvd;
+    a.out = b_attn;
+    a.cache_k = cache_k; a.cache_v = cache_v; a.scale_k = scale_k; a.scale_v = scale_v;
+    a.seq_stride_kv = kv_rows_per_seq * 128; a.seq_stride_sc = kv_rows_per_seq;
+    a.pos = d_pos; a.rope_cos = rope_cos; a.rope_sin = rope_sin;
+    a.layer = l; a.n_q = cfg.num_q_heads; a.n_kv = cfg.num_kv_heads; a.head_dim = 128;
+    a.max_seq = cfg.max_seq_len; a.batch = batch; a.max_len = max_len; a.append = 1;
+    a.scratch = attn_scratch; a.use_pdl = use_pdl;
+    a.q_stride = a.kv_stride = qd + 2 * kvd;
+    TZ_KERNEL(tenzo_cuda_attention_int8(&a, stream));
+    launches += 2;
+
+    // out projection + residual
+    g.x = b_attn; g.x_stride = qd; g.norm_w = d.attn_sub_norm; g.w = d.o; g.K = h;
+    g.n_blocks = h / 64; g.seg_end[0] = g.seg_end[1] = g.seg_end[2] = g.n_blocks; g.seg_scale[0] = d.s_o;
+    g.epilogue = TENZO_EPI_RESIDUAL; g.resid = b_x; g.out = b_h1; g.out_stride = h;
+    TZ_KERNEL(tenzo_cuda_tl1_gemv(&g, stream));
+    launches += 1;
+
+    if (d.has_mlp) {
+        g.x = b_h1; g.x_stride = h; g.norm_w = d.post_norm; g.w = d.gateup; g.K = h;
+        g.n_blocks = 2 * ffn / 64; g.seg_end[0] = ffn / 64; g.seg_end[1] = g.seg_end[2] = g.n_blocks;
+        g.seg_scale[0] = d.s_gate; g.seg_scale[1] = d.s_up;
+        g.epilogue = TENZO_EPI_RELU2_GLU; g.resid = nullptr; g.out = b_act; g.out_stride = ffn;
+        TZ_KERNEL(tenzo_cuda_tl1_gemv(&g, stream));
+
+        g.x = b_act; g.x_stride = ffn; g.norm_w = d.ffn_sub_norm; g.w = d.down; g.K = ffn;
+        g.n_blocks = h / 64; g.seg_end[0] = g.seg_end[1] = g.seg_end[2] = g.n_blocks; g.seg_scale[0] = d.s_down;
+        g.epilogue = TENZO_EPI_RESIDUAL; g.resid = b_h1; g.out = b_x; g.out_stride = h;
+        TZ_KERNEL(tenzo_cuda_tl1_gemv(&g, stream));
+        launches += 2;
+    } else {
+        TZ_CUDA(cudaMemcpyAsync(b_x, b_h1, (size_t)batch * h * 4, cudaMemcpyDeviceToDevice, stream));   // :1630
+    }
+}
+
+void Engine::enqueue_step(bool with_logits, bool feed_back, int max_len) {
+    if (!lm_w) throw std::runtime_error("LM head / embedding was never set");
+    TZ_KERNEL(tenzo_cuda_embedding_i8(lm_w, lm_scales, h, d_tokens, batch, b_x, h, stream));
+    launches += 1;
+    for (int l = 0; l < L; ++l) enqueue_layer(l, max_len);
+    if (with_logits) {
+        TZ_KERNEL(tenzo_cuda_lm_head_i8(b_x, final_norm, 1, 1e-5f, lm_w, lm_scales, V, h, batch, h, b_logits, nullptr,
+                                        d_next, lm_scratch, use_pdl, stream));
+        launches += 2;
+    }
+    advance_kernel<<<(batch + 127) / 128, 128, 0, stream>>>(d_pos, d_tokens, d_next, batch, feed_back ? 1 : 0);
+    TZ_CUDA(cudaGetLastError());
+    launches += 1;
+}
+
+static int bucket_for(int len, int max_seq) {
+    int b = 256;
+    while (b < len) b <<= 1;
+    return b < max_seq ? b : max_seq;
+}
+
+// One step for all sequences. The graph key is (with_logits, feed_back, attention bucket).
+void Engine::run_step(bool with_logits, bool feed_back) {
+    int longest = 0;
+    for (int s = 0; s < batch; ++s) {
+        if (seq_len[s] + 1 > cfg.max_seq_len) throw std::out_of_range("KV cache is full (max_seq_len reached)");
+        longest = seq_len[s] + 1 > longest ? seq_len[s] + 1 : longest;
+    }
+    const int max_len = bucket_for(longest, cfg.max_seq_len);
+    if (!use_graph) {
+        enqueue_step(with_logits, feed_back, max_len);
+    } else {
+        const int key = (with_logits ? 1 : 0) | (feed_back ? 2 : 0) | (max_len << 2);
+        auto it = graphs.find(key);
+        if (it == graphs.end()) {
+            const unsigned long long before = launches;
+            cudaGraph_t graph = nullptr;
+            TZ_CUDA(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
+            try {
+                enqueue_step(with_logits, feed_back, max_len);
+            } catch (...) {
+                cudaStreamEndCapture(stream, &graph);
+                if (graph) cudaGraphDestroy(graph);
+                launches = before;
+                throw;
+            }
+            TZ_CUDA(cudaStreamEndCapture(stream, &graph));
+            cudaGraphExec_t exec = nullptr;
+            cudaError_t e = cudaGraphInstantiate(&exec, graph, 0);
+            cudaGraphDestroy(graph);
+            if (e != cudaSuccess) throw CudaError(e, "cudaGraphInstantiate");
+            graph_kernels[key] = launches - before;
+            launches = before;
+            it = graphs.emplace(key, exec).first;
+        }
+        TZ_CUDA(cudaGraphLaunch(it->second, stream));
+        launches += graph_kernels[key];
+    }
+    for (int s = 0; s < batch; ++s) seq_len[s] += 1;   // :1831-1835, once per token
+}
+
+void Engine::push_state(const int* tokens) {
+    for (int s = 0; s < batch; ++s) {
+        if (tokens) {
+            if (tokens[s] < 0 || tokens[s] >= V) throw std::out_of_range("token id outside [0, vocab_size)");
+            h_tokens[s] = tokens[s];
+        }
+        h_pos[s] = seq_len[s];
+    }
+    if (tokens) TZ_CUDA(cudaMemcpyAsync(d_tokens, h_tokens, (size_t)batch * 4, cudaMemcpyHostToDevice, stream));
+    TZ_CUDA(cudaMemcpyAsync(d_pos, h_pos, (size_t)batch * 4, cudaMemcpyHostToDevice, stream));
+}
+
+void Engine::prefill(const int* tokens) {
+    push_state(tokens);
+    TZ_CUDA(cudaEventRecord(ev0, stream));
+    run_step(false, false);
+    TZ_CUDA(cudaEventRecord(ev1, stream));
+    TZ_CUDA(cudaStreamSynchronize(stream));
+}
+
+void Engine::generate(const int* cur, int* out) {
+    push_state(cur);
+    TZ_CUDA(cudaEventRecord(ev0, stream));
+    run_step(true, false);
+    TZ_CUDA(cudaEventRecord(ev1, stream));
+    TZ_CUDA(cudaMemcpyAsync(h_next, d_next, (size_t)batch * 4, cudaMemcpyDeviceToHost, stream));
+    TZ_CUDA(cudaStreamSynchronize(stream));
+    for (int s = 0; s < batch; ++s) out[s] = h_next[s];
+}
+
+void Engine::decode_greedy(const int* first, int n_steps, int* out) {
+    if (n_steps <= 0) return;
+    if ((size_t)n_steps * batch > history_cap) {
+        if (d_history) cudaFree(d_history);
+        d_history = nullptr;
+        TZ_CUDA(cudaMalloc((void**)&d_history, (size_t)n_steps * batch * 4));
+        history_cap = (size_t)n_steps * batch;
+    }
+    push_state(first);
+    TZ_CUDA(cudaEventRecord(ev0, stream));
+    for (int i = 0; i < n_steps; ++i) {
+        run_step(true, true);
+        record_tokens_kernel<<<(batch + 127) / 128, 128, 0, stream>>>(d_next, d_history, i, batch);
+        launches += 1;
+    }
+    TZ_CUDA(cudaEventRecord(ev1, stream));
+    TZ_CUDA(cudaMemcpyAsync(out, d_history, (size_t)n_steps * batch * 4, cudaMemcpyDeviceToHost, stream));
+    TZ_CUDA(cudaStreamSynchronize(stream));
+}
+
+void Engine::kv_fill(int len, unsigned long long seed) {
+    const size_t rows = (size_t)batch * kv_rows_per_seq;
+    kv_fill_kernel<<<148 * 16, 256, 0, stream>>>(cache_k, cache_v, scale_k, scale_v, rows, cfg.max_seq_len, len, seed);
+    TZ_CUDA(cudaGetLastError());
+    TZ_CUDA(cudaStreamSynchronize(stream));
+    for (auto& n : seq_len) n = len;
+}
+
+float Engine::last_ms() {
+    float ms = 0.0f;
+    if (cudaEventElapsedTime(&ms, ev0, ev1) != cudaSuccess) return -1.0f;
+    return ms;
+}
+
+// The reference sampler (TenzoEngine.cpp:1722-1807) on host logits, for the stochastic path and
+// for greedy decoding with a repetition penalty. Candidate order follows std::pair<float,int>.
+int Engine::sample_host(std::vector<float>& lg, const tenzo_sampling_params_t& p, const int* past, int n_past) {
+    int top_k = p.top_k < 1 ? 1 : (p.top_k > 64 ? 64 : p.top_k);
+    if (p.repetition_penalty != 1.0f && past && n_past > 0)
+        for (int i = 0; i < n_past; ++i) {
+            const int t = past[i];
+            if (t >= 0 && t < V) lg[t] = lg[t] > 0.0f ? lg[t] / p.repetition_penalty : lg[t] * p.repetition_penalty;
+        }
+    if (p.temperature <= 0.0f) {
+        int best = 0;
+        for (int i = 1; i < V; ++i)
+            if (lg[i] > lg[best]) best = i;
+        return best;
+    }
+    float cl[64];
+    int ci[64], n = 0;
+    for (int i = 0; i < V; ++i) {
+        const float l = lg[i];
+        if (n == top_k) {
+            if (!(l > cl[n - 1])) continue;
+            --n;
+        }
+        int q = n;
+        while (q > 0 && (cl[q - 1] < l || (!(l < cl[q - 1]) && ci[q - 1] < i))) { cl[q] = cl[q - 1]; ci[q] = ci[q - 1]; --q; }
+        cl[q] = l; ci[q] = i; ++n;
+    }
+    float probs[64], sum = 0.0f;
+    for (int i = 0; i < n; ++i) { probs[i] = std::exp((cl[i] - cl[0]) / p.temperature); sum += probs[i]; }
+    for (int i = 0; i < n; ++i) probs[i] /= sum;
+    float cum = 0.0f;
+    int cut = n;
+    for (int i = 0; i < n; ++i) { cum += probs[i]; if (cum >= p.top_p) { cut = i + 1; break; } }
+    float sub = 0.0f;
+    for (int i = 0; i < cut; ++i) sub += probs[i];
+    for (int i = 0; i < cut; ++i) probs[i] /= sub;
+    const float r = static_cast<float>(std::rand()) / static_cast<float>(RAND_MAX);   // :1800, process-global rand()
+    float acc = 0.0f;
+    for (int i = 0; i < cut; ++i) { acc += probs[i]; if (r <= acc) return ci[i]; }
+    return ci[0];
+}
+
+}  // namespace tz

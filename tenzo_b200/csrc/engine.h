@@ -1,0 +1,86 @@
+// Engine state shared between engine.cu (behaviour) and capi.cu (the extern "C" boundary).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <map>
+#include <string>
+#include <vector>
+
+#include "../../include/tenzo.h"
+#include "../../include/tenzo_ext.h"
+
+namespace tz {
+
+extern thread_local std::string g_last_error;
+void set_error(const std::string& m);
+
+struct LayerDev {
+    uint8_t* qkv = nullptr;      // q|k|v row blocks back to back, TL1 layout
+    uint8_t* o = nullptr;
+    uint8_t* gateup = nullptr;   // gate|up
+    uint8_t* down = nullptr;
+    float s_q = 1, s_k = 1, s_v = 1, s_o = 1, s_gate = 1, s_up = 1, s_down = 1;
+    float *in_norm = nullptr, *attn_sub_norm = nullptr, *post_norm = nullptr, *ffn_sub_norm = nullptr;
+    bool has_mlp = false, set = false;
+};
+
+class Engine {
+public:
+    Engine(const tenzo_config_t& cfg, const tenzo_ext_options_t& opt);
+    ~Engine();
+    Engine(const Engine&) = delete;
+    Engine& operator=(const Engine&) = delete;
+
+    void set_layer(int l, const tenzo_layer_weights_t& w);
+    void set_final_norm(const float* w);
+    void set_lm_head(const int8_t* w, const float* scales);
+
+    void prefill(const int* tokens);                       // one token per sequence, no logits
+    void generate(const int* cur, int* out);               // device argmax
+    void decode_greedy(const int* first, int n_steps, int* out);
+    int sample_host(std::vector<float>& logits, const tenzo_sampling_params_t& p, const int* past, int n_past);
+
+    void push_state(const int* tokens);
+    void run_step(bool with_logits, bool feed_back);
+    void enqueue_step(bool with_logits, bool feed_back, int max_len);
+    void enqueue_layer(int l, int max_len);
+    void invalidate_graphs();
+    void* upload(const void* host, size_t bytes);
+    float last_ms();
+    void kv_fill(int len, unsigned long long seed);
+
+    tenzo_config_t cfg;
+    int batch = 1, device = 0, use_graph = 1, use_pdl = 1;
+    float rope_theta = 10000.0f;
+    int h = 0, qd = 0, kvd = 0, ffn = 0, L = 0, V = 0;
+    cudaStream_t stream = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    std::vector<LayerDev> layers;
+    float* final_norm = nullptr;
+    int8_t* lm_w = nullptr;
+    float* lm_scales = nullptr;
+
+    int *d_tokens = nullptr, *d_pos = nullptr, *d_next = nullptr, *d_history = nullptr;
+    size_t history_cap = 0;
+    float *b_x = nullptr, *b_qkv = nullptr, *b_attn = nullptr, *b_h1 = nullptr, *b_act = nullptr, *b_logits = nullptr;
+    int8_t *cache_k = nullptr, *cache_v = nullptr;
+    float *scale_k = nullptr, *scale_v = nullptr;
+    size_t kv_rows_per_seq = 0;
+    float *rope_cos = nullptr, *rope_sin = nullptr;
+    int32_t* splitk_acc = nullptr;
+    uint32_t* splitk_cnt = nullptr;
+    void *attn_scratch = nullptr, *lm_scratch = nullptr;
+    int *h_pin = nullptr, *h_tokens = nullptr, *h_pos = nullptr, *h_next = nullptr;
+    std::vector<int> seq_len;
+    std::vector<void*> owned;
+    std::map<int, cudaGraphExec_t> graphs;
+    std::map<int, unsigned long long> graph_kernels;
+    unsigned long long launches = 0;
+};
+
+}  // namespace tz
+
+struct tenzo_engine_opaque {
+    tz::Engine* impl;
+};

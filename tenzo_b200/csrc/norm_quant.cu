@@ -1,0 +1,79 @@
+// Standalone fused RMSNorm + per-token absmax quantiser (both flavours the reference uses).
+//
+// qmax = 31 : the quantiser half of build_lut — floor 1e-6, q = round(y*(31/m)), scale m/31
+//             (src/runtime/TenzoEngine.cpp:27-42 of the reference).
+// qmax = 127: compute_logits' quantiser — floor 1e-8, s = amax/127, q = clamp(round(y*(1/s)))
+//             (:1666-1678).
+// The GEMV and LM-head kernels carry the same code in their prologues; this entry exists for the
+// backend class's executeRMSNorm and for checking the quantiser on its own.
+#include "common.cuh"
+#include "../../include/tenzo_kernels.h"
+
+namespace tz {
+
+constexpr int kNqThreads = 256;
+
+__global__ void __launch_bounds__(kNqThreads) rmsnorm_quant_kernel(
+    const float* __restrict__ x, const float* __restrict__ norm_w, int do_norm, float eps, int dim, int qmax,
+    int x_stride, float* y_out, int8_t* q_out, float* scale_out) {
+    extern __shared__ float s_y[];            // dim floats + 32 scratch
+    float* s_f = s_y + dim;
+    const int tid = threadIdx.x, seq = blockIdx.x;
+    const float* xs = x + (size_t)seq * x_stride;
+
+    float ss = 0.0f;
+    for (int i = tid; i < dim; i += kNqThreads) {
+        const float v = xs[i];
+        s_y[i] = v;
+        ss += v * v;
+    }
+    float m = 0.0f;
+    if (do_norm) {
+        ss = block_sum(ss, s_f);
+        const float inv_rms = rms_inv(ss, dim, eps);
+        for (int i = tid; i < dim; i += kNqThreads) {
+            const float y = rms_apply(s_y[i], inv_rms, norm_w, i);
+            s_y[i] = y;
+            m = fmaxf(m, fabsf(y));
+        }
+    } else {
+        for (int i = tid; i < dim; i += kNqThreads) m = fmaxf(m, fabsf(s_y[i]));
+    }
+    if (y_out)
+        for (int i = tid; i < dim; i += kNqThreads) y_out[(size_t)seq * dim + i] = s_y[i];
+    if (!q_out && !scale_out) return;
+    m = block_max(m, s_f);
+    if (qmax == 31) {
+        m = fmaxf(m, 1e-6f);
+        const float to_q = 31.0f / m;
+        if (q_out)
+            for (int i = tid; i < dim; i += kNqThreads)
+                q_out[(size_t)seq * dim + i] = (int8_t)(int)roundf(s_y[i] * to_q);
+        if (scale_out && tid == 0) scale_out[seq] = m / 31.0f;
+    } else {
+        m = fmaxf(m, 1e-8f);
+        const float s = m / 127.0f, inv = 1.0f / s;
+        if (q_out)
+            for (int i = tid; i < dim; i += kNqThreads)
+                q_out[(size_t)seq * dim + i] = (int8_t)(int)fminf(fmaxf(roundf(s_y[i] * inv), -128.0f), 127.0f);
+        if (scale_out && tid == 0) scale_out[seq] = s;
+    }
+}
+
+}  // namespace tz
+
+extern "C" int tenzo_cuda_rmsnorm_quant(const float* x, const float* norm_w, int do_norm, float eps, int dim,
+                                        int qmax, int batch, int x_stride, float* y_out, int8_t* q_out,
+                                        float* scale_out, void* stream) {
+    if (!x || dim <= 0 || batch <= 0 || (qmax != 31 && qmax != 127)) return -1;
+    if (dim > 16384) return -5;
+    const size_t smem = (size_t)(dim + 32) * sizeof(float);
+    if (smem > 48 * 1024) {
+        cudaError_t ea = cudaFuncSetAttribute(tz::rmsnorm_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024);
+        if (ea != cudaSuccess) return (int)ea;
+    }
+    tz::rmsnorm_quant_kernel<<<batch, tz::kNqThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+        x, norm_w, do_norm, eps, dim, qmax, x_stride, y_out, q_out, scale_out);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : (int)e;
+}
