@@ -20,7 +20,7 @@
 
 namespace tenzo {
 
-class CUDARuntime {
+class __attribute__((visibility("default"))) CUDARuntime {
 public:
     static CUDARuntime& getInstance();
 

@@ -66,6 +66,11 @@ TENZO_API tenzo_status_t tenzo_ext_run_layer(tenzo_engine_t engine, int layer);
 TENZO_API tenzo_status_t tenzo_ext_synchronize(tenzo_engine_t engine);
 /* Device time of the most recent step / decode_greedy call, from CUDA events on the engine's stream (ms). */
 TENZO_API float tenzo_ext_last_device_ms(tenzo_engine_t engine);
+/* Measurement aid: runs the engine's own TL1 matrices (q|k|v, out, gate|up, down of every layer,
+ * in layer order, on the engine's activation buffers) `iters` times back to back with no attention
+ * or LM head in between, and returns the CUDA-event time in ms (< 0 on failure). *launches
+ * receives the number of GEMV kernels timed. */
+TENZO_API float tenzo_ext_bench_gemv_stack(tenzo_engine_t engine, int iters, unsigned long long* launches);
 /* Number of kernels launched (or replayed through a graph) since the engine was created. */
 TENZO_API unsigned long long tenzo_ext_kernel_launches(tenzo_engine_t engine);
 /* Message for the most recent failure on this thread ("" if none). */

@@ -222,7 +222,7 @@ __global__ void __launch_bounds__(kHd) attn_merge_kernel(const AttnLaunch L) {
     const tenzo_attention_args& a = L.a;
     const int qh = blockIdx.x, seq = blockIdx.y, d = threadIdx.x;
     const int T = a.pos[seq] + 1;
-    const int active = (T + kChunk - 1) / kChunk;
+    const int active = min((T + kChunk - 1) / kChunk, L.n_splits);
     const size_t base = ((size_t)seq * a.n_q + qh) * L.n_splits;
     float M = -1e30f;
     for (int i = 0; i < active; ++i) M = fmaxf(M, L.part_ml[(base + i) * 2]);

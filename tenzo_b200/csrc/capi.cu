@@ -350,6 +350,16 @@ tenzo_status_t tenzo_ext_synchronize(tenzo_engine_t engine) {
 
 float tenzo_ext_last_device_ms(tenzo_engine_t engine) { return live(engine) ? engine->impl->last_ms() : -1.0f; }
 
+float tenzo_ext_bench_gemv_stack(tenzo_engine_t engine, int iters, unsigned long long* launches) {
+    if (!live(engine) || iters <= 0) return -1.0f;
+    float ms = -1.0f;
+    guarded([&]() -> tenzo_status_t {
+        ms = engine->impl->bench_gemv_stack(iters, launches);
+        return TENZO_SUCCESS;
+    });
+    return ms;
+}
+
 unsigned long long tenzo_ext_kernel_launches(tenzo_engine_t engine) { return live(engine) ? engine->impl->launches : 0ull; }
 
 const char* tenzo_ext_last_error(void) { return tz::g_last_error.c_str(); }

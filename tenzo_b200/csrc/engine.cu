@@ -258,7 +258,7 @@ void Engine::invalidate_graphs() {
     graphs.clear();
 }
 
-void Engine::enqueue_layer(int l, int max_len) {
+void Engine::enqueue_layer(int l, int max_len, bool gemv_only) {
     const LayerDev& d = layers[l];
     if (!d.set) throw std::runtime_error("layer weights were never set");
     tenzo_tl1_gemv_args g;
@@ -290,8 +290,10 @@ void Engine::enqueue_layer(int l, int max_len) {
     a.max_seq = cfg.max_seq_len; a.batch = batch; a.max_len = max_len; a.append = 1;
     a.scratch = attn_scratch; a.use_pdl = use_pdl;
     a.q_stride = a.kv_stride = qd + 2 * kvd;
-    TZ_KERNEL(tenzo_cuda_attention_int8(&a, stream));
-    launches += 2;
+    if (!gemv_only) {
+        TZ_KERNEL(tenzo_cuda_attention_int8(&a, stream));
+        launches += 2;
+    }
 
     // out projection + residual
     g.x = b_attn; g.x_stride = qd; g.norm_w = d.attn_sub_norm; g.w = d.o; g.K = h;
@@ -434,6 +436,40 @@ void Engine::kv_fill(int len, unsigned long long seed) {
     TZ_CUDA(cudaGetLastError());
     TZ_CUDA(cudaStreamSynchronize(stream));
     for (auto& n : seq_len) n = len;
+}
+
+float Engine::bench_gemv_stack(int iters, unsigned long long* n_launches) {
+    const unsigned long long before = launches;
+    cudaGraph_t graph = nullptr;
+    TZ_CUDA(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
+    try {
+        for (int l = 0; l < L; ++l) enqueue_layer(l, 1, true);
+    } catch (...) {
+        cudaStreamEndCapture(stream, &graph);
+        if (graph) cudaGraphDestroy(graph);
+        launches = before;
+        throw;
+    }
+    TZ_CUDA(cudaStreamEndCapture(stream, &graph));
+    const unsigned long long per_iter = launches - before;
+    launches = before;
+    cudaGraphExec_t exec = nullptr;
+    cudaError_t e = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) throw CudaError(e, "cudaGraphInstantiate");
+    TZ_CUDA(cudaEventRecord(ev0, stream));
+    for (int i = 0; i < iters; ++i) {
+        e = cudaGraphLaunch(exec, stream);
+        if (e != cudaSuccess) break;
+    }
+    cudaEventRecord(ev1, stream);
+    cudaError_t es = cudaStreamSynchronize(stream);
+    cudaGraphExecDestroy(exec);
+    if (e != cudaSuccess) throw CudaError(e, "cudaGraphLaunch");
+    if (es != cudaSuccess) throw CudaError(es, "cudaStreamSynchronize");
+    launches += per_iter * iters;
+    if (n_launches) *n_launches = per_iter * iters;
+    return last_ms();
 }
 
 float Engine::last_ms() {

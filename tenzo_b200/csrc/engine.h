@@ -44,7 +44,8 @@ public:
     void push_state(const int* tokens);
     void run_step(bool with_logits, bool feed_back);
     void enqueue_step(bool with_logits, bool feed_back, int max_len);
-    void enqueue_layer(int l, int max_len);
+    void enqueue_layer(int l, int max_len, bool gemv_only = false);
+    float bench_gemv_stack(int iters, unsigned long long* n_launches);
     void invalidate_graphs();
     void* upload(const void* host, size_t bytes);
     float last_ms();

@@ -1,0 +1,203 @@
+"""RMSNorm+quantiser, fused attention and LM head on the GPU against the oracle / golden vectors."""
+import hashlib
+
+import numpy as np
+import pytest
+import torch
+from gpu_helpers import cpu_rms_norm, dev, host
+from helpers import ora, rel_err, synth
+
+pytestmark = pytest.mark.gpu
+P = ora.ptr
+FP_TOL = 1e-3   # north-star tolerance for floating-point outputs (relative to the tensor's max)
+
+
+@pytest.mark.parametrize("dim", [64, 100, 2560, 6912])
+def test_rmsnorm_quant_golden(cuda_lib, golden, dim):
+    from tenzo_b200 import kernels
+    g = golden["rmsnorm_quant"]
+    x, w = g[f"d{dim}_x"], g[f"d{dim}_w"]
+    y, _, _ = kernels.rmsnorm_quant(dev(x[None]), dev(w), qmax=31)
+    # quantiser alone on the reference's own normalised vector: exact
+    _, q, s = kernels.rmsnorm_quant(dev(g[f"d{dim}_y"][None]), None, do_norm=False, qmax=31)
+    torch.cuda.synchronize()
+    assert rel_err(host(y)[0], g[f"d{dim}_y"]) < 1e-6
+    assert np.array_equal(host(q)[0], g[f"d{dim}_a"]) and np.float32(host(s)[0]) == g[f"d{dim}_inv"]
+
+
+def test_quant127_matches_oracle(cuda_lib):
+    from tenzo_b200 import kernels
+    O = ora.load_oracle()
+    rng = np.random.default_rng(51)
+    x = np.stack([rng.standard_normal(2560).astype(np.float32) * s for s in (1e-3, 1.0, 50.0)] + [np.zeros(2560, np.float32)])
+    _, q, s = kernels.rmsnorm_quant(dev(x), None, do_norm=False, qmax=127)
+    torch.cuda.synchronize()
+    for b in range(4):
+        q8 = np.zeros(2560, np.int8)
+        sx = O.ora_act_quant127(P(x[b], ora.c_f32p), 2560, P(q8, ora.c_i8p))
+        assert np.array_equal(host(q)[b], q8) and np.float32(host(s)[b]) == np.float32(sx)
+
+
+def rope_tables(max_seq, theta):
+    O = ora.load_oracle()
+    cs, sn = np.zeros((max_seq, 64), np.float32), np.zeros((max_seq, 64), np.float32)
+    for p in range(max_seq):
+        O.ora_rope_table(p, 128, theta, P(cs[p], ora.c_f32p), P(sn[p], ora.c_f32p))
+    return cs, sn
+
+
+@pytest.mark.parametrize("theta", [10000.0, 500000.0])
+def test_attention_token_by_token(cuda_lib, theta):
+    """Decode 300 tokens through the fused kernel; the appended int8 rows and scales must equal the
+    oracle's bit for bit, the fp32 outputs within tolerance. Covers chunk boundaries 255/256/257."""
+    from tenzo_b200 import kernels
+    O = ora.load_oracle()
+    L, nq, nkv, hd, ms, steps = 2, 8, 2, 128, 320, 300
+    rng = np.random.default_rng(13)
+    q = rng.standard_normal((steps, nq * hd)).astype(np.float32)
+    k = rng.standard_normal((steps, nkv * hd)).astype(np.float32)
+    v = rng.standard_normal((steps, nkv * hd)).astype(np.float32)
+    cs, sn = rope_tables(ms, theta)
+    dcs, dsn = dev(cs), dev(sn)
+    ck = torch.zeros(1, L, nkv, ms, hd, dtype=torch.int8, device="cuda")
+    cv = torch.zeros_like(ck)
+    sk = torch.zeros(1, L, nkv, ms, dtype=torch.float32, device="cuda")
+    sv = torch.zeros_like(sk)
+    ock, ocv = np.zeros(L * nkv * ms * hd, np.int8), np.zeros(L * nkv * ms * hd, np.int8)
+    osk, osv = np.zeros(L * nkv * ms, np.float32), np.zeros(L * nkv * ms, np.float32)
+    worst = 0.0
+    for t in range(steps):
+        out = kernels.attention_int8(dev(q[t][None]), dev(k[t][None]), dev(v[t][None]), ck, cv, sk, sv,
+                                     torch.tensor([t], dtype=torch.int32, device="cuda"), layer=1, n_q=nq, n_kv=nkv,
+                                     max_seq=ms, rope_cos=dcs, rope_sin=dsn, max_len=t + 1)
+        qq, kk, vv, o = q[t].copy(), k[t].copy(), v[t].copy(), np.zeros(nq * hd, np.float32)
+        O.ora_attention_int8(1, t, nq, nkv, hd, ms, theta, P(qq, ora.c_f32p), P(kk, ora.c_f32p), P(vv, ora.c_f32p), P(o, ora.c_f32p),
+                             P(ock, ora.c_i8p), P(ocv, ora.c_i8p), P(osk, ora.c_f32p), P(osv, ora.c_f32p))
+        worst = max(worst, rel_err(host(out)[0], o))
+    assert worst < FP_TOL, f"attention output relative error {worst}"
+    assert np.array_equal(host(ck).reshape(-1), ock) and np.array_equal(host(cv).reshape(-1), ocv)
+    assert np.array_equal(host(sk).reshape(-1), osk) and np.array_equal(host(sv).reshape(-1), osv)
+
+
+def test_attention_golden_outputs(cuda_lib, golden):
+    """Imported reference cache + the reference's outputs at selected positions (append disabled)."""
+    from tenzo_b200 import kernels
+    g = golden["attention"]
+    L, nq, nkv, hd, ms, steps = (int(v) for v in g["dims"])
+    rng = np.random.default_rng(13)
+    q = rng.standard_normal((steps, nq * hd)).astype(np.float32)
+    k = rng.standard_normal((steps, nkv * hd)).astype(np.float32)
+    v = rng.standard_normal((steps, nkv * hd)).astype(np.float32)
+    assert hashlib.sha256(np.concatenate([q, k, v], axis=1).tobytes()).hexdigest() == str(g["qkv_sha"])
+    ck = torch.zeros(1, 1, nkv, ms, hd, dtype=torch.int8, device="cuda")
+    cv = torch.zeros_like(ck)
+    sk = torch.zeros(1, 1, nkv, ms, dtype=torch.float32, device="cuda")
+    sv = torch.zeros_like(sk)
+    ck[0, 0, :, :steps], cv[0, 0, :, :steps] = dev(g["cache_k"]), dev(g["cache_v"])
+    sk[0, 0, :, :steps], sv[0, 0, :, :steps] = dev(g["scale_k"]), dev(g["scale_v"])
+    cs, sn = rope_tables(ms, 10000.0)
+    for i, t in enumerate(int(t) for t in g["keep"]):
+        out = kernels.attention_int8(dev(q[t][None]), None, None, ck, cv, sk, sv, torch.tensor([t], dtype=torch.int32, device="cuda"),
+                                     layer=0, n_q=nq, n_kv=nkv, max_seq=ms, rope_cos=dev(cs), rope_sin=dev(sn), append=False)
+        assert rel_err(host(out)[0], g["outs"][i]) < FP_TOL, f"position {t}"
+
+
+def test_attention_batched_ragged_lengths(cuda_lib):
+    """Sequences of different lengths in one launch (batch 3, GQA group 4, context up to 700)."""
+    from tenzo_b200 import kernels
+    O = ora.load_oracle()
+    B, nq, nkv, hd, ms = 3, 20, 5, 128, 768
+    lens = [1, 256, 700]
+    rng = np.random.default_rng(52)
+    ck = rng.integers(-127, 128, (B, 1, nkv, ms, hd)).astype(np.int8)
+    cv = rng.integers(-127, 128, (B, 1, nkv, ms, hd)).astype(np.int8)
+    sk = (0.01 + 0.02 * rng.random((B, 1, nkv, ms))).astype(np.float32)
+    sv = (0.01 + 0.02 * rng.random((B, 1, nkv, ms))).astype(np.float32)
+    q = rng.standard_normal((B, nq * hd)).astype(np.float32)
+    k = rng.standard_normal((B, nkv * hd)).astype(np.float32)
+    v = rng.standard_normal((B, nkv * hd)).astype(np.float32)
+    cs, sn = rope_tables(ms, 10000.0)
+    pos = np.array([n - 1 for n in lens], np.int32)
+    dck, dcv, dsk, dsv = dev(ck), dev(cv), dev(sk), dev(sv)
+    out = kernels.attention_int8(dev(q), dev(k), dev(v), dck, dcv, dsk, dsv, dev(pos), layer=0, n_q=nq, n_kv=nkv, max_seq=ms,
+                                 rope_cos=dev(cs), rope_sin=dev(sn))
+    torch.cuda.synchronize()
+    for b in range(B):
+        ock, ocv, osk, osv = ck[b].reshape(-1).copy(), cv[b].reshape(-1).copy(), sk[b].reshape(-1).copy(), sv[b].reshape(-1).copy()
+        qq, kk, vv, o = q[b].copy(), k[b].copy(), v[b].copy(), np.zeros(nq * hd, np.float32)
+        O.ora_attention_int8(0, int(pos[b]), nq, nkv, hd, ms, 10000.0, P(qq, ora.c_f32p), P(kk, ora.c_f32p), P(vv, ora.c_f32p),
+                             P(o, ora.c_f32p), P(ock, ora.c_i8p), P(ocv, ora.c_i8p), P(osk, ora.c_f32p), P(osv, ora.c_f32p))
+        assert rel_err(host(out)[b], o) < FP_TOL
+        assert np.array_equal(host(dck)[b].reshape(-1), ock) and np.array_equal(host(dsv)[b].reshape(-1), osv)
+
+
+def test_lm_head_golden_and_argmax(cuda_lib, golden):
+    from tenzo_b200 import kernels
+    g = golden["lm_head"]
+    w, s, x, fn = g["w"], g["s"], g["x"], g["final_norm"]
+    lg, _, arg = kernels.lm_head_i8(dev(x[None]), dev(w), dev(s), norm_w=dev(fn))
+    y = cpu_rms_norm(x, fn)
+    lg2, acc2, arg2 = kernels.lm_head_i8(dev(y[None]), dev(w), dev(s), do_norm=False, want_acc=True)
+    torch.cuda.synchronize()
+    assert np.array_equal(host(lg2)[0], g["logits"])                 # teacher-forced: exact
+    assert np.array_equal(host(acc2)[0], w.astype(np.int32) @ g["x8"].astype(np.int32))
+    assert rel_err(host(lg)[0], g["logits"]) < FP_TOL
+    assert int(host(arg2)[0]) == int(np.argmax(g["logits"])) == int(host(arg)[0])
+
+
+def test_lm_head_first_maximum_wins(cuda_lib):
+    """Duplicate rows give equal logits; greedy keeps the lowest index (TenzoEngine.cpp:1749)."""
+    from tenzo_b200 import kernels
+    rng = np.random.default_rng(53)
+    V, H = 5000, 256
+    w = rng.integers(-127, 128, (V, H)).astype(np.int8)
+    s = np.full(V, 0.01, np.float32)
+    x = rng.standard_normal((1, H)).astype(np.float32)
+    lg, _, _ = kernels.lm_head_i8(dev(x), dev(w), dev(s), do_norm=False)
+    best = int(np.argmax(host(lg)[0]))
+    for dup in (best + 1234, best - 7 if best >= 7 else best + 77, V - 1):
+        w[dup % V] = w[best]
+    lg, _, arg = kernels.lm_head_i8(dev(x), dev(w), dev(s), do_norm=False)
+    torch.cuda.synchronize()
+    l = host(lg)[0]
+    assert int(host(arg)[0]) == int(np.argmax(l)) == min(i for i in range(V) if l[i] == l.max())
+
+
+def test_full_vocab_lm_head_properties(cuda_lib):
+    """128256 x 2560 (the benchmark shape): checksum of int32 accumulators against numpy."""
+    from tenzo_b200 import kernels
+    rng = np.random.default_rng(54)
+    V, H = 128256, 2560
+    w = rng.integers(-127, 128, (V, H), dtype=np.int8)
+    s = (0.001 + 0.001 * rng.random(V)).astype(np.float32)
+    x = rng.standard_normal((1, H)).astype(np.float32)
+    lg, acc, arg = kernels.lm_head_i8(dev(x), dev(w), dev(s), do_norm=False, want_acc=True)
+    _, q, sx = kernels.rmsnorm_quant(dev(x), None, do_norm=False, qmax=127)
+    torch.cuda.synchronize()
+    x8 = host(q)[0].astype(np.int64)
+    rows = rng.integers(0, V, 512)
+    assert np.array_equal(host(acc)[0][rows], (w[rows].astype(np.int64) @ x8).astype(np.int32))
+    assert int(host(acc)[0].astype(np.int64).sum()) == int(w.astype(np.int64).sum(axis=0) @ x8)
+    l = host(lg)[0]
+    assert int(host(arg)[0]) == int(np.argmax(l))
+    assert np.array_equal(l[rows], host(acc)[0][rows].astype(np.float32) * (np.float32(host(sx)[0]) * s[rows]))
+
+
+def test_embedding_and_repack(cuda_lib):
+    from tenzo_b200 import kernels
+    O = ora.load_oracle()
+    rng = np.random.default_rng(55)
+    w = rng.integers(-127, 128, (300, 256)).astype(np.int8)
+    s = rng.random(300).astype(np.float32)
+    toks = np.array([0, 299, 17], np.int32)
+    x = kernels.embedding_i8(dev(w), dev(s), dev(toks))
+    N, K = 192, 70
+    t = rng.integers(-1, 2, (N, K)).astype(np.int8)
+    raw = np.zeros((N // 4, K), np.uint8)
+    for r in range(N):
+        raw[r // 4] |= ((t[r] + 1).astype(np.uint8) << (2 * (r % 4)))
+    packed = kernels.tl1_pack_rows2bit(dev(raw), N, K)
+    torch.cuda.synchronize()
+    for i, tok in enumerate(toks):
+        assert np.array_equal(host(x)[i], w[tok].astype(np.float32) * s[tok])
+    assert np.array_equal(host(packed), synth.pack_tl1(t))

@@ -1,0 +1,153 @@
+"""TL1 GEMV on the GPU through the C ABI against the CPU oracle: int32 accumulators, quantised
+activations and the fp32 epilogue must be bit-identical on identical fp32 inputs."""
+import hashlib
+
+import numpy as np
+import pytest
+import torch
+from gpu_helpers import cpu_bitlinear, cpu_rms_norm, dev, host
+from helpers import ora, rel_err, synth
+
+pytestmark = pytest.mark.gpu
+P = ora.ptr
+
+
+def sha(a):
+    return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
+
+
+@pytest.mark.parametrize("name", ["k2", "k64", "ragged", "mid", "cfg0", "down"])
+def test_against_reference_golden_vectors(cuda_lib, golden, name):
+    from tenzo_b200 import kernels
+    g = golden["tl1_gemv"]
+    N, K = (int(v) for v in g[f"{name}_shape"])
+    if f"{name}_w" in g.files:
+        w = g[f"{name}_w"]
+    else:
+        w = synth.random_tl1_packed(np.random.default_rng([11, N, K]), N, K)
+        assert sha(w) == str(g[f"{name}_wsha"])
+    r = kernels.tl1_gemv(dev(g[f"{name}_x"][None]), dev(w), N // 64, K, [float(g[f"{name}_scale"])], want_acc=True, want_act=True)
+    torch.cuda.synchronize()
+    assert np.array_equal(host(r["acc"])[0], g[f"{name}_acc"]), "int32 accumulators differ"
+    assert np.float32(host(r["inv"])[0]) == g[f"{name}_inv"]
+    assert np.array_equal(host(r["out"])[0], g[f"{name}_out"]), "fp32 outputs differ"
+
+
+@pytest.mark.parametrize("N,K", [(64, 2), (64, 4), (64, 126), (64, 128), (128, 130), (192, 258), (256, 384), (640, 2560),
+                                 (2560, 2560), (6912, 2560), (2560, 6912), (4096, 4096), (128, 16384)])
+@pytest.mark.parametrize("batch", [1, 3])
+def test_bit_exact_on_seeded_inputs(cuda_lib, N, K, batch):
+    from tenzo_b200 import kernels
+    rng = np.random.default_rng([41, N, K, batch])
+    w = synth.random_tl1_packed(rng, N, K)
+    x = (rng.standard_normal((batch, K)) * np.float32(10.0) ** rng.integers(-2, 3, (batch, 1))).astype(np.float32)
+    scale = float(synth.weight_scale(rng))
+    r = kernels.tl1_gemv(dev(x), dev(w), N // 64, K, [scale], want_acc=True, want_act=True)
+    torch.cuda.synchronize()
+    O = ora.load_oracle()
+    for b in range(batch):
+        out, acc, inv = cpu_bitlinear(x[b], w, N, K, scale)
+        a = np.zeros(K, np.int8)
+        O.ora_act_quant31(P(x[b], ora.c_f32p), K, P(a, ora.c_i8p))
+        assert np.array_equal(host(r["a"])[b], a), "quantised activations differ"
+        assert np.float32(host(r["inv"])[b]) == inv
+        assert np.array_equal(host(r["acc"])[b], acc), "int32 accumulators differ"
+        assert np.array_equal(host(r["out"])[b], out), "fp32 outputs differ"
+
+
+def test_edge_activations(cuda_lib):
+    """All-zero input (1e-6 floor), a single spike, exact .5 rounding ties, saturating +-31."""
+    from tenzo_b200 import kernels
+    N, K = 128, 256
+    rng = np.random.default_rng(42)
+    w = synth.random_tl1_packed(rng, N, K)
+    xs = np.zeros((4, K), np.float32)
+    xs[1, 17] = -3.0
+    xs[2] = np.float32(31.0) * np.sign(rng.standard_normal(K)).astype(np.float32)
+    xs[3] = (np.arange(K) % 63 - 31).astype(np.float32) + np.float32(0.5) * (np.arange(K) % 2)
+    xs[3, 0] = 31.0
+    r = kernels.tl1_gemv(dev(xs), dev(w), N // 64, K, [0.5], want_acc=True)
+    torch.cuda.synchronize()
+    for b in range(4):
+        out, acc, _ = cpu_bitlinear(xs[b], w, N, K, 0.5)
+        assert np.array_equal(host(r["acc"])[b], acc) and np.array_equal(host(r["out"])[b], out)
+    assert not host(r["acc"])[0].any()
+
+
+def test_fused_qkv_segments_and_norm(cuda_lib):
+    """The q|k|v launch: three scale segments, RMSNorm fused in front (TenzoEngine.cpp:1542-1572)."""
+    from tenzo_b200 import kernels
+    h, qd, kvd = 2560, 2560, 640
+    rng = np.random.default_rng(43)
+    ws = [synth.random_tl1_packed(rng, n, h) for n in (qd, kvd, kvd)]
+    scales = [0.011, 0.017, 0.023]
+    x = (2.5 * rng.standard_normal((2, h))).astype(np.float32)
+    nw = (1 + 0.1 * rng.standard_normal(h)).astype(np.float32)
+    wcat = np.concatenate(ws)
+    nb = (qd + 2 * kvd) // 64
+    # teacher-forced: normalise on the CPU, quantise + multiply on the GPU -> exact
+    y = np.stack([cpu_rms_norm(x[b], nw) for b in range(2)])
+    r = kernels.tl1_gemv(dev(y), dev(wcat), nb, h, scales, [qd // 64, (qd + kvd) // 64, nb], want_acc=True)
+    # fused: normalise on the GPU too -> fp32 tolerance
+    rf = kernels.tl1_gemv(dev(x), dev(wcat), nb, h, scales, [qd // 64, (qd + kvd) // 64, nb], norm_w=dev(nw), do_norm=True)
+    torch.cuda.synchronize()
+    for b in range(2):
+        ref = np.concatenate([cpu_bitlinear(y[b], w, n, h, s)[0] for w, n, s in zip(ws, (qd, kvd, kvd), scales)])
+        acc = np.concatenate([cpu_bitlinear(y[b], w, n, h, s)[1] for w, n, s in zip(ws, (qd, kvd, kvd), scales)])
+        assert np.array_equal(host(r["acc"])[b], acc)
+        assert np.array_equal(host(r["out"])[b], ref)
+        assert rel_err(host(rf["out"])[b], ref) < 1e-3   # north-star tolerance for floating point
+
+
+def test_residual_and_glu_epilogues(cuda_lib):
+    from tenzo_b200 import kernels
+    h, f = 512, 704
+    rng = np.random.default_rng(44)
+    O = ora.load_oracle()
+    x = rng.standard_normal((2, h)).astype(np.float32)
+    res = rng.standard_normal((2, h)).astype(np.float32)
+    wo = synth.random_tl1_packed(rng, h, h)
+    r = kernels.tl1_gemv(dev(x), dev(wo), h // 64, h, [0.02], epilogue=kernels.EPI_RESIDUAL, resid=dev(res))
+    wg, wu = synth.random_tl1_packed(rng, f, h), synth.random_tl1_packed(rng, f, h)
+    g = kernels.tl1_gemv(dev(x), dev(np.concatenate([wg, wu])), 2 * f // 64, h, [0.02, 0.03], [f // 64, 2 * f // 64, 2 * f // 64],
+                         epilogue=kernels.EPI_RELU2_GLU)
+    torch.cuda.synchronize()
+    for b in range(2):
+        o = cpu_bitlinear(x[b], wo, h, h, 0.02)[0]
+        assert np.array_equal(host(r["out"])[b], res[b] + o)                     # TenzoEngine.cpp:1590
+        gate, up = cpu_bitlinear(x[b], wg, f, h, 0.02)[0], cpu_bitlinear(x[b], wu, f, h, 0.03)[0]
+        act = np.zeros(f, np.float32)
+        O.ora_relu2_glu(P(gate, ora.c_f32p), P(up, ora.c_f32p), P(act, ora.c_f32p), f)
+        assert np.array_equal(host(g["out"])[b], act)                            # :1616-1620
+
+
+def test_properties_at_full_size(cuda_lib):
+    """Size-independent checks on the 6912 x 2560 shape: sign symmetry, column-sum identity, and the
+    split-K scratch is left zero (so back-to-back launches cannot leak into each other)."""
+    from tenzo_b200 import kernels
+    N, K = 6912, 2560
+    rng = np.random.default_rng(45)
+    w = synth.random_tl1_packed(rng, N, K)
+    x = rng.standard_normal((1, K)).astype(np.float32)
+    sc = kernels.SplitKScratch(1, N // 64)
+    dw = dev(w)
+    a = kernels.tl1_gemv(dev(x), dw, N // 64, K, [1.0], want_acc=True, want_act=True, scratch=sc)
+    b = kernels.tl1_gemv(dev(-x), dw, N // 64, K, [1.0], want_acc=True, scratch=sc)
+    c = kernels.tl1_gemv(dev(x), dw, N // 64, K, [1.0], want_acc=True, scratch=sc)
+    torch.cuda.synchronize()
+    assert np.array_equal(host(a["acc"]), -host(b["acc"]))          # round-half-away is odd-symmetric
+    assert np.array_equal(host(a["acc"]), host(c["acc"]))
+    assert not host(sc.acc).any() and not host(sc.cnt).any()
+    colsum = synth.unpack_tl1(w, N, K).astype(np.int64).sum(axis=0)
+    assert int(host(a["acc"]).astype(np.int64).sum()) == int(colsum @ host(a["a"])[0].astype(np.int64))
+
+
+def test_argument_errors(cuda_lib):
+    from tenzo_b200 import kernels
+    x, w = torch.zeros(1, 64, device="cuda"), torch.zeros(64 * 64 // 4, dtype=torch.uint8, device="cuda")
+    with pytest.raises(RuntimeError):
+        kernels.tl1_gemv(x, w, 1, 63, [1.0])           # odd K
+    with pytest.raises(RuntimeError):
+        kernels.tl1_gemv(x, w[1:], 1, 64, [1.0])       # misaligned weights
+    with pytest.raises(RuntimeError):
+        kernels.tl1_gemv(x, w, 1, 64, [1.0], epilogue=kernels.EPI_RESIDUAL)   # residual missing
