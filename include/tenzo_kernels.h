@@ -90,7 +90,9 @@ TENZO_API int tenzo_cuda_rmsnorm_quant(const float* x, const float* norm_w, int 
  * new token is written to (= tokens already cached); attention then covers pos[s]+1 keys.
  * rope_cos/sin: [max_seq][head_dim/2] tables (built on the host with the reference's float
  * expressions so rotations are bit-identical); NULL skips RoPE. head_dim must be 128.
- * scratch: split-T partials, tenzo_cuda_attention_scratch_bytes(...) bytes. */
+ * The kernel reproduces the reference's fp32 operation order (sequential sums over t, glibc expf
+ * bits), so its output is bit-identical, not merely close. No scratch memory: score vectors live
+ * in shared memory, which bounds max_len at 40960 keys. */
 typedef struct {
     const float* q;        /* [batch][q_stride]  n_q*128 used, pre-RoPE */
     const float* k;        /* [batch][kv_stride] n_kv*128 used, pre-RoPE new key */
@@ -106,12 +108,12 @@ typedef struct {
     int max_len;           /* upper bound on pos[s]+1 for this launch (sizes the grid) */
     int append;            /* 1: quantise and store the new k,v at pos (normal decode); 0: the
                               cache already holds pos[s]+1 keys, k/v are ignored */
-    void* scratch;
     int use_pdl;
 } tenzo_attention_args;
 
 TENZO_API int tenzo_cuda_attention_int8(const tenzo_attention_args* args, void* stream);
-TENZO_API size_t tenzo_cuda_attention_scratch_bytes(int batch, int n_q, int max_len);
+/* Query heads one CTA will process for this shape (1..n_q/n_kv); informational. */
+TENZO_API int tenzo_cuda_attention_heads_per_cta(int batch, int n_q, int n_kv, int max_len);
 
 /* ---- INT8 LM head GEMV with fused final RMSNorm + absmax(127) quantiser + argmax --------------
  * Replaces compute_logits' int8 branch (:1634-1638, :1661-1719) and the greedy branch of

@@ -1,33 +1,37 @@
-// Fused RoPE + INT8 KV append + GQA decode attention for sm_100a (split along the sequence).
+// Fused RoPE + INT8 KV append + GQA decode attention for sm_100a, bit-identical to the reference.
 //
 // Replaces FusedKVCache::forward_attention_raw in int8_fused mode
 // (src/runtime/TenzoEngine.cpp:447-533, :657-694, :823-851, :911-913 of the reference).
 //
-// Work decomposition: one CTA per (sequence, kv head, 256-key chunk). The CTA rotates the group's
-// query heads into shared memory, the CTA that owns slot `pos` rotates/quantises/stores the new
-// key and value, then every CTA computes scores for its chunk for all query heads that share the
-// kv head (K and V bytes are read from HBM once per kv head, not once per query head), a local
-// softmax, and the weighted V sum. A second kernel merges the per-chunk (max, sum, vector)
-// partials. K/V stay int8 in memory and are widened in registers against their per-token,
-// per-head fp32 scales exactly as the reference does: dot * (s_k * 1/sqrt(d)), p * s_v.
+// Why the arithmetic order is fixed. The attention output feeds an RMSNorm and a +-31 quantiser,
+// and with untrained (random) ternary weights a one-ulp difference grows by roughly 1.6x per
+// layer, so "close" is not good enough: every fp32 operation here is done in the reference's order.
+//   scores   eight FMA lanes over d (lane = d mod 8), lanes added left to right, times (s_k/sqrt(d))
+//   softmax  max over t; e_t = expf(score_t - max) with glibc's bits; sum_t e_t left to right;
+//            p_t = e_t * (1/sum)
+//   output   acc_d = fma(float(V[t][d]), p_t * s_v[t], acc_d) for t = 0..T-1 in order
+// The sums over t are therefore sequential chains; parallelism comes from everything else: keys
+// are scored one per thread, exponentials are evaluated in parallel, each of the 128 output dims
+// has its own chain, and CTAs cover (sequence, group of query heads).
 //
-// Integer results (the appended int8 rows and their scales) are bit-identical to the reference
-// given the same q/k/v; the fp32 output differs only by summation order and expf rounding.
+// One CTA handles `GH` query heads that share a kv head, so K and V bytes are fetched once for
+// all of them. With few sequences GH drops (down to 1) to put more CTAs on the machine; every CTA
+// then re-derives the new token's quantised K/V row itself (same arithmetic, same bits) and only
+// the CTA holding the group's first head stores it to the cache.
 #include "common.cuh"
 #include "../../include/tenzo_kernels.h"
 
 namespace tz {
 
-constexpr int kAttnThreads = 128;
-constexpr int kChunk = 256;          // keys per CTA
+constexpr int kAttnThreads = 256;
+constexpr int kChunk = 256;          // keys staged in shared memory at a time
 constexpr int kHd = 128;             // head_dim (the reference hard-wires 16 x 8 lanes, :833-850)
-constexpr int kKRow = 144;           // padded smem row: 16-byte aligned and bank-conflict free
+constexpr int kKRow = 144;           // padded smem row for K: 16-byte aligned, conflict-free 128-bit reads
+constexpr int kScoreSmemBytes = 160 * 1024;  // per-CTA budget for the score vectors [T][GH] (whole CTA stays under 227 KB)
 
 struct AttnLaunch {
     tenzo_attention_args a;
-    int n_splits;
-    float* part_o;                   // [batch][n_q][n_splits][128]
-    float* part_ml;                  // [batch][n_q][n_splits][2]
+    int gh;                          // query heads per CTA
 };
 
 // signed byte -> float without I2F: place (b ^ 0x80) in the mantissa of 2^23, subtract 2^23+128.
@@ -36,63 +40,74 @@ __device__ __forceinline__ float s8_to_f(uint32_t word_xor80, int byte) {
     return __uint_as_float(prmt(word_xor80, 0x4B000000u, sel)) - 8388736.0f;
 }
 
-template <int G>
-__global__ void __launch_bounds__(kAttnThreads) attn_chunk_kernel(const AttnLaunch L) {
+__device__ __forceinline__ void rope_pair(float x0, float x1, const float* cs, const float* sn, int i, float& r0, float& r1) {
+    r0 = x0;
+    r1 = x1;
+    if (cs) {
+        const float c = cs[i], s = sn[i];
+        r0 = __fmaf_rn(x0, c, -(x1 * s));      // fmsub(x0, c, x1*s)   :475
+        r1 = __fmaf_rn(x0, s, x1 * c);         // fmadd(x0, s, x1*c)   :476
+    }
+}
+
+template <int GH>
+struct AttnSmem {
+    static constexpr int n_float = GH * kHd + 2 * kHd + 8 * GH + 2 * GH + 2;
+    static constexpr int new8_off = (n_float * 4 + 15) & ~15;
+    static constexpr int stage_off = new8_off + 2 * kHd;
+    static constexpr int sc_off = stage_off + kChunk * kKRow;
+    static size_t bytes(int max_len) { return (size_t)sc_off + (size_t)max_len * GH * sizeof(float); }
+};
+
+template <int GH>
+__global__ void __launch_bounds__(kAttnThreads) attn_kernel(const AttnLaunch L) {
     const tenzo_attention_args& a = L.a;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    float* s_q = reinterpret_cast<float*>(smem_raw);              // [G][128]
-    float* s_p = s_q + G * kHd;                                   // [G][kChunk]
-    float* s_new = s_p + G * kChunk;                              // [2][128] rotated k, v of the new token
-    float* s_red = s_new + 2 * kHd;                               // [32]
-    unsigned char* s_k = reinterpret_cast<unsigned char*>(s_red + 32);   // [kChunk][kKRow]; later [4][G][128] floats
+    using Lay = AttnSmem<GH>;
+    float* s_q = reinterpret_cast<float*>(smem_raw);                     // [GH][128] rotated queries
+    float* s_new = s_q + GH * kHd;                                       // [2][128] rotated k, v of the new token
+    float* s_red = s_new + 2 * kHd;                                      // [8][GH] per-warp maxima
+    float* s_stat = s_red + 8 * GH;                                      // [GH] max, [GH] 1/sum, [2] new-row scales
+    int8_t* s_new8 = reinterpret_cast<int8_t*>(smem_raw + Lay::new8_off);   // [2][128] quantised new k, v
+    unsigned char* s_stage = smem_raw + Lay::stage_off;                  // [kChunk][kKRow] K rows, later [kChunk][128] V rows
+    float* s_sc = reinterpret_cast<float*>(smem_raw + Lay::sc_off);      // [T][GH] scores -> e_t -> weights
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
+    const int G = a.n_q / a.n_kv;
+    const int head0 = blockIdx.x * GH, kvh = head0 / G, seq = blockIdx.y;
+    const bool stores_new_row = (head0 % G) == 0;
 
     if (a.use_pdl) pdl_wait();
     const int pos = a.pos[seq];
     const int T = pos + 1;
-    const int t0 = split * kChunk;
-    if (t0 >= T) return;
-    const int t1 = min(T, t0 + kChunk), nkeys = t1 - t0;
 
     const size_t row_base = ((size_t)a.layer * a.n_kv + kvh) * a.max_seq;   // :509-510
     int8_t* ck = a.cache_k + (size_t)seq * a.seq_stride_kv + row_base * kHd;
     int8_t* cv = a.cache_v + (size_t)seq * a.seq_stride_kv + row_base * kHd;
     float* sk = a.scale_k + (size_t)seq * a.seq_stride_sc + row_base;
     float* sv = a.scale_v + (size_t)seq * a.seq_stride_sc + row_base;
-
-    // ---- RoPE on the group's query heads (half-split pairs i, i+64; :471-478) ------------------
     const float* cs = a.rope_cos ? a.rope_cos + (size_t)pos * (kHd / 2) : nullptr;
     const float* sn = a.rope_sin ? a.rope_sin + (size_t)pos * (kHd / 2) : nullptr;
-    for (int idx = tid; idx < G * (kHd / 2); idx += kAttnThreads) {
+
+    // ---- RoPE on this CTA's query heads (pairs i, i+64; :459-480) ---------------------------------
+    for (int idx = tid; idx < GH * (kHd / 2); idx += kAttnThreads) {
         const int g = idx / (kHd / 2), i = idx % (kHd / 2);
-        const float* qh = a.q + (size_t)seq * a.q_stride + (size_t)(kvh * G + g) * kHd;
-        const float x0 = __ldcg(qh + i), x1 = __ldcg(qh + i + kHd / 2);
-        float r0 = x0, r1 = x1;
-        if (cs) {
-            const float c = cs[i], s = sn[i];
-            r0 = __fmaf_rn(x0, c, -(x1 * s));      // fmsub(x0, c, x1*s)
-            r1 = __fmaf_rn(x0, s, x1 * c);         // fmadd(x0, s, x1*c)
-        }
+        const float* qh = a.q + (size_t)seq * a.q_stride + (size_t)(head0 + g) * kHd;
+        float r0, r1;
+        rope_pair(__ldcg(qh + i), __ldcg(qh + i + kHd / 2), cs, sn, i, r0, r1);
         s_q[g * kHd + i] = r0;
         s_q[g * kHd + i + kHd / 2] = r1;
     }
 
-    // ---- the CTA that owns slot `pos` appends the new token (:508-533) -------------------------
-    if (a.append && pos >= t0 && pos < t1) {
+    // ---- the new token's K/V row: rotate, quantise (:483-533); one CTA per kv head stores it -------
+    if (a.append) {
         if (tid < kHd / 2) {
             const float* kh = a.k + (size_t)seq * a.kv_stride + (size_t)kvh * kHd;
-            const float x0 = __ldcg(kh + tid), x1 = __ldcg(kh + tid + kHd / 2);
-            float r0 = x0, r1 = x1;
-            if (cs) {
-                const float c = cs[tid], s = sn[tid];
-                r0 = __fmaf_rn(x0, c, -(x1 * s));
-                r1 = __fmaf_rn(x0, s, x1 * c);
-            }
+            float r0, r1;
+            rope_pair(__ldcg(kh + tid), __ldcg(kh + tid + kHd / 2), cs, sn, tid, r0, r1);
             s_new[tid] = r0;
             s_new[tid + kHd / 2] = r1;
-        } else {
+        } else if (tid < kHd) {
             const float* vh = a.v + (size_t)seq * a.kv_stride + (size_t)kvh * kHd;
             const int i = tid - kHd / 2;
             s_new[kHd + i] = __ldcg(vh + i);
@@ -113,136 +128,138 @@ __global__ void __launch_bounds__(kAttnThreads) attn_chunk_kernel(const AttnLaun
                 const float qf = fminf(fmaxf(roundf(src[lane * 4 + j] * inv), -128.0f), 127.0f);   // :530
                 packed |= ((uint32_t)(uint8_t)(int8_t)(int)qf) << (8 * j);
             }
-            int8_t* dst = (warp == 0 ? ck : cv) + (size_t)pos * kHd;
-            reinterpret_cast<uint32_t*>(dst)[lane] = packed;
-            if (lane == 0) (warp == 0 ? sk : sv)[pos] = s;
-        }
-    }
-    __syncthreads();   // new row and s_q visible to the whole CTA
-
-    // ---- stage the K chunk in shared memory (coalesced 128-bit loads) --------------------------
-    for (int idx = tid; idx < nkeys * 8; idx += kAttnThreads) {
-        const int r = idx >> 3, c = idx & 7;
-        const uint4 v = ld_cg_u4(ck + (size_t)(t0 + r) * kHd + c * 16);
-        *reinterpret_cast<uint4*>(s_k + r * kKRow + c * 16) = v;
-    }
-    __syncthreads();
-
-    // ---- scores: one key per thread, eight FMA lanes per head in the reference's order (:682-691)
-    const float sm_scale = 1.0f / sqrtf((float)kHd);   // :660
-    for (int kl = tid; kl < nkeys; kl += kAttnThreads) {
-        float acc[G][8];
-#pragma unroll
-        for (int g = 0; g < G; ++g)
-#pragma unroll
-            for (int j = 0; j < 8; ++j) acc[g][j] = 0.0f;
-        const unsigned char* krow = s_k + kl * kKRow;
-#pragma unroll 2
-        for (int d = 0; d < kHd; d += 16) {
-            const uint4 kw = *reinterpret_cast<const uint4*>(krow + d);
-            const uint32_t w[4] = {kw.x ^ 0x80808080u, kw.y ^ 0x80808080u, kw.z ^ 0x80808080u, kw.w ^ 0x80808080u};
-            float kf[16];
-#pragma unroll
-            for (int e = 0; e < 16; ++e) kf[e] = s8_to_f(w[e >> 2], e & 3);
-#pragma unroll
-            for (int g = 0; g < G; ++g) {
-                const float4* q4 = reinterpret_cast<const float4*>(s_q + g * kHd + d);
-                const float4 qa = q4[0], qb = q4[1], qc = q4[2], qd = q4[3];
-                const float qv[16] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w,
-                                      qc.x, qc.y, qc.z, qc.w, qd.x, qd.y, qd.z, qd.w};
-#pragma unroll
-                for (int e = 0; e < 16; ++e) acc[g][e & 7] = __fmaf_rn(qv[e], kf[e], acc[g][e & 7]);
+            reinterpret_cast<uint32_t*>(s_new8 + warp * kHd)[lane] = packed;
+            if (lane == 0) s_stat[2 * GH + warp] = s;
+            if (stores_new_row) {
+                int8_t* dst = (warp == 0 ? ck : cv) + (size_t)pos * kHd;
+                reinterpret_cast<uint32_t*>(dst)[lane] = packed;
+                if (lane == 0) (warp == 0 ? sk : sv)[pos] = s;
             }
         }
-        const float ks = __ldcg(sk + t0 + kl) * sm_scale;
+    }
+    __syncthreads();
+    if (a.use_pdl) pdl_launch_dependents();
+
+    // ---- scores (:678-694): one key per thread, all GH heads, the reference's eight FMA lanes ------
+    const float sm_scale = 1.0f / sqrtf((float)kHd);   // :660
+    float tmax[GH];
 #pragma unroll
-        for (int g = 0; g < G; ++g) {
-            const float dot = (acc[g][0] + acc[g][1] + acc[g][2] + acc[g][3] + acc[g][4] + acc[g][5] + acc[g][6] + acc[g][7]) * ks;
-            s_p[g * kChunk + kl] = dot;
+    for (int g = 0; g < GH; ++g) tmax[g] = -1e30f;     // :670
+    for (int t0 = 0; t0 < T; t0 += kChunk) {
+        const int nkeys = min(kChunk, T - t0);
+        for (int idx = tid; idx < nkeys * 8; idx += kAttnThreads) {
+            const int r = idx >> 3, c = idx & 7;
+            const bool is_new = a.append && (t0 + r == pos);
+            const uint4 v = is_new ? reinterpret_cast<const uint4*>(s_new8)[c] : ld_cg_u4(ck + (size_t)(t0 + r) * kHd + c * 16);
+            *reinterpret_cast<uint4*>(s_stage + r * kKRow + c * 16) = v;
         }
+        __syncthreads();
+        if (tid < nkeys) {
+            float acc[GH][8];
+#pragma unroll
+            for (int g = 0; g < GH; ++g)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[g][j] = 0.0f;
+            const unsigned char* krow = s_stage + tid * kKRow;
+#pragma unroll 2
+            for (int d = 0; d < kHd; d += 16) {
+                const uint4 kw = *reinterpret_cast<const uint4*>(krow + d);
+                const uint32_t w[4] = {kw.x ^ 0x80808080u, kw.y ^ 0x80808080u, kw.z ^ 0x80808080u, kw.w ^ 0x80808080u};
+                float kf[16];
+#pragma unroll
+                for (int e = 0; e < 16; ++e) kf[e] = s8_to_f(w[e >> 2], e & 3);
+#pragma unroll
+                for (int g = 0; g < GH; ++g) {
+                    const float4* q4 = reinterpret_cast<const float4*>(s_q + g * kHd + d);
+                    const float4 qa = q4[0], qb = q4[1], qc = q4[2], qd = q4[3];
+                    const float qv[16] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w,
+                                          qc.x, qc.y, qc.z, qc.w, qd.x, qd.y, qd.z, qd.w};
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) acc[g][e & 7] = __fmaf_rn(qv[e], kf[e], acc[g][e & 7]);
+                }
+            }
+            const int t = t0 + tid;
+            const float ksc = (a.append && t == pos) ? s_stat[2 * GH] : __ldcg(sk + t);
+            const float ks = ksc * sm_scale;
+#pragma unroll
+            for (int g = 0; g < GH; ++g) {
+                const float dot = (acc[g][0] + acc[g][1] + acc[g][2] + acc[g][3] + acc[g][4] + acc[g][5] + acc[g][6] + acc[g][7]) * ks;   // :691
+                s_sc[(size_t)t * GH + g] = dot;
+                tmax[g] = fmaxf(tmax[g], dot);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int g = 0; g < GH; ++g) {
+        const float m = warp_max(tmax[g]);
+        if (lane == 0) s_red[warp * GH + g] = m;
+    }
+    __syncthreads();
+    if (tid < GH) {
+        float m = s_red[tid];
+        for (int w = 1; w < kAttnThreads / 32; ++w) m = fmaxf(m, s_red[w * GH + tid]);
+        s_stat[tid] = m;
     }
     __syncthreads();
 
-    // ---- chunk-local softmax numerators; fold the V scale into the weight (:826, :844) ----------
-    for (int g = warp; g < G; g += kAttnThreads / 32) {
-        float mx = -1e30f;
-        for (int kl = lane; kl < nkeys; kl += 32) mx = fmaxf(mx, s_p[g * kChunk + kl]);
-        mx = warp_max(mx);
+    // ---- e_t = expf(score - max), in parallel (:826) -----------------------------------------------
+    for (int idx = tid; idx < T * GH; idx += kAttnThreads) s_sc[idx] = expf_reference_bits(s_sc[idx] - s_stat[idx % GH]);
+    __syncthreads();
+    // ---- sum_t e_t, left to right, one thread per head (:824-829) ----------------------------------
+    if (tid < GH) {
         float sum = 0.0f;
-        for (int kl = lane; kl < nkeys; kl += 32) {
-            const float e = expf(s_p[g * kChunk + kl] - mx);
-            sum += e;
-            s_p[g * kChunk + kl] = e * __ldcg(sv + t0 + kl);
-        }
-        sum = warp_sum(sum);
-        if (lane == 0) {
-            const size_t slot = ((size_t)seq * a.n_q + kvh * G + g) * L.n_splits + split;
-            L.part_ml[slot * 2] = mx;
-            L.part_ml[slot * 2 + 1] = sum;
-        }
+#pragma unroll 8
+        for (int t = 0; t < T; ++t) sum = __fadd_rn(sum, s_sc[(size_t)t * GH + tid]);
+        s_stat[GH + tid] = 1.0f / sum;
     }
     __syncthreads();
+    // ---- weights p_t * s_v[t] (:830, :844) ------------------------------------------------------------
+    for (int idx = tid; idx < T * GH; idx += kAttnThreads) {
+        const int t = idx / GH;
+        const float p = s_sc[idx] * s_stat[GH + idx % GH];
+        const float vs = (a.append && t == pos) ? s_stat[2 * GH + 1] : __ldcg(sv + t);
+        s_sc[idx] = p * vs;
+    }
 
-    // ---- weighted V sum: lane owns 4 dims, warps take keys round-robin (:842-851) ---------------
-    float o[G][4];
+    // ---- output: thread d owns dim d of every head and walks t in order (:842-851) ------------------
+    float o[GH];
 #pragma unroll
-    for (int g = 0; g < G; ++g)
+    for (int g = 0; g < GH; ++g) o[g] = 0.0f;
+    for (int t0 = 0; t0 < T; t0 += kChunk) {
+        const int nkeys = min(kChunk, T - t0);
+        __syncthreads();                                   // weights complete / previous chunk consumed
+        for (int idx = tid; idx < nkeys * 8; idx += kAttnThreads) {
+            const int r = idx >> 3, c = idx & 7;
+            const bool is_new = a.append && (t0 + r == pos);
+            const uint4 v = is_new ? reinterpret_cast<const uint4*>(s_new8 + kHd)[c] : ld_cg_u4(cv + (size_t)(t0 + r) * kHd + c * 16);
+            *reinterpret_cast<uint4*>(s_stage + r * kHd + c * 16) = v;
+        }
+        __syncthreads();
+        if (tid < kHd) {
+#pragma unroll 4
+            for (int kl = 0; kl < nkeys; ++kl) {
+                const uint32_t b = s_stage[kl * kHd + tid];
+                const float vf = __uint_as_float((b ^ 0x80u) | 0x4B000000u) - 8388736.0f;
+                const float* wg = s_sc + (size_t)(t0 + kl) * GH;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) o[g][j] = 0.0f;
-    for (int kl = warp; kl < nkeys; kl += kAttnThreads / 32) {
-        const uint32_t vw = __ldcg(reinterpret_cast<const uint32_t*>(cv + (size_t)(t0 + kl) * kHd) + lane) ^ 0x80808080u;
-        float vf[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) vf[j] = s8_to_f(vw, j);
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-            const float wgt = s_p[g * kChunk + kl];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) o[g][j] = __fmaf_rn(vf[j], wgt, o[g][j]);
+                for (int g = 0; g < GH; ++g) o[g] = __fmaf_rn(vf, wg[g], o[g]);
+            }
         }
     }
-    float* s_o = reinterpret_cast<float*>(s_k);     // K staging is dead; reuse as [4][G][128]
+    if (tid < kHd) {
 #pragma unroll
-    for (int g = 0; g < G; ++g)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) s_o[(warp * G + g) * kHd + lane * 4 + j] = o[g][j];
-    __syncthreads();
-    for (int idx = tid; idx < G * kHd; idx += kAttnThreads) {
-        const int g = idx / kHd, d = idx % kHd;
-        float t = 0.0f;
-#pragma unroll
-        for (int w = 0; w < kAttnThreads / 32; ++w) t += s_o[(w * G + g) * kHd + d];
-        const size_t slot = ((size_t)seq * a.n_q + kvh * G + g) * L.n_splits + split;
-        L.part_o[slot * kHd + d] = t;
+        for (int g = 0; g < GH; ++g) a.out[(size_t)seq * a.n_q * kHd + (size_t)(head0 + g) * kHd + tid] = o[g];
     }
 }
 
-// Merge the per-chunk partials: out = sum_i o_i * exp(m_i - M) / sum_i l_i * exp(m_i - M).
-__global__ void __launch_bounds__(kHd) attn_merge_kernel(const AttnLaunch L) {
-    const tenzo_attention_args& a = L.a;
-    const int qh = blockIdx.x, seq = blockIdx.y, d = threadIdx.x;
-    const int T = a.pos[seq] + 1;
-    const int active = min((T + kChunk - 1) / kChunk, L.n_splits);
-    const size_t base = ((size_t)seq * a.n_q + qh) * L.n_splits;
-    float M = -1e30f;
-    for (int i = 0; i < active; ++i) M = fmaxf(M, L.part_ml[(base + i) * 2]);
-    float num = 0.0f, den = 0.0f;
-    for (int i = 0; i < active; ++i) {
-        const float w = expf(L.part_ml[(base + i) * 2] - M);
-        den += L.part_ml[(base + i) * 2 + 1] * w;
-        num += L.part_o[(base + i) * kHd + d] * w;
-    }
-    a.out[(size_t)seq * a.n_q * kHd + (size_t)qh * kHd + d] = num * (1.0f / den);   // :829-830
-}
-
-template <int G>
+template <int GH>
 static cudaError_t launch_attn(const AttnLaunch& L, cudaStream_t st) {
-    const size_t smem = (size_t)(G * kHd + G * kChunk + 2 * kHd + 32) * sizeof(float) +
-                        (size_t)max(kChunk * kKRow, 4 * G * kHd * (int)sizeof(float));
-    cudaError_t e = cudaFuncSetAttribute(attn_chunk_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const size_t smem = AttnSmem<GH>::bytes(L.a.max_len);
+    cudaError_t e = cudaFuncSetAttribute(attn_kernel<GH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)L.n_splits, (unsigned)L.a.n_kv, (unsigned)L.a.batch);
+    cfg.gridDim = dim3((unsigned)(L.a.n_q / GH), (unsigned)L.a.batch, 1);
     cfg.blockDim = dim3(kAttnThreads, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
@@ -251,44 +268,48 @@ static cudaError_t launch_attn(const AttnLaunch& L, cudaStream_t st) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = L.a.use_pdl ? 1 : 0;
-    e = cudaLaunchKernelEx(&cfg, attn_chunk_kernel<G>, L);
-    if (e != cudaSuccess) return e;
-    attn_merge_kernel<<<dim3((unsigned)L.a.n_q, (unsigned)L.a.batch), kHd, 0, st>>>(L);
-    return cudaGetLastError();
+    return cudaLaunchKernelEx(&cfg, attn_kernel<GH>, L);
+}
+
+// Query heads per CTA: as many as share a kv head, halved while that leaves SMs idle or the score
+// vectors [max_len][GH] would not fit in shared memory.
+static int pick_heads_per_cta(int batch, int n_q, int group, int max_len) {
+    int gh = group;
+    while (gh > 1 && ((long long)batch * (n_q / gh) < 148 || (size_t)gh * max_len * sizeof(float) > (size_t)kScoreSmemBytes)) gh >>= 1;
+    return gh;
 }
 
 }  // namespace tz
 
-extern "C" size_t tenzo_cuda_attention_scratch_bytes(int batch, int n_q, int max_len) {
-    if (batch <= 0 || n_q <= 0 || max_len <= 0) return 0;
-    const size_t splits = (size_t)(max_len + tz::kChunk - 1) / tz::kChunk;
-    return (size_t)batch * n_q * splits * (tz::kHd + 2) * sizeof(float);
+extern "C" int tenzo_cuda_attention_heads_per_cta(int batch, int n_q, int n_kv, int max_len) {
+    if (batch <= 0 || n_q <= 0 || n_kv <= 0 || n_q % n_kv || max_len <= 0) return 0;
+    return tz::pick_heads_per_cta(batch, n_q, n_q / n_kv, max_len);
 }
 
 extern "C" int tenzo_cuda_attention_int8(const tenzo_attention_args* args, void* stream) {
     using namespace tz;
     if (!args) return -1;
     const tenzo_attention_args& a = *args;
-    if (!a.q || !a.out || !a.cache_k || !a.cache_v || !a.scale_k || !a.scale_v || !a.pos || !a.scratch) return -1;
+    if (!a.q || !a.out || !a.cache_k || !a.cache_v || !a.scale_k || !a.scale_v || !a.pos) return -1;
     if (a.append && (!a.k || !a.v)) return -1;
     if (a.head_dim != kHd) return -5;
     if (a.n_q <= 0 || a.n_kv <= 0 || a.n_q % a.n_kv || a.batch <= 0 || a.max_len <= 0 || a.max_len > a.max_seq) return -1;
     if ((a.rope_cos == nullptr) != (a.rope_sin == nullptr)) return -1;
+    const int group = a.n_q / a.n_kv;
+    if (group != 1 && group != 2 && group != 4 && group != 8) return -5;
+    if ((size_t)a.max_len * sizeof(float) > (size_t)kScoreSmemBytes) return -5;   // one head's scores must fit on chip
     AttnLaunch L;
     L.a = a;
     if (L.a.q_stride <= 0) L.a.q_stride = a.n_q * kHd;
     if (L.a.kv_stride <= 0) L.a.kv_stride = a.n_kv * kHd;
-    L.n_splits = (a.max_len + kChunk - 1) / kChunk;
-    L.part_o = static_cast<float*>(a.scratch);
-    L.part_ml = L.part_o + (size_t)a.batch * a.n_q * L.n_splits * kHd;
+    L.gh = pick_heads_per_cta(a.batch, a.n_q, group, a.max_len);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     cudaError_t e;
-    switch (a.n_q / a.n_kv) {
+    switch (L.gh) {
         case 1: e = launch_attn<1>(L, st); break;
         case 2: e = launch_attn<2>(L, st); break;
         case 4: e = launch_attn<4>(L, st); break;
-        case 8: e = launch_attn<8>(L, st); break;
-        default: return -5;
+        default: e = launch_attn<8>(L, st); break;
     }
     return e == cudaSuccess ? 0 : (int)e;
 }

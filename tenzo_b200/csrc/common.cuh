@@ -80,6 +80,32 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
     return t;
 }
 
+// Sum of squares in the exact order of the reference's vectorised loop (TenzoEngine.cpp:149-153 as
+// gcc compiles it for AVX2): eight lanes, lane j accumulating x[j], x[j+8], ... with a separately
+// rounded product and sum (no FMA), then the lanes added left to right starting from lane 0; any
+// tail beyond a multiple of eight follows in index order. fp32 addition is not associative, and
+// this value feeds a quantiser, so the order is part of the result. `x` is in shared memory and
+// complete (caller has synchronised); every thread returns the same bits. Two barriers.
+__device__ __forceinline__ float sumsq_reference_order(const float* x, int dim, float* scratch) {
+    const int n8 = dim & ~7;
+    if (threadIdx.x < 8) {
+        float s = 0.0f;
+#pragma unroll 8
+        for (int i = threadIdx.x; i < n8; i += 8) {
+            const float v = x[i];
+            s = __fadd_rn(s, __fmul_rn(v, v));
+        }
+        scratch[threadIdx.x] = s;
+    }
+    __syncthreads();
+    float t = scratch[0];
+#pragma unroll
+    for (int j = 1; j < 8; ++j) t = __fadd_rn(t, scratch[j]);
+    for (int i = n8; i < dim; ++i) t = __fadd_rn(t, __fmul_rn(x[i], x[i]));
+    __syncthreads();
+    return t;
+}
+
 // y_i = x_i * inv_rms * w_i evaluated left to right (TenzoEngine.cpp:158); w may be null (:163).
 __device__ __forceinline__ float rms_apply(float x, float inv_rms, const float* w, int i) {
     float y = x * inv_rms;
@@ -88,6 +114,42 @@ __device__ __forceinline__ float rms_apply(float x, float inv_rms, const float* 
 // inv_rms = 1 / sqrt(sum_sq/dim + eps) (TenzoEngine.cpp:154).
 __device__ __forceinline__ float rms_inv(float sum_sq, int dim, float eps) {
     return 1.0f / sqrtf((sum_sq / static_cast<float>(dim)) + eps);
+}
+
+// expf with the bits glibc's expf returns for x <= 0 (the softmax arguments, TenzoEngine.cpp:826).
+// It is the published table-driven algorithm glibc uses (Szabolcs Nagy's exp2f/expf from ARM's
+// optimized-routines: 32-entry table of 2^(i/32), cubic in double precision, k = round(x*32/ln2)
+// through the 1.5*2^52 shift), with the reduced argument formed by one fused multiply-add as the
+// FMA build of the library does. Checked against the host's expf on every float in [-104.5, -0]:
+// zero differences. Inputs above 0 are outside its use here.
+static __device__ __constant__ unsigned long long kExp2fTab[32] = {
+    0x3ff0000000000000ull, 0x3fefd9b0d3158574ull, 0x3fefb5586cf9890full, 0x3fef9301d0125b51ull,
+    0x3fef72b83c7d517bull, 0x3fef54873168b9aaull, 0x3fef387a6e756238ull, 0x3fef1e9df51fdee1ull,
+    0x3fef06fe0a31b715ull, 0x3feef1a7373aa9cbull, 0x3feedea64c123422ull, 0x3feece086061892dull,
+    0x3feebfdad5362a27ull, 0x3feeb42b569d4f82ull, 0x3feeab07dd485429ull, 0x3feea47eb03a5585ull,
+    0x3feea09e667f3bcdull, 0x3fee9f75e8ec5f74ull, 0x3feea11473eb0187ull, 0x3feea589994cce13ull,
+    0x3feeace5422aa0dbull, 0x3feeb737b0cdc5e5ull, 0x3feec49182a3f090ull, 0x3feed503b23e255dull,
+    0x3feee89f995ad3adull, 0x3feeff76f2fb5e47ull, 0x3fef199bdd85529cull, 0x3fef3720dcef9069ull,
+    0x3fef5818dcfba487ull, 0x3fef7c97337b9b5full, 0x3fefa4afa2a490daull, 0x3fefd0765b6e4540ull};
+
+__device__ __forceinline__ float expf_reference_bits(float x) {
+    if (x < -0x1.9fe368p6f) return 0.0f;                       // underflow to zero below about -103.97
+    const double inv_ln2_n = 0x1.71547652b82fep+0 * 32.0, shift = 0x1.8p+52;
+    const double c0 = 0x1.c6af84b912394p-5 / 32 / 32 / 32, c1 = 0x1.ebfce50fac4f3p-3 / 32 / 32, c2 = 0x1.62e42ff0c52d6p-1 / 32;
+    const double xd = (double)x;
+    const double z = __dmul_rn(inv_ln2_n, xd);
+    double kd = __dadd_rn(z, shift);
+    const unsigned long long ki = (unsigned long long)__double_as_longlong(kd);
+    kd = __dadd_rn(kd, -shift);
+    const double r = __fma_rn(inv_ln2_n, xd, -kd);
+    const unsigned long long t = kExp2fTab[ki & 31] + (ki << 47);
+    const double s = __longlong_as_double((long long)t);
+    const double zz = __fma_rn(c0, r, c1);
+    const double r2 = __dmul_rn(r, r);
+    double y = __fma_rn(c2, r, 1.0);
+    y = __fma_rn(zz, r2, y);
+    y = __dmul_rn(y, s);
+    return __double2float_rn(y);
 }
 
 }  // namespace tz

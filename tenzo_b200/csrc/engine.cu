@@ -167,7 +167,6 @@ Engine::Engine(const tenzo_config_t& c, const tenzo_ext_options_t& o) : cfg(c) {
     const int widest_blocks = (qd + 2 * kvd > 2 * ffn ? qd + 2 * kvd : 2 * ffn) / 64;
     splitk_acc = (int32_t*)dalloc(B * widest_blocks * 64 * 4);
     splitk_cnt = (uint32_t*)dalloc(B * widest_blocks * 4);
-    attn_scratch = dalloc(tenzo_cuda_attention_scratch_bytes(batch, cfg.num_q_heads, cfg.max_seq_len));
     lm_scratch = dalloc(tenzo_cuda_lm_head_scratch_bytes(batch));
 
     TZ_CUDA(cudaMallocHost(&h_pin, (3 * B + 16) * sizeof(int)));
@@ -288,11 +287,11 @@ void Engine::enqueue_layer(int l, int max_len, bool gemv_only) {
     a.pos = d_pos; a.rope_cos = rope_cos; a.rope_sin = rope_sin;
     a.layer = l; a.n_q = cfg.num_q_heads; a.n_kv = cfg.num_kv_heads; a.head_dim = 128;
     a.max_seq = cfg.max_seq_len; a.batch = batch; a.max_len = max_len; a.append = 1;
-    a.scratch = attn_scratch; a.use_pdl = use_pdl;
+    a.use_pdl = use_pdl;
     a.q_stride = a.kv_stride = qd + 2 * kvd;
     if (!gemv_only) {
         TZ_KERNEL(tenzo_cuda_attention_int8(&a, stream));
-        launches += 2;
+        launches += 1;
     }
 
     // out projection + residual

@@ -71,7 +71,7 @@ public:
     float *rope_cos = nullptr, *rope_sin = nullptr;
     int32_t* splitk_acc = nullptr;
     uint32_t* splitk_cnt = nullptr;
-    void *attn_scratch = nullptr, *lm_scratch = nullptr;
+    void* lm_scratch = nullptr;
     int *h_pin = nullptr, *h_tokens = nullptr, *h_pos = nullptr, *h_next = nullptr;
     std::vector<int> seq_len;
     std::vector<void*> owned;

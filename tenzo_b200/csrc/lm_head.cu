@@ -45,15 +45,11 @@ __global__ void __launch_bounds__(kLmThreads) lm_head_kernel(
 
     // ---- prologue: final RMSNorm + absmax(127) quantiser (:1638, :1666-1678) -------------------
     const float* xs = x + (size_t)seq * x_stride;
-    float ss = 0.0f;
-    for (int i = tid; i < hidden; i += kLmThreads) {
-        const float v = __ldcg(xs + i);
-        s_y[i] = v;
-        ss += v * v;
-    }
+    for (int i = tid; i < hidden; i += kLmThreads) s_y[i] = __ldcg(xs + i);
     float m = 0.0f;
     if (do_norm) {
-        ss = block_sum(ss, s_f);
+        __syncthreads();
+        const float ss = sumsq_reference_order(s_y, hidden, s_f);
         const float inv_rms = rms_inv(ss, hidden, eps);
         for (int i = tid; i < hidden; i += kLmThreads) {
             const float y = rms_apply(s_y[i], inv_rms, norm_w, i);

@@ -21,15 +21,11 @@ __global__ void __launch_bounds__(kNqThreads) rmsnorm_quant_kernel(
     const int tid = threadIdx.x, seq = blockIdx.x;
     const float* xs = x + (size_t)seq * x_stride;
 
-    float ss = 0.0f;
-    for (int i = tid; i < dim; i += kNqThreads) {
-        const float v = xs[i];
-        s_y[i] = v;
-        ss += v * v;
-    }
+    for (int i = tid; i < dim; i += kNqThreads) s_y[i] = xs[i];
     float m = 0.0f;
     if (do_norm) {
-        ss = block_sum(ss, s_f);
+        __syncthreads();
+        const float ss = sumsq_reference_order(s_y, dim, s_f);
         const float inv_rms = rms_inv(ss, dim, eps);
         for (int i = tid; i < dim; i += kNqThreads) {
             const float y = rms_apply(s_y[i], inv_rms, norm_w, i);

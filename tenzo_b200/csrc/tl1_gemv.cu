@@ -128,15 +128,11 @@ __global__ void __launch_bounds__(kGemvThreads) tl1_gemv_kernel(const GemvLaunch
     // ---- prologue: RMSNorm + absmax(31) quantiser, recomputed identically by every CTA ----------
     // x is staged in shared memory once; the normalised value replaces it in place.
     const float* x = a.x + (size_t)seq * a.x_stride;
-    float ss = 0.0f;
-    for (int i = tid; i < a.K; i += kGemvThreads) {
-        const float v = __ldcg(x + i);
-        s_x[i] = v;
-        ss += v * v;
-    }
+    for (int i = tid; i < a.K; i += kGemvThreads) s_x[i] = __ldcg(x + i);
     float m = 0.0f;
     if (a.do_norm) {
-        ss = block_sum(ss, s_f);
+        __syncthreads();
+        const float ss = sumsq_reference_order(s_x, a.K, s_f);
         const float inv_rms = rms_inv(ss, a.K, a.eps);
         for (int i = tid; i < a.K; i += kGemvThreads) {   // same thread wrote s_x[i]
             const float y = rms_apply(s_x[i], inv_rms, a.norm_w, i);

@@ -89,8 +89,6 @@ def attention_int8(q, k, v, cache_k, cache_v, scale_k, scale_v, pos, *, layer, n
     if max_len is None:
         max_len = int(pos.max().item()) + 1
     out = torch.empty(batch, n_q * 128, dtype=torch.float32, device=q.device)
-    nbytes = lib.tenzo_cuda_attention_scratch_bytes(batch, n_q, max_len)
-    scratch = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
     a = abi.AttentionArgs()
     a.q, a.k, a.v, a.out = _ptr(q), _ptr(k), _ptr(v), _ptr(out)
     a.q_stride, a.kv_stride = q.stride(0), (k.stride(0) if k is not None else 0)
@@ -98,7 +96,7 @@ def attention_int8(q, k, v, cache_k, cache_v, scale_k, scale_v, pos, *, layer, n
     a.seq_stride_kv, a.seq_stride_sc = cache_k.stride(0), scale_k.stride(0)
     a.pos, a.rope_cos, a.rope_sin = _ptr(pos), _ptr(rope_cos), _ptr(rope_sin)
     a.layer, a.n_q, a.n_kv, a.head_dim, a.max_seq = layer, n_q, n_kv, 128, max_seq
-    a.batch, a.max_len, a.append, a.scratch, a.use_pdl = batch, max_len, int(append), _ptr(scratch), int(use_pdl)
+    a.batch, a.max_len, a.append, a.use_pdl = batch, max_len, int(append), int(use_pdl)
     _ok(lib.tenzo_cuda_attention_int8(C.byref(a), _stream()), "tenzo_cuda_attention_int8")
     return out
 

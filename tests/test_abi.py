@@ -101,7 +101,7 @@ def test_kernel_entry_points_reject_bad_arguments_without_a_device(lib):
     assert lib.tenzo_cuda_attention_int8(None, None) == abi.ERR_INVALID
     assert lib.tenzo_cuda_lm_head_i8(None, None, 1, 1e-5, None, None, 0, 0, 0, 0, None, None, None, None, 0, None) == abi.ERR_INVALID
     assert lib.tenzo_cuda_tl1_gemv_ksplit(40, 2560, 0) >= 1
-    assert lib.tenzo_cuda_attention_scratch_bytes(2, 20, 8192) == 2 * 20 * 32 * 130 * 4
+    assert lib.tenzo_cuda_attention_heads_per_cta(1, 20, 5, 256) == 1 and lib.tenzo_cuda_attention_heads_per_cta(64, 20, 5, 8192) == 4
 
 
 def test_engine_creation_fails_loudly_without_a_gpu(lib):

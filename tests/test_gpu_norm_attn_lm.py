@@ -1,4 +1,9 @@
-"""RMSNorm+quantiser, fused attention and LM head on the GPU against the oracle / golden vectors."""
+"""RMSNorm+quantiser, fused attention and LM head on the GPU against the oracle / golden vectors.
+
+Everything here is compared with `==`, floats included: the kernels reproduce the reference's fp32
+operation order (RMS sum lanes, score lanes, sequential softmax sum and value accumulation,
+glibc's expf bits), because with untrained ternary weights a last-bit difference grows ~1.6x per
+layer and no tolerance survives 30 layers."""
 import hashlib
 
 import numpy as np
@@ -21,7 +26,10 @@ def test_rmsnorm_quant_golden(cuda_lib, golden, dim):
     # quantiser alone on the reference's own normalised vector: exact
     _, q, s = kernels.rmsnorm_quant(dev(g[f"d{dim}_y"][None]), None, do_norm=False, qmax=31)
     torch.cuda.synchronize()
-    assert rel_err(host(y)[0], g[f"d{dim}_y"]) < 1e-6
+    if dim % 8 == 0:
+        assert np.array_equal(host(y)[0], g[f"d{dim}_y"]), "normalised vector differs"
+    else:   # the reference compiler's handling of a ragged vector tail is not reproduced; engine dims are multiples of 64
+        assert rel_err(host(y)[0], g[f"d{dim}_y"]) < 1e-6
     assert np.array_equal(host(q)[0], g[f"d{dim}_a"]) and np.float32(host(s)[0]) == g[f"d{dim}_inv"]
 
 
@@ -65,7 +73,6 @@ def test_attention_token_by_token(cuda_lib, theta):
     sv = torch.zeros_like(sk)
     ock, ocv = np.zeros(L * nkv * ms * hd, np.int8), np.zeros(L * nkv * ms * hd, np.int8)
     osk, osv = np.zeros(L * nkv * ms, np.float32), np.zeros(L * nkv * ms, np.float32)
-    worst = 0.0
     for t in range(steps):
         out = kernels.attention_int8(dev(q[t][None]), dev(k[t][None]), dev(v[t][None]), ck, cv, sk, sv,
                                      torch.tensor([t], dtype=torch.int32, device="cuda"), layer=1, n_q=nq, n_kv=nkv,
@@ -73,8 +80,7 @@ def test_attention_token_by_token(cuda_lib, theta):
         qq, kk, vv, o = q[t].copy(), k[t].copy(), v[t].copy(), np.zeros(nq * hd, np.float32)
         O.ora_attention_int8(1, t, nq, nkv, hd, ms, theta, P(qq, ora.c_f32p), P(kk, ora.c_f32p), P(vv, ora.c_f32p), P(o, ora.c_f32p),
                              P(ock, ora.c_i8p), P(ocv, ora.c_i8p), P(osk, ora.c_f32p), P(osv, ora.c_f32p))
-        worst = max(worst, rel_err(host(out)[0], o))
-    assert worst < FP_TOL, f"attention output relative error {worst}"
+        assert np.array_equal(host(out)[0], o), f"attention output differs at position {t} (rel err {rel_err(host(out)[0], o):.2e})"
     assert np.array_equal(host(ck).reshape(-1), ock) and np.array_equal(host(cv).reshape(-1), ocv)
     assert np.array_equal(host(sk).reshape(-1), osk) and np.array_equal(host(sv).reshape(-1), osv)
 
@@ -99,7 +105,7 @@ def test_attention_golden_outputs(cuda_lib, golden):
     for i, t in enumerate(int(t) for t in g["keep"]):
         out = kernels.attention_int8(dev(q[t][None]), None, None, ck, cv, sk, sv, torch.tensor([t], dtype=torch.int32, device="cuda"),
                                      layer=0, n_q=nq, n_kv=nkv, max_seq=ms, rope_cos=dev(cs), rope_sin=dev(sn), append=False)
-        assert rel_err(host(out)[0], g["outs"][i]) < FP_TOL, f"position {t}"
+        assert np.array_equal(host(out)[0], g["outs"][i]), f"position {t}"
 
 
 def test_attention_batched_ragged_lengths(cuda_lib):
@@ -127,7 +133,7 @@ def test_attention_batched_ragged_lengths(cuda_lib):
         qq, kk, vv, o = q[b].copy(), k[b].copy(), v[b].copy(), np.zeros(nq * hd, np.float32)
         O.ora_attention_int8(0, int(pos[b]), nq, nkv, hd, ms, 10000.0, P(qq, ora.c_f32p), P(kk, ora.c_f32p), P(vv, ora.c_f32p),
                              P(o, ora.c_f32p), P(ock, ora.c_i8p), P(ocv, ora.c_i8p), P(osk, ora.c_f32p), P(osv, ora.c_f32p))
-        assert rel_err(host(out)[b], o) < FP_TOL
+        assert np.array_equal(host(out)[b], o), f"sequence {b}: rel err {rel_err(host(out)[b], o):.2e}"
         assert np.array_equal(host(dck)[b].reshape(-1), ock) and np.array_equal(host(dsv)[b].reshape(-1), osv)
 
 
@@ -141,7 +147,7 @@ def test_lm_head_golden_and_argmax(cuda_lib, golden):
     torch.cuda.synchronize()
     assert np.array_equal(host(lg2)[0], g["logits"])                 # teacher-forced: exact
     assert np.array_equal(host(acc2)[0], w.astype(np.int32) @ g["x8"].astype(np.int32))
-    assert rel_err(host(lg)[0], g["logits"]) < FP_TOL
+    assert np.array_equal(host(lg)[0], g["logits"])                  # fused final norm: exact as well
     assert int(host(arg2)[0]) == int(np.argmax(g["logits"])) == int(host(arg)[0])
 
 
