@@ -125,6 +125,26 @@ TENZO_API int tenzo_cuda_lm_head_i8(const float* x, const float* norm_w, int do_
                                     int* argmax_out, void* scratch, int use_pdl, void* stream);
 TENZO_API size_t tenzo_cuda_lm_head_scratch_bytes(int batch);
 
+/* ---- LM head without any allocation -------------------------------------------------------------
+ * No counterpart in the reference. Same computation and results as tenzo_cuda_lm_head_i8, for
+ * callers that are not allowed to allocate device memory while running (a server whose memory is
+ * fully committed to its KV pool, a host application that bans cudaMalloc after start-up): the
+ * argmax scratch is a fixed array inside the library (151,552 bytes held on each GPU that loads the
+ * library, for the life of the process) instead of a caller-provided buffer, and the call performs
+ * no cudaMalloc/cudaFree or other allocating routine.
+ *   - batch <= tenzo_cuda_lm_head_static_max_batch() (32); larger batches return
+ *     TENZO_ERROR_UNSUPPORTED (-5) and should use tenzo_cuda_lm_head_i8 with their own scratch.
+ *   - The first call on each device looks up the array's device address (the device must be
+ *     current); make that first call before starting any stream capture.
+ *   - All calls on a device share the one array. It is fully rewritten by every call, so nothing
+ *     needs clearing, but two calls that overlap on the GPU (different streams) would race on it:
+ *     keep calls on one stream or otherwise ordered. */
+TENZO_API int tenzo_cuda_lm_head_i8_static(const float* x, const float* norm_w, int do_norm, float eps,
+                                           const int8_t* w, const float* row_scales, int vocab, int hidden,
+                                           int batch, int x_stride, float* logits, int32_t* acc_out,
+                                           int* argmax_out, int use_pdl, void* stream);
+TENZO_API int tenzo_cuda_lm_head_static_max_batch(void);
+
 /* ---- INT8 embedding row dequantisation ---------------------------------------------------------
  * Replaces embedding_lookup's int8 branch (:1299-1315): x = (float)W8[tok] * scale[tok]. */
 TENZO_API int tenzo_cuda_embedding_i8(const int8_t* w, const float* row_scales, int hidden,

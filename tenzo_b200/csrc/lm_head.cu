@@ -186,6 +186,50 @@ extern "C" int tenzo_cuda_lm_head_i8(const float* x, const float* norm_w, int do
     return e == cudaSuccess ? 0 : (int)e;
 }
 
+// ---- allocation-free variant ------------------------------------------------------------------
+// The per-CTA argmax candidates (kLmCtas x 8 bytes per sequence) normally live in scratch the caller
+// allocates. Some hosts may not allocate at all once they are running - a serving loop that has
+// handed every byte of device memory to its KV-cache pool, or a plugin slot where the embedding
+// application forbids cudaMalloc after start-up - so this variant keeps that scratch in a fixed
+// device array that is part of the library image. It costs kLmStaticMaxBatch * kLmCtas * 8 bytes
+// (151,552) on every GPU that loads the library, until the process exits.
+namespace tz {
+constexpr int kLmStaticMaxBatch = 32;
+static __device__ __align__(256) unsigned char g_lm_static_scratch[kLmStaticMaxBatch * kLmCtas * sizeof(LmBest)];
+
+// In host code the array's name is only a handle for the runtime, not a device address, so the
+// address is looked up once per device (with that device current) and cached.
+static void* lm_static_scratch_address(cudaError_t* err) {
+    static void* per_device[64] = {nullptr};
+    int dev = 0;
+    *err = cudaGetDevice(&dev);
+    if (*err != cudaSuccess) return nullptr;
+    if (dev < 0 || dev >= 64) { *err = cudaErrorInvalidDevice; return nullptr; }
+    if (!per_device[dev]) {
+        void* p = nullptr;
+        *err = cudaGetSymbolAddress(&p, g_lm_static_scratch);
+        if (*err != cudaSuccess) return nullptr;
+        per_device[dev] = p;
+    }
+    return per_device[dev];
+}
+}  // namespace tz
+
+extern "C" int tenzo_cuda_lm_head_i8_static(const float* x, const float* norm_w, int do_norm, float eps,
+                                            const int8_t* w, const float* row_scales, int vocab, int hidden,
+                                            int batch, int x_stride, float* logits, int32_t* acc_out,
+                                            int* argmax_out, int use_pdl, void* stream) {
+    if (batch > tz::kLmStaticMaxBatch) return -5;   // beyond the built-in scratch: use tenzo_cuda_lm_head_i8
+    if (batch <= 0) return -1;
+    cudaError_t e = cudaSuccess;
+    void* scratch = tz::lm_static_scratch_address(&e);
+    if (!scratch) return (int)e;
+    return tenzo_cuda_lm_head_i8(x, norm_w, do_norm, eps, w, row_scales, vocab, hidden, batch, x_stride, logits,
+                                 acc_out, argmax_out, scratch, use_pdl, stream);
+}
+
+extern "C" int tenzo_cuda_lm_head_static_max_batch(void) { return tz::kLmStaticMaxBatch; }
+
 extern "C" int tenzo_cuda_embedding_i8(const int8_t* w, const float* row_scales, int hidden, const int* tokens,
                                        int batch, float* x, int x_stride, void* stream) {
     if (!w || !row_scales || !tokens || !x || hidden <= 0 || batch <= 0) return -1;

@@ -115,6 +115,17 @@ def lm_head_i8(x, w, row_scales, *, norm_w=None, do_norm=True, eps=1e-5, want_lo
     return logits, acc, arg
 
 
+def lm_head_i8_static(x, w, row_scales, *, norm_w=None, do_norm=True, eps=1e-5, logits=None, argmax=None, use_pdl=False):
+    """LM head through the allocation-free entry point: the caller passes every buffer (logits
+    [batch, vocab] fp32 and argmax [batch] int32, both preallocated); the library allocates nothing."""
+    lib = load_library()
+    batch, hidden = x.shape
+    _ok(lib.tenzo_cuda_lm_head_i8_static(_ptr(x), _ptr(norm_w), int(do_norm), eps, _ptr(w), _ptr(row_scales), w.shape[0],
+                                         hidden, batch, x.stride(0), _ptr(logits), None, _ptr(argmax), int(use_pdl), _stream()),
+        "tenzo_cuda_lm_head_i8_static")
+    return logits, argmax
+
+
 def embedding_i8(w, row_scales, tokens):
     lib = load_library()
     batch, hidden = tokens.shape[0], w.shape[1]
