@@ -52,7 +52,7 @@ private:
     void* d_act_ = nullptr; size_t act_cap_ = 0;
     void* d_w_ = nullptr;   size_t w_cap_ = 0;
     void* d_out_ = nullptr; size_t out_cap_ = 0;
-    void* d_scratch_ = nullptr; size_t scratch_cap_ = 0;
+    void* d_ws_ = nullptr;  size_t ws_cap_ = 0;
 };
 
 }  // namespace tenzo

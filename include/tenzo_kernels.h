@@ -61,18 +61,23 @@ typedef struct {
     float* inv_out;        /* optional [batch] m/31 */
     int batch;
     int x_stride, out_stride;
-    /* split-K scratch, zero-initialised once by the caller and left zero by every launch:
-     * splitk_acc >= batch*n_blocks*64 ints, splitk_cnt >= batch*n_blocks uints. May be NULL when
-     * tenzo_cuda_tl1_gemv_ksplit(...) returns 1 for the shape. */
-    int32_t* splitk_acc;
-    uint32_t* splitk_cnt;
+    const void* prefetch;  /* optional: memory the NEXT kernel in the stream will read (e.g. the next
+                              layer's weights); requested into L2 while this kernel runs */
+    size_t prefetch_bytes;
+    void* workspace;       /* batch > 1 only: tenzo_cuda_tl1_gemv_workspace_bytes(batch, K) bytes, 16-byte
+                              aligned; receives the packed int8 activations (contents need not be kept) */
     int use_pdl;           /* launch with programmatic stream serialisation (weights prefetch
                               overlaps the previous kernel's tail); 0 = ordinary launch */
 } tenzo_tl1_gemv_args;
 
 TENZO_API int tenzo_cuda_tl1_gemv(const tenzo_tl1_gemv_args* args, void* stream);
-/* K-split factor the launcher will pick for this shape (so callers can size the scratch). */
+/* Cluster size along K (1, 2, 4 or 8 CTAs share one row block) the launcher picks for this shape; informational. */
 TENZO_API int tenzo_cuda_tl1_gemv_ksplit(int n_blocks, int K, int epilogue);
+TENZO_API size_t tenzo_cuda_tl1_gemv_workspace_bytes(int batch, int K);
+/* The kernel's waits on asynchronous copies are bounded. Returns 1 (and clears the flag) if any launch
+ * since the last call gave up waiting — its output is then invalid; 0 otherwise; -1 if the query failed.
+ * Synchronises with the device. */
+TENZO_API int tenzo_cuda_tl1_gemv_take_timeouts(void);
 
 /* ---- standalone fused RMSNorm + per-token absmax quantiser ------------------------------------
  * Replaces rms_norm_raw (:148-166) followed by the quantiser half of build_lut (:27-42,

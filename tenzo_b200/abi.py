@@ -50,7 +50,7 @@ class Tl1GemvArgs(C.Structure):
         ("epilogue", C.c_int), ("resid", C.c_void_p), ("out", C.c_void_p),
         ("acc_out", C.c_void_p), ("a_out", C.c_void_p), ("inv_out", C.c_void_p),
         ("batch", C.c_int), ("x_stride", C.c_int), ("out_stride", C.c_int),
-        ("splitk_acc", C.c_void_p), ("splitk_cnt", C.c_void_p), ("use_pdl", C.c_int),
+        ("prefetch", C.c_void_p), ("prefetch_bytes", C.c_size_t), ("workspace", C.c_void_p), ("use_pdl", C.c_int),
     ]
 
 
@@ -80,7 +80,7 @@ EXT_SYMBOLS = [
     "tenzo_ext_kernel_launches", "tenzo_ext_last_error", "tenzo_ext_bench_gemv_stack",
 ]
 KERNEL_SYMBOLS = [
-    "tenzo_cuda_tl1_gemv", "tenzo_cuda_tl1_gemv_ksplit", "tenzo_cuda_rmsnorm_quant", "tenzo_cuda_attention_int8",
+    "tenzo_cuda_tl1_gemv", "tenzo_cuda_tl1_gemv_ksplit", "tenzo_cuda_tl1_gemv_workspace_bytes", "tenzo_cuda_tl1_gemv_take_timeouts", "tenzo_cuda_rmsnorm_quant", "tenzo_cuda_attention_int8",
     "tenzo_cuda_attention_heads_per_cta", "tenzo_cuda_lm_head_i8", "tenzo_cuda_lm_head_scratch_bytes",
     "tenzo_cuda_embedding_i8", "tenzo_cuda_tl1_pack_rows2bit", "tenzo_cuda_lm_head_i8_static",
     "tenzo_cuda_lm_head_static_max_batch",
@@ -143,6 +143,8 @@ def declare_kernel_abi(L):
     vp, i32, f32, sz = C.c_void_p, C.c_int, C.c_float, C.c_size_t
     L.tenzo_cuda_tl1_gemv.restype, L.tenzo_cuda_tl1_gemv.argtypes = i32, [C.POINTER(Tl1GemvArgs), vp]
     L.tenzo_cuda_tl1_gemv_ksplit.restype, L.tenzo_cuda_tl1_gemv_ksplit.argtypes = i32, [i32, i32, i32]
+    L.tenzo_cuda_tl1_gemv_workspace_bytes.restype, L.tenzo_cuda_tl1_gemv_workspace_bytes.argtypes = sz, [i32, i32]
+    L.tenzo_cuda_tl1_gemv_take_timeouts.restype, L.tenzo_cuda_tl1_gemv_take_timeouts.argtypes = i32, []
     L.tenzo_cuda_rmsnorm_quant.restype = i32
     L.tenzo_cuda_rmsnorm_quant.argtypes = [vp, vp, i32, f32, i32, i32, i32, i32, vp, vp, vp, vp]
     L.tenzo_cuda_attention_int8.restype, L.tenzo_cuda_attention_int8.argtypes = i32, [C.POINTER(AttentionArgs), vp]

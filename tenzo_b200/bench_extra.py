@@ -1,0 +1,158 @@
+"""Secondary benchmark workloads (BASELINE configs 0, 2, 3), reached through `bench.py --workload`.
+
+  gemv          config 0: one TL1 bitlinear GEMV 6912 x 2560 at batch 1, cycled over 64 distinct
+                seeded matrices (283 MB, larger than L2) captured in one CUDA graph.
+  attn          config 2: fused INT8-KV GQA decode attention alone, batch 64, 20/5 heads, ctx 8192.
+  decode_batch  config 3: batched greedy decode of the BitNet-2B shape, KV prefilled on the device.
+
+Each prints one JSON line in the same format as the default workload.
+"""
+from __future__ import annotations
+
+import json
+import os
+
+import numpy as np
+
+from . import synth
+
+
+def _peak():
+    from pathlib import Path
+    p = Path(__file__).resolve().parents[1] / "MEASURED_PEAKS.json"
+    if p.exists():
+        return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def _random_tl1_device(n_bytes: int, seed: int):
+    import torch
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    table = torch.from_numpy(synth._BYTE81).cuda()
+    return table[torch.randint(0, 81, (n_bytes,), generator=g, device="cuda", dtype=torch.int64)].contiguous()
+
+
+def run_gemv(args):
+    import torch
+    from . import kernels
+    N, K, n_mat = 6912, 2560, 64
+    ws = [_random_tl1_device(N * K // 4, 100 + i) for i in range(n_mat)]
+    x = torch.randn(1, K, device="cuda", generator=torch.Generator(device="cuda").manual_seed(1))
+    out = torch.empty(1, N, device="cuda")
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        for w in ws[:2]:
+            kernels.tl1_gemv(x, w, N // 64, K, [0.016], out=out, use_pdl=bool(args.pdl))
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for i, w in enumerate(ws):      # each launch asks L2 for the next matrix, as the decode engine does
+                kernels.tl1_gemv(x, w, N // 64, K, [0.016], out=out, use_pdl=bool(args.pdl), prefetch=ws[(i + 1) % n_mat])
+        for _ in range(max(3, args.warmup)):
+            graph.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        stream.synchronize()
+        e0.record(stream)
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record(stream)
+        stream.synchronize()
+    ms = e0.elapsed_time(e1)
+    launches = args.steps * n_mat
+    bytes_per = N * K // 4 + 4 * K + 4 * N
+    gbs = bytes_per * launches / (ms * 1e-3) / 1e9
+    peak = _peak()
+    print(json.dumps({
+        "metric": "tl1_gemv_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup),
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
+        "data": "synthetic", "config": {"workload": f"gemv: TL1 bitlinear {N}x{K}, batch 1, {n_mat} distinct matrices per step "
+                                                    f"({n_mat * N * K // 4 / 1e6:.0f} MB > L2), one graph per step", "pdl": int(args.pdl)},
+        "gpu_launches": launches,
+        "roofline": {"bound": "hbm", "kernel": "tl1_gemv_kernel", "achieved": gbs, "peak": peak[0], "peak_source": peak[1], "unit": "GB/s",
+                     "frac": gbs / peak[0], "traffic": None, "bytes_per_launch": bytes_per, "us_per_launch": ms * 1e3 / launches},
+    }), flush=True)
+
+
+def run_attn(args):
+    import torch
+    from . import kernels
+    B, nq, nkv, T = args.batch if args.batch != 256 else 64, 20, 5, args.context if args.context != 4096 else 8192
+    g = torch.Generator(device="cuda").manual_seed(2)
+    ck = torch.randint(-127, 128, (B, 1, nkv, T, 128), generator=g, device="cuda", dtype=torch.int8)
+    cv = torch.randint(-127, 128, (B, 1, nkv, T, 128), generator=g, device="cuda", dtype=torch.int8)
+    sk = 0.01 + 0.02 * torch.rand(B, 1, nkv, T, generator=g, device="cuda")
+    sv = 0.01 + 0.02 * torch.rand(B, 1, nkv, T, generator=g, device="cuda")
+    q = torch.randn(B, nq * 128, generator=g, device="cuda")
+    k = torch.randn(B, nkv * 128, generator=g, device="cuda")
+    v = torch.randn(B, nkv * 128, generator=g, device="cuda")
+    pos = torch.full((B,), T - 1, dtype=torch.int32, device="cuda")
+    for _ in range(max(3, args.warmup)):
+        kernels.attention_int8(q, k, v, ck, cv, sk, sv, pos, layer=0, n_q=nq, n_kv=nkv, max_seq=T, max_len=T)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(args.steps):
+        kernels.attention_int8(q, k, v, ck, cv, sk, sv, pos, layer=0, n_q=nq, n_kv=nkv, max_seq=T, max_len=T)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    bytes_per = B * nkv * T * (2 * 128 + 8) + B * nq * 128 * 8
+    gbs = bytes_per / (ms * 1e-3) / 1e9
+    peak = _peak()
+    print(json.dumps({
+        "metric": "attention_int8_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup),
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 x int8", "data": "synthetic",
+        "config": {"workload": f"attn: fused INT8-KV GQA decode attention, batch {B}, {nq}q/{nkv}kv heads, context {T}",
+                   "l2": f"KV {bytes_per / 1e6:.0f} MB per step, larger than L2"},
+        "gpu_launches": args.steps,
+        "roofline": {"bound": "hbm", "kernel": "attn_kernel", "achieved": gbs, "peak": peak[0], "peak_source": peak[1], "unit": "GB/s",
+                     "frac": gbs / peak[0], "traffic": None, "bytes_per_launch": bytes_per, "us_per_launch": ms * 1e3},
+    }), flush=True)
+
+
+def run_decode_batch(args):
+    import torch
+    from .engine import Engine
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))))
+    B = args.batch // world                      # sequences are sharded across ranks, no data-path collective
+    ctx = args.context
+    cfg = dict(synth.BITNET_2B, max_seq_len=ctx + args.steps + max(3, args.warmup) + 8)
+    model = synth.SyntheticModel(cfg, seed=0)
+    eng = Engine(model.config_struct(), batch=B).load_synthetic(model)
+    eng.kv_fill_random(ctx, seed=rank)
+    first = synth.prompt_tokens(1000 + rank, B, cfg["vocab_size"])
+    warm = eng.decode_greedy(first, max(3, args.warmup))
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    l0 = eng.kernel_launches()
+    eng.decode_greedy(warm[-1], args.steps)
+    ms = eng.last_device_ms()
+    launches = eng.kernel_launches() - l0
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    if rank == 0:
+        print(json.dumps({
+            "metric": "decode_tokens_per_second_batched", "value": B * world * args.steps / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": {"workload": f"decode_batch: BitNet-2B shape, global batch {B * world}, context {ctx} (device-filled KV), "
+                                   f"{B} sequences per GPU", "parallelism": f"dp{world}"},
+            "gpu_launches": int(launches),
+        }), flush=True)
+    eng.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run(args):
+    fn = {"gemv": run_gemv, "attn": run_attn, "decode_batch": run_decode_batch}.get(args.workload)
+    if fn is None:
+        raise SystemExit(f"unknown workload {args.workload!r}")
+    return fn(args)

@@ -35,6 +35,48 @@ __device__ __forceinline__ uint4 ld_stream_u4(const void* p) {
 // Coherent (L2) loads for data another CTA of the same kernel may have just written.
 __device__ __forceinline__ uint4 ld_cg_u4(const void* p) { return __ldcg(reinterpret_cast<const uint4*>(p)); }
 
+// Ask L2 to fetch [base, base+bytes) ahead of use: the kernels of a decode step run one after another
+// on data-dependent vectors, so each kernel requests the NEXT kernel's weights while it works and
+// HBM keeps streaming across kernel boundaries. Work is spread over the whole grid, one line per thread.
+__device__ __forceinline__ void l2_prefetch_slice(const void* base, size_t bytes) {
+    if (!base) return;
+    const size_t n_lines = (bytes + 127) / 128;
+    const size_t cta = blockIdx.x + (size_t)gridDim.x * (blockIdx.y + (size_t)gridDim.y * blockIdx.z);
+    const size_t n_threads = (size_t)gridDim.x * gridDim.y * gridDim.z * blockDim.x;
+    for (size_t c = cta * blockDim.x + threadIdx.x; c < n_lines; c += n_threads)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(static_cast<const char*>(base) + c * 128));
+}
+
+// ---- bulk asynchronous copy (TMA, 1-D) global -> shared with mbarrier completion ---------------------
+// A bulk copy keeps tens of kilobytes in flight per SM from a single instruction; ordinary loads
+// are capped by the load/store unit's request queue long before HBM latency is covered.
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_init_fence() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+// dst and src 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, unsigned bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_addr(dst)), "l"(src), "r"(bytes), "r"(smem_addr(bar)) : "memory");
+}
+// Wait for phase `parity` of an mbarrier, giving up after a bounded number of polls (each poll
+// already blocks for a hardware-defined interval). Returns false on give-up so the caller can flag
+// the failure and leave instead of hanging the GPU.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, unsigned parity) {
+    const uint32_t addr = smem_addr(bar);
+    for (int it = 0; it < (1 << 20); ++it) {
+        uint32_t done;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
 // Programmatic dependent launch: wait until the kernels this one depends on have completed and
 // their memory is visible / allow the next kernel in the stream to begin its own prologue.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
@@ -90,8 +132,18 @@ __device__ __forceinline__ float sumsq_reference_order(const float* x, int dim, 
     const int n8 = dim & ~7;
     if (threadIdx.x < 8) {
         float s = 0.0f;
-#pragma unroll 8
-        for (int i = threadIdx.x; i < n8; i += 8) {
+        int i = threadIdx.x;
+        // 16 loads in flight ahead of the dependent adds: the chain runs at add latency, not load latency
+        for (; i + 8 * 15 < n8; i += 8 * 16) {
+            float v[16];
+#pragma unroll
+            for (int u = 0; u < 16; ++u) v[u] = x[i + 8 * u];
+#pragma unroll
+            for (int u = 0; u < 16; ++u) v[u] = __fmul_rn(v[u], v[u]);
+#pragma unroll
+            for (int u = 0; u < 16; ++u) s = __fadd_rn(s, v[u]);
+        }
+        for (; i < n8; i += 8) {
             const float v = x[i];
             s = __fadd_rn(s, __fmul_rn(v, v));
         }

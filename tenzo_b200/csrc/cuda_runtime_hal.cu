@@ -82,11 +82,8 @@ bool CUDARuntime::executeBitLinearTL1(const float* act, const uint8_t* weight, f
     cudaStream_t st = static_cast<cudaStream_t>(stream_);
     const size_t wb = N * K / 4, nb = N / 64;
     if (!ensure(M * K * 4, wb, M * N * 4)) return false;
-    const size_t need = M * nb * 64 * 4 + M * nb * 4;
-    if (need > scratch_cap_) {
-        if (!grow(d_scratch_, scratch_cap_, need)) return false;
-        if (cudaMemsetAsync(d_scratch_, 0, need, st) != cudaSuccess) return false;
-    }
+    const size_t ws_bytes = tenzo_cuda_tl1_gemv_workspace_bytes((int)M, (int)K);
+    if (!grow(d_ws_, ws_cap_, ws_bytes)) return false;
     if (cudaMemcpyAsync(d_act_, act, M * K * 4, cudaMemcpyHostToDevice, st) != cudaSuccess) return false;
     if (cudaMemcpyAsync(d_w_, weight, wb, cudaMemcpyHostToDevice, st) != cudaSuccess) return false;
     tenzo_tl1_gemv_args g;
@@ -95,8 +92,7 @@ bool CUDARuntime::executeBitLinearTL1(const float* act, const uint8_t* weight, f
     g.w = static_cast<const uint8_t*>(d_w_); g.n_blocks = (int)nb; g.K = (int)K;
     g.seg_end[0] = g.seg_end[1] = g.seg_end[2] = (int)nb; g.seg_scale[0] = scale;
     g.epilogue = TENZO_EPI_STORE; g.out = static_cast<float*>(d_out_); g.out_stride = (int)N; g.batch = (int)M;
-    g.splitk_acc = static_cast<int32_t*>(d_scratch_);
-    g.splitk_cnt = reinterpret_cast<uint32_t*>(static_cast<char*>(d_scratch_) + M * nb * 64 * 4);
+    g.workspace = d_ws_;
     if (tenzo_cuda_tl1_gemv(&g, st) != 0) return false;
     if (cudaMemcpyAsync(out, d_out_, M * N * 4, cudaMemcpyDeviceToHost, st) != cudaSuccess) return false;
     return cudaStreamSynchronize(st) == cudaSuccess;

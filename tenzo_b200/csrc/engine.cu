@@ -164,10 +164,8 @@ Engine::Engine(const tenzo_config_t& c, const tenzo_ext_options_t& o) : cfg(c) {
         TZ_CUDA(cudaStreamSynchronize(stream));
     }
 
-    const int widest_blocks = (qd + 2 * kvd > 2 * ffn ? qd + 2 * kvd : 2 * ffn) / 64;
-    splitk_acc = (int32_t*)dalloc(B * widest_blocks * 64 * 4);
-    splitk_cnt = (uint32_t*)dalloc(B * widest_blocks * 4);
     lm_scratch = dalloc(tenzo_cuda_lm_head_scratch_bytes(batch));
+    gemv_ws = dalloc(tenzo_cuda_tl1_gemv_workspace_bytes(batch, h > ffn ? h : ffn));
 
     TZ_CUDA(cudaMallocHost(&h_pin, (3 * B + 16) * sizeof(int)));
     h_tokens = h_pin;
@@ -265,9 +263,8 @@ void Engine::enqueue_layer(int l, int max_len, bool gemv_only) {
     g.eps = 1e-5f;
     g.do_norm = 1;
     g.batch = batch;
-    g.splitk_acc = splitk_acc;
-    g.splitk_cnt = splitk_cnt;
     g.use_pdl = use_pdl;
+    g.workspace = gemv_ws;
 
     // q | k | v
     g.x = b_x; g.x_stride = h; g.norm_w = d.in_norm; g.w = d.qkv; g.K = h;
@@ -275,6 +272,7 @@ void Engine::enqueue_layer(int l, int max_len, bool gemv_only) {
     g.seg_end[0] = qd / 64; g.seg_end[1] = (qd + kvd) / 64; g.seg_end[2] = g.n_blocks;
     g.seg_scale[0] = d.s_q; g.seg_scale[1] = d.s_k; g.seg_scale[2] = d.s_v;
     g.epilogue = TENZO_EPI_STORE; g.out = b_qkv; g.out_stride = qd + 2 * kvd;
+    g.prefetch = d.o; g.prefetch_bytes = (size_t)h * h / 4;
     TZ_KERNEL(tenzo_cuda_tl1_gemv(&g, stream));
     launches += 1;
 
@@ -298,6 +296,9 @@ void Engine::enqueue_layer(int l, int max_len, bool gemv_only) {
     g.x = b_attn; g.x_stride = qd; g.norm_w = d.attn_sub_norm; g.w = d.o; g.K = h;
     g.n_blocks = h / 64; g.seg_end[0] = g.seg_end[1] = g.seg_end[2] = g.n_blocks; g.seg_scale[0] = d.s_o;
     g.epilogue = TENZO_EPI_RESIDUAL; g.resid = b_x; g.out = b_h1; g.out_stride = h;
+    const LayerDev* nxt = l + 1 < L ? &layers[l + 1] : nullptr;
+    if (d.has_mlp) { g.prefetch = d.gateup; g.prefetch_bytes = (size_t)2 * ffn * h / 4; }
+    else { g.prefetch = nxt ? nxt->qkv : nullptr; g.prefetch_bytes = (size_t)(qd + 2 * kvd) * h / 4; }
     TZ_KERNEL(tenzo_cuda_tl1_gemv(&g, stream));
     launches += 1;
 
@@ -306,11 +307,14 @@ void Engine::enqueue_layer(int l, int max_len, bool gemv_only) {
         g.n_blocks = 2 * ffn / 64; g.seg_end[0] = ffn / 64; g.seg_end[1] = g.seg_end[2] = g.n_blocks;
         g.seg_scale[0] = d.s_gate; g.seg_scale[1] = d.s_up;
         g.epilogue = TENZO_EPI_RELU2_GLU; g.resid = nullptr; g.out = b_act; g.out_stride = ffn;
+        g.prefetch = d.down; g.prefetch_bytes = (size_t)h * ffn / 4;
         TZ_KERNEL(tenzo_cuda_tl1_gemv(&g, stream));
 
         g.x = b_act; g.x_stride = ffn; g.norm_w = d.ffn_sub_norm; g.w = d.down; g.K = ffn;
         g.n_blocks = h / 64; g.seg_end[0] = g.seg_end[1] = g.seg_end[2] = g.n_blocks; g.seg_scale[0] = d.s_down;
         g.epilogue = TENZO_EPI_RESIDUAL; g.resid = b_h1; g.out = b_x; g.out_stride = h;
+        if (nxt) { g.prefetch = nxt->qkv; g.prefetch_bytes = (size_t)(qd + 2 * kvd) * h / 4; }
+        else { g.prefetch = lm_w; g.prefetch_bytes = (size_t)64 << 20; if ((size_t)V * h < g.prefetch_bytes) g.prefetch_bytes = (size_t)V * h; }
         TZ_KERNEL(tenzo_cuda_tl1_gemv(&g, stream));
         launches += 2;
     } else {
@@ -391,6 +395,13 @@ void Engine::push_state(const int* tokens) {
     TZ_CUDA(cudaMemcpyAsync(d_pos, h_pos, (size_t)batch * 4, cudaMemcpyHostToDevice, stream));
 }
 
+// The TL1 kernel's waits on asynchronous copies are bounded; a give-up is reported here instead of
+// hanging the device. Polled sparsely on the per-token path (the query synchronises).
+void Engine::check_device_status(bool force) {
+    if (!force && (++status_poll & 31) != 0) return;
+    if (tenzo_cuda_tl1_gemv_take_timeouts() > 0) throw std::runtime_error("a TL1 kernel gave up waiting for its weight copy; results are invalid");
+}
+
 void Engine::prefill(const int* tokens) {
     push_state(tokens);
     TZ_CUDA(cudaEventRecord(ev0, stream));
@@ -406,6 +417,7 @@ void Engine::generate(const int* cur, int* out) {
     TZ_CUDA(cudaEventRecord(ev1, stream));
     TZ_CUDA(cudaMemcpyAsync(h_next, d_next, (size_t)batch * 4, cudaMemcpyDeviceToHost, stream));
     TZ_CUDA(cudaStreamSynchronize(stream));
+    check_device_status(false);
     for (int s = 0; s < batch; ++s) out[s] = h_next[s];
 }
 
@@ -427,6 +439,7 @@ void Engine::decode_greedy(const int* first, int n_steps, int* out) {
     TZ_CUDA(cudaEventRecord(ev1, stream));
     TZ_CUDA(cudaMemcpyAsync(out, d_history, (size_t)n_steps * batch * 4, cudaMemcpyDeviceToHost, stream));
     TZ_CUDA(cudaStreamSynchronize(stream));
+    check_device_status(true);
 }
 
 void Engine::kv_fill(int len, unsigned long long seed) {

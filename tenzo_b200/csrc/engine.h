@@ -49,6 +49,8 @@ public:
     void invalidate_graphs();
     void* upload(const void* host, size_t bytes);
     float last_ms();
+    void check_device_status(bool force);
+    unsigned status_poll = 0;
     void kv_fill(int len, unsigned long long seed);
 
     tenzo_config_t cfg;
@@ -69,9 +71,7 @@ public:
     float *scale_k = nullptr, *scale_v = nullptr;
     size_t kv_rows_per_seq = 0;
     float *rope_cos = nullptr, *rope_sin = nullptr;
-    int32_t* splitk_acc = nullptr;
-    uint32_t* splitk_cnt = nullptr;
-    void* lm_scratch = nullptr;
+    void *lm_scratch = nullptr, *gemv_ws = nullptr;
     int *h_pin = nullptr, *h_tokens = nullptr, *h_pos = nullptr, *h_next = nullptr;
     std::vector<int> seq_len;
     std::vector<void*> owned;

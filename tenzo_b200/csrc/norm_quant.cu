@@ -56,6 +56,72 @@ __global__ void __launch_bounds__(kNqThreads) rmsnorm_quant_kernel(
     }
 }
 
+// Batched front half of the TL1 GEMM: per sequence RMSNorm + absmax(31) quantiser, written as the
+// packed tensor-core B fragments tl1_mma_kernel consumes: words[seq][set][t][0] holds 4*a for the
+// even columns of column pairs 16*set + 4*i + t (byte i = 0..3), words[seq][set][t][1] the odd
+// columns unscaled; columns beyond K are zero. inv[seq] = max|y|/31.
+__global__ void __launch_bounds__(kNqThreads) act_quant_kernel(
+    const float* x, const float* __restrict__ norm_w, int do_norm, float eps, int K, int x_stride,
+    uint32_t* words, float* inv, int8_t* a_out, int use_pdl) {
+    extern __shared__ float s_y[];            // K floats + 32 scratch
+    float* s_f = s_y + K;
+    const int tid = threadIdx.x, seq = blockIdx.x;
+    if (use_pdl) pdl_wait();
+    const float* xs = x + (size_t)seq * x_stride;
+    for (int i = tid; i < K; i += kNqThreads) s_y[i] = __ldcg(xs + i);
+    __syncthreads();
+    float m = 0.0f;
+    if (do_norm) {
+        const float ss = sumsq_reference_order(s_y, K, s_f);
+        const float inv_rms = rms_inv(ss, K, eps);
+        for (int i = tid; i < K; i += kNqThreads) {
+            const float y = rms_apply(s_y[i], inv_rms, norm_w, i);
+            s_y[i] = y;
+            m = fmaxf(m, fabsf(y));
+        }
+    } else {
+        for (int i = tid; i < K; i += kNqThreads) m = fmaxf(m, fabsf(s_y[i]));
+    }
+    m = fmaxf(block_max(m, s_f), 1e-6f);      // TenzoEngine.cpp:28-32
+    const float to_q = 31.0f / m;             // :34
+    if (use_pdl) pdl_launch_dependents();
+    const int nsets = ((K >> 1) + 15) / 16;
+    for (int wd = tid; wd < nsets * 8; wd += kNqThreads) {
+        const int s = wd >> 3, tt = (wd >> 1) & 3, odd = wd & 1;
+        uint32_t word = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int col = 2 * (16 * s + 4 * i + tt) + odd;
+            const int q = col < K ? (int)roundf(s_y[col] * to_q) : 0;   // :41-42
+            word |= (uint32_t)(uint8_t)(int8_t)(odd ? q : 4 * q) << (8 * i);
+        }
+        words[(size_t)seq * nsets * 8 + wd] = word;
+    }
+    if (tid == 0) inv[seq] = m / 31.0f;       // :35
+    if (a_out)
+        for (int i = tid; i < K; i += kNqThreads) a_out[(size_t)seq * K + i] = (int8_t)(int)roundf(s_y[i] * to_q);
+}
+
+cudaError_t launch_act_quant(const float* x, const float* norm_w, int do_norm, float eps, int K, int batch, int x_stride,
+                             uint32_t* words, float* inv, int8_t* a_out, int use_pdl, cudaStream_t st) {
+    const size_t smem = (size_t)(K + 32) * sizeof(float);
+    if (smem > 48 * 1024) {
+        cudaError_t ea = cudaFuncSetAttribute(act_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024);
+        if (ea != cudaSuccess) return ea;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)batch, 1, 1);
+    cfg.blockDim = dim3(kNqThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = use_pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, act_quant_kernel, x, norm_w, do_norm, eps, K, x_stride, words, inv, a_out, use_pdl);
+}
+
 }  // namespace tz
 
 extern "C" int tenzo_cuda_rmsnorm_quant(const float* x, const float* norm_w, int do_norm, float eps, int dim,

@@ -1,5 +1,6 @@
-// TL1 ternary GEMV for sm_100a with the RMSNorm + absmax(31) activation quantiser fused into its
-// prologue and the reference's three epilogues (store / residual add / squared-ReLU GLU).
+// TL1 ternary GEMV / skinny GEMM for sm_100a on the int8 tensor-core path (mma.sync m16n8k32,
+// u8 x s8 -> s32), with the RMSNorm + absmax(31) activation quantiser fused into its prologue at
+// batch 1 and the reference's three epilogues (store / residual add / squared-ReLU GLU).
 //
 // What it replaces in the reference CPU engine (src/runtime/TenzoEngine.cpp): rms_norm_raw
 // (:148-166), build_lut (:22-62), compute_single_block (:64-127) and their call sites (:1542-1628).
@@ -8,260 +9,451 @@
 //   * The reference looks every 4-bit index up in a 16-entry table of clamp(w0*a0+w1*a1). With
 //     |a| <= 31 the clamp can never fire, so the accumulator is the plain integer dot product
 //     sum_k w[r][k]*a[k]; any exact integer evaluation gives the same int32.
-//   * A warp streams one 64-row block in tiles of 64 column pairs (2 KB, four coalesced 128-bit
-//     loads per lane, all issued before anything else so HBM latency is paid once).
-//     Lane l's i-th load holds, for column pair g = 64t + 16i + (l>>1), the 16 bytes of row pairs
-//     c = 16(l&1) .. +15. A 4x4 byte transpose (8 PRMT per 16 bytes) turns that into words that
-//     carry ONE row pair at four column pairs, which is the shape dp4a wants.
-//   * Each byte is c0 | c1<<2 | c2<<4 | c3<<6 with codes c = w+1 in {0,1,2}: (c0,c1) = row c at
-//     columns (2g,2g+1), (c2,c3) = row c+32. Masking (no shifts) gives bytes c0, 4*c1, 16*c2,
-//     64*c3; the even-column activation is stored pre-multiplied by 4 (|4a| <= 124 fits int8), so
-//     dp4a(mask0,4a_even)+dp4a(mask1,a_odd) = 4*sum(c*a) for the low row and the other two masks
-//     give 64*sum(c*a) for the high row. One LOP3 + one DP4A per 4 weights.
-//   * sum(w*a) = sum(c*a) - sum(a); sum(a) falls out of two extra dp4a per tile.
-//   * Lanes of equal parity hold partial sums for the same 32 rows at different columns: a
-//     halving butterfly (30 shuffles) leaves every lane with two finished rows.
-//   * K can be split across CTAs; partials meet in an int32 scratch through atomicAdd (integer,
-//     hence order-free and exact) and the last CTA to arrive runs the epilogue and re-zeroes the
-//     scratch.
+//   * Weights stay in the reference's layout [N/64][K/2][32 B]. Lane (g = lane>>2, t = lane&3) of a
+//     warp reads, for a "set" of 16 column pairs, the four 32-bit words at byte 4g of column pairs
+//     16s+4i+t (i = 0..3) from the staged copy (bank-conflict free). A 4x4 byte transpose
+//     (8 PRMT) turns them into T[j] = row pair 4g+j at those four column pairs.
+//   * A byte of the layout is c0 | c1<<2 | c2<<4 | c3<<6 with codes c = w+1 in {0,1,2}: (c0,c1) =
+//     row c at columns (2p,2p+1), (c2,c3) = row c+32. Masking without shifting gives bytes
+//     c0, 4c1, 16c2, 64c3 — four ready-made u8 A fragments of mma.m16n8k32:
+//        a0 = T&0x03.. (row 4g+j, even cols)    a2 = T&0x0C.. (row 4g+j, odd cols, x4)
+//        a1 = T&0x30.. (row 32+4g+j, even, x16) a3 = T&0xC0.. (row 32+4g+j, odd, x64)
+//     The B fragment holds the int8 activations of up to 8 sequences, even columns pre-multiplied
+//     by 4 (|4a| <= 124), so the low rows accumulate 4*sum(c*a) and the high rows 64*sum(c*a).
+//     One LOP3 per fragment register, four MMAs per 512 weight bytes per 8 sequences, and the
+//     tensor core does the reduction over k that a dot-product kernel would do with shuffles.
+//   * sum(w*a) = sum(c*a) - sum(a); sum(a) per sequence is accumulated while the activations are
+//     staged.
+//   * K can be split across the CTAs of a thread-block cluster (2, 4 or 8): partials meet in the
+//     leader CTA's shared memory through distributed-shared-memory atomicAdd (integer, hence
+//     order-free and exact) between hardware cluster barriers; the leader runs the epilogue.
+//   * Each CTA brings its weight bytes into shared memory with 1-D bulk asynchronous copies (TMA)
+//     completing on mbarriers, issued by one thread as the very first thing the kernel does: tens
+//     of kilobytes per SM are in flight from a handful of instructions, which ordinary loads cannot
+//     do (the load/store unit's request queue saturates at a fraction of the HBM latency-bandwidth
+//     product). Every wait on an mbarrier is bounded; a give-up raises a flag the host can read.
+//   * Nothing that does not depend on the previous kernel waits for it: the bulk copies, the norm
+//     weights and an L2 prefetch of the NEXT kernel's weights are issued before griddepcontrol.wait.
+//   * batch == 1: every CTA normalises and quantises the activation itself (bit-identical to the
+//     reference, see common.cuh) and only packs the columns of its own K range.
+//     batch > 1: act_quant_kernel (norm_quant.cu) has written packed int8 activations to a
+//     workspace; CTAs stage their K range for 8 or 32 sequences and reuse every weight word for all.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "../../include/tenzo_kernels.h"
 
 namespace tz {
 
-constexpr int kGemvWarps = 8;
-constexpr int kGemvThreads = kGemvWarps * 32;
-constexpr int kTileGroups = 64;   // column pairs per warp tile
-constexpr int kUnroll = 4;        // tiles whose loads are in flight per warp at once
+namespace cg = cooperative_groups;
+
+#ifndef TZ_FUSED_WARPS
+#define TZ_FUSED_WARPS 16
+#endif
+constexpr int kFusedWarps = TZ_FUSED_WARPS;    // batch 1: one CTA per row block; two fit on an SM so consecutive kernels overlap
+constexpr int kBatchedWarps = 16;
 
 struct GemvLaunch {
     tenzo_tl1_gemv_args a;
-    int ksplit;
+    int ksplit;      // cluster size along K
     int units;       // CTAs along the row dimension (n_blocks, or n_blocks/2 in GLU mode)
-    int tiles;       // ceil(K/2 / 64)
+    int nsets;       // ceil(K/2 / 16)
+    const uint32_t* act_words;   // batch > 1: [batch][nsets][4][2] packed activations
+    const float* act_inv;        // batch > 1: [batch] m/31
 };
 
 __device__ __forceinline__ float seg_scale_for(const tenzo_tl1_gemv_args& a, int block) {
     return block < a.seg_end[0] ? a.seg_scale[0] : (block < a.seg_end[1] ? a.seg_scale[1] : a.seg_scale[2]);
 }
 
-// One tile: 4 registers-worth (uint4) per lane already loaded; accumulate into lo/hi.
-__device__ __forceinline__ void consume_tile(const uint4 (&r)[4], uint32_t ae4, uint32_t ao,
-                                             int (&lo)[16], int (&hi)[16], int& sa4) {
-    sa4 = dp4a_us(0x01010101u, ae4, sa4);
-    sa4 = dp4a_us(0x04040404u, ao, sa4);
-    const uint32_t* w0 = reinterpret_cast<const uint32_t*>(&r[0]);
-    const uint32_t* w1 = reinterpret_cast<const uint32_t*>(&r[1]);
-    const uint32_t* w2 = reinterpret_cast<const uint32_t*>(&r[2]);
-    const uint32_t* w3 = reinterpret_cast<const uint32_t*>(&r[3]);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        // 4x4 byte transpose: T[m] = (R0.m, R1.m, R2.m, R3.m)
-        const uint32_t t0 = prmt(w0[j], w1[j], 0x5140u), t1 = prmt(w2[j], w3[j], 0x5140u);
-        const uint32_t t2 = prmt(w0[j], w1[j], 0x7362u), t3 = prmt(w2[j], w3[j], 0x7362u);
-        uint32_t T[4];
-        T[0] = prmt(t0, t1, 0x5410u);
-        T[1] = prmt(t0, t1, 0x7632u);
-        T[2] = prmt(t2, t3, 0x5410u);
-        T[3] = prmt(t2, t3, 0x7632u);
-#pragma unroll
-        for (int m = 0; m < 4; ++m) {
-            const int c = 4 * j + m;
-            lo[c] = dp4a_us(T[m] & 0x03030303u, ae4, lo[c]);
-            lo[c] = dp4a_us(T[m] & 0x0C0C0C0Cu, ao, lo[c]);
-            hi[c] = dp4a_us(T[m] & 0x30303030u, ae4, hi[c]);
-            hi[c] = dp4a_us(T[m] & 0xC0C0C0C0u, ao, hi[c]);
-        }
-    }
+__device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__global__ void __launch_bounds__(kGemvThreads) tl1_gemv_kernel(const GemvLaunch L) {
+__device__ __forceinline__ uint32_t ld_stream_u32(const void* p) {
+    uint32_t v;
+    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+
+// Optional in-kernel timeline (compile with -DTZ_TRACE): first and last CTA record %globaltimer at
+// stage boundaries into g_trace; compiled out of the library build.
+#ifdef TZ_TRACE
+__device__ unsigned long long g_trace[4096 * 8];
+__device__ unsigned int g_trace_n;
+__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define TZ_TRACE_DECL unsigned long long tr[8] = {0, 0, 0, 0, 0, 0, 0, 0}
+#define TZ_STAMP(k) do { if (threadIdx.x == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)) tr[k] = gtime(); } while (0)
+#define TZ_TRACE_FLUSH do { if (threadIdx.x == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)) { \
+    const unsigned slot = atomicAdd(&g_trace_n, 1u); \
+    if (slot < 4096) { for (int k = 0; k < 7; ++k) g_trace[slot * 8 + k] = tr[k]; g_trace[slot * 8 + 7] = blockIdx.x; } } } while (0)
+#else
+#define TZ_TRACE_DECL do {} while (0)
+#define TZ_STAMP(k) do {} while (0)
+#define TZ_TRACE_FLUSH do {} while (0)
+#endif
+
+constexpr int kChunks = 8;         // bulk copies (and mbarriers) per row block: compute starts when the first lands
+
+__device__ int g_tl1_timeouts = 0; // set when a bounded mbarrier wait gave up (the result of that launch is invalid)
+
+template <int NT, bool FUSED>
+struct GemvSmem {
+    static constexpr int SL = FUSED ? 1 : 8 * NT;                       // sequences per CTA
+    // 32-bit words: s_d[128*SL] | s_sa4[SL] | s_inv[SL] | scratch[32] | mbarriers[2*kChunks x 2 words]
+    //               | s_b[sets*SL*8] | weights[nb_cta*sets*128] | (fused) x[K]
+    static __host__ __device__ int head_words() { return (128 * SL + 2 * SL + 32 + 2 + 4 * kChunks + 3) & ~3; }
+    static __host__ __device__ size_t bytes(int sets_per_cta, int K, int nb_cta) {
+        return (size_t)(head_words() + sets_per_cta * SL * 8 + nb_cta * sets_per_cta * 128 + (FUSED ? K + 8 : 0)) * 4;
+    }
+};
+
+template <int NT, bool FUSED>
+__global__ void __launch_bounds__((FUSED ? kFusedWarps : kBatchedWarps) * 32, FUSED ? 2 : 1) tl1_mma_kernel(const GemvLaunch L) {
+    constexpr int kGemvWarps = FUSED ? kFusedWarps : kBatchedWarps;
+    constexpr int kGemvThreads = kGemvWarps * 32;
+    using Lay = GemvSmem<NT, FUSED>;
+    constexpr int SL = Lay::SL;
     const tenzo_tl1_gemv_args& a = L.a;
     extern __shared__ __align__(16) uint32_t smem[];
-    // smem: act_e[tiles*16] | act_o[tiles*16] | red[128] | fscratch[32] | flag[4] | x[K]
-    uint32_t* s_ae = smem;
-    uint32_t* s_ao = smem + L.tiles * 16;
-    int* s_red = reinterpret_cast<int*>(smem + 2 * L.tiles * 16);
-    float* s_f = reinterpret_cast<float*>(s_red + 128);
-    int* s_flag = reinterpret_cast<int*>(s_f + 32);
-    float* s_x = reinterpret_cast<float*>(s_flag + 4);
+    int* s_d = reinterpret_cast<int*>(smem);                 // [rows_cta][SL] scaled accumulators
+    int* s_sa4 = s_d + 128 * SL;                             // [SL] 4 * sum(a) over this CTA's columns
+    float* s_inv = reinterpret_cast<float*>(s_sa4 + SL);     // [SL] m/31 per sequence
+    float* s_f = s_inv + SL;                                 // [32] reduction scratch
+    uint64_t* s_bar = reinterpret_cast<uint64_t*>(smem + ((128 * SL + 2 * SL + 32 + 1) & ~1));   // [2][kChunks]
+    uint32_t* s_b = smem + Lay::head_words();                // [sets][SL][4 t][2] packed activations
 
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int unit = blockIdx.x / L.ksplit, split = blockIdx.x % L.ksplit, seq = blockIdx.y;
+    TZ_TRACE_DECL;
+    TZ_STAMP(0);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t4 = lane & 3;
+    const int unit = blockIdx.x / L.ksplit, split = blockIdx.x % L.ksplit, seq0 = blockIdx.y * SL;
     const bool glu = a.epilogue == TENZO_EPI_RELU2_GLU;
     const int nb_cta = glu ? 2 : 1;                 // row blocks handled by this CTA
     const int wb = kGemvWarps / nb_cta;             // warps per row block
     const int my_blk = glu ? (warp & 1) : 0;        // which of the CTA's row blocks this warp feeds
     const int wi = glu ? (warp >> 1) : warp;        // index among the warps of that row block
-    const int block = glu ? (my_blk ? unit + L.units : unit) : unit;
     const int kh = a.K >> 1;                        // column pairs
+    cg::cluster_group cluster = cg::this_cluster();
 
-    // K range of this CTA in tiles, and this warp's tiles: t_begin + wi, + wb, ...
-    const int t_begin = (int)(((long long)L.tiles * split) / L.ksplit);
-    const int t_end = (int)(((long long)L.tiles * (split + 1)) / L.ksplit);
-    const int my_tiles = (t_end - t_begin - wi + wb - 1) / wb;   // may be <= 0
+    // K range of this CTA in sets of 16 column pairs (512 weight bytes per row block per set)
+    const int s_begin = (int)(((long long)L.nsets * split) / L.ksplit);
+    const int s_end = (int)(((long long)L.nsets * (split + 1)) / L.ksplit);
+    const int n_cta_sets = s_end - s_begin;
+    const int my_sets = (n_cta_sets - wi + wb - 1) / wb;   // this warp takes sets wi, wi+wb, ... of the range
+    uint32_t* s_wt = s_b + n_cta_sets * SL * 8;              // [nb_cta][n_cta_sets][128 words] weights as in memory
+    float* s_x = reinterpret_cast<float*>(s_wt + nb_cta * n_cta_sets * 128);   // fused only: x[K]
+    const int sets_per_chunk = (n_cta_sets + kChunks - 1) / kChunks;
 
-    const uint8_t* wblk = a.w + (size_t)block * kh * 32;
-    uint4 r[kUnroll][4];
-    auto load_tiles = [&](int first) {
+    // ---- weights: bulk-copy this CTA's slice of each row block into shared memory ----------------
+    // They do not depend on the previous kernel, so they are requested before anything else.
+    const unsigned range_bytes = (unsigned)(min(s_end * 512, kh * 32) - s_begin * 512);
+    if (tid == 0) {
+        for (int i = 0; i < nb_cta * kChunks; ++i) mbar_init(&s_bar[i], 1);
+        mbar_init_fence();
+        for (int bk = 0; bk < nb_cta; ++bk) {
+            const int block = bk ? unit + L.units : unit;
+            const uint8_t* src = a.w + (size_t)block * kh * 32 + (size_t)s_begin * 512;
+            for (int c = 0; c < kChunks; ++c) {
+                const unsigned off = (unsigned)c * sets_per_chunk * 512;
+                const unsigned bytes = off < range_bytes ? min((unsigned)sets_per_chunk * 512, range_bytes - off) : 0u;
+                mbar_expect_tx(&s_bar[bk * kChunks + c], bytes);   // zero bytes completes the phase at once
+                if (bytes)
+                    bulk_g2s(reinterpret_cast<uint8_t*>(s_wt + bk * n_cta_sets * 128) + off, src + off, bytes, &s_bar[bk * kChunks + c]);
+            }
+        }
+    }
+    l2_prefetch_slice(a.prefetch, a.prefetch_bytes);
+
+    const int rows_cta = nb_cta * 64;
+    for (int i = tid; i < rows_cta * SL; i += kGemvThreads) s_d[i] = 0;
+    for (int i = tid; i < SL; i += kGemvThreads) s_sa4[i] = 0;
+    constexpr int kWRegs = 16;                      // norm weights held in registers while waiting (K <= 16*threads)
+    float wreg[kWRegs];
+    const bool has_w = FUSED && a.do_norm && a.norm_w;
+    const bool w_in_regs = has_w && a.K <= kWRegs * kGemvThreads;
+    if (w_in_regs) {
 #pragma unroll
-        for (int u = 0; u < kUnroll; ++u) {
-            const int t = t_begin + wi + (first + u) * wb;
+        for (int r = 0; r < kWRegs; ++r) {
+            const int i = tid + r * kGemvThreads;
+            wreg[r] = i < a.K ? __ldg(a.norm_w + i) : 0.0f;   // model constant: no need to wait for the previous kernel
+        }
+    }
+    if (L.ksplit > 1) {
+        __syncthreads();
+        cluster.barrier_arrive();                   // "my s_d is zeroed": peers may add into it after their wait
+    }
+
+    TZ_STAMP(1);
+    if (a.use_pdl) pdl_wait();
+    TZ_STAMP(2);
+
+    float resid_v = 0.0f;                           // batch 1: fetched now so the epilogue does not wait on it
+    if (FUSED && a.epilogue == TENZO_EPI_RESIDUAL && split == 0 && tid < 64)
+        resid_v = __ldcg(a.resid + (size_t)seq0 * a.out_stride + unit * 64 + tid);
+
+    if (FUSED) {
+        // ---- RMSNorm + absmax(31) quantiser, recomputed identically by every CTA --------------
+        const float* x = a.x + (size_t)seq0 * a.x_stride;
+        const bool vec = ((a.K & 3) == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+        if (vec) {
+            for (int i = tid; i < (a.K >> 2); i += kGemvThreads)
+                reinterpret_cast<float4*>(s_x)[i] = __ldcg(reinterpret_cast<const float4*>(x) + i);
+        } else {
+            for (int i = tid; i < a.K; i += kGemvThreads) s_x[i] = __ldcg(x + i);
+        }
+        __syncthreads();
+        float m = 0.0f;
+        if (a.do_norm) {
+            const float ss = sumsq_reference_order(s_x, a.K, s_f);
+            const float inv_rms = rms_inv(ss, a.K, a.eps);
+            if (w_in_regs) {
+#pragma unroll
+                for (int r = 0; r < kWRegs; ++r) {
+                    const int i = tid + r * kGemvThreads;
+                    if (i < a.K) {
+                        const float y = s_x[i] * inv_rms * wreg[r];   // x * inv_rms * w, left to right (:158)
+                        s_x[i] = y;
+                        m = fmaxf(m, fabsf(y));
+                    }
+                }
+            } else {
+                for (int i = tid; i < a.K; i += kGemvThreads) {
+                    const float y = rms_apply(s_x[i], inv_rms, has_w ? a.norm_w : nullptr, i);
+                    s_x[i] = y;
+                    m = fmaxf(m, fabsf(y));
+                }
+            }
+        } else {
+            for (int i = tid; i < a.K; i += kGemvThreads) m = fmaxf(m, fabsf(s_x[i]));
+        }
+        m = fmaxf(block_max(m, s_f), 1e-6f);        // TenzoEngine.cpp:28-32
+        const float to_q = 31.0f / m;               // :34
+        if (tid == 0) s_inv[0] = m / 31.0f;         // :35
+        // pack only this CTA's columns: one 32-bit fragment word per (set, t, even/odd)
+        int sa = 0;
+        for (int wd = tid; wd < n_cta_sets * 8; wd += kGemvThreads) {
+            const int s = s_begin + (wd >> 3), tt = (wd >> 1) & 3, odd = wd & 1;
+            uint32_t word = 0;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                const int g = t * kTileGroups + 16 * i + (lane >> 1);
-                if (first + u < my_tiles && g < kh)
-                    r[u][i] = ld_stream_u4(wblk + (size_t)g * 32 + (lane & 1) * 16);
-                else
-                    r[u][i] = make_uint4(0, 0, 0, 0);
+                const int col = 2 * (16 * s + 4 * i + tt) + odd;
+                const int q = col < a.K ? (int)roundf(s_x[col] * to_q) : 0;   // :41-42, half away from zero
+                sa += q;
+                word |= (uint32_t)(uint8_t)(int8_t)(odd ? q : 4 * q) << (8 * i);
             }
+            s_b[wd] = word;
         }
-    };
-    // Weights do not depend on the previous kernel: get them moving before anything else.
-    load_tiles(0);
-
-    if (tid < 128) s_red[tid] = 0;
-    for (int i = tid; i < 2 * L.tiles * 16; i += kGemvThreads) smem[i] = 0;   // zero pad ragged K
-
-    if (a.use_pdl) pdl_wait();
-
-    // ---- prologue: RMSNorm + absmax(31) quantiser, recomputed identically by every CTA ----------
-    // x is staged in shared memory once; the normalised value replaces it in place.
-    const float* x = a.x + (size_t)seq * a.x_stride;
-    for (int i = tid; i < a.K; i += kGemvThreads) s_x[i] = __ldcg(x + i);
-    float m = 0.0f;
-    if (a.do_norm) {
-        __syncthreads();
-        const float ss = sumsq_reference_order(s_x, a.K, s_f);
-        const float inv_rms = rms_inv(ss, a.K, a.eps);
-        for (int i = tid; i < a.K; i += kGemvThreads) {   // same thread wrote s_x[i]
-            const float y = rms_apply(s_x[i], inv_rms, a.norm_w, i);
-            s_x[i] = y;
-            m = fmaxf(m, fabsf(y));
+        sa = warp_sum_i(sa);
+        if (lane == 0 && sa) atomicAdd(&s_sa4[0], 4 * sa);
+        if ((a.a_out || a.inv_out) && blockIdx.x == 0) {                      // parity-check outputs
+            for (int i = tid; i < a.K; i += kGemvThreads)
+                if (a.a_out) a.a_out[(size_t)seq0 * a.K + i] = (int8_t)(int)roundf(s_x[i] * to_q);
+            if (a.inv_out && tid == 0) a.inv_out[seq0] = m / 31.0f;
         }
     } else {
-        for (int i = tid; i < a.K; i += kGemvThreads) m = fmaxf(m, fabsf(s_x[i]));
-    }
-    m = fmaxf(block_max(m, s_f), 1e-6f);            // TenzoEngine.cpp:28-32 (barriers also cover the zero fill)
-    const float to_q = 31.0f / m;                   // :34
-    const float inv_act = m / 31.0f;                // :35
-    {
-        uint8_t* be = reinterpret_cast<uint8_t*>(s_ae);
-        uint8_t* bo = reinterpret_cast<uint8_t*>(s_ao);
-        for (int i = tid; i < a.K; i += kGemvThreads) {
-            const int q = (int)roundf(s_x[i] * to_q);   // :41-42, half away from zero
-            const int g = i >> 1, t = g >> 6, within = g & 63;
-            const int pos = ((t * 16 + (within & 15)) << 2) + (within >> 4);
-            if (i & 1) bo[pos] = (uint8_t)(int8_t)q;
-            else       be[pos] = (uint8_t)(int8_t)(4 * q);
-            if (a.a_out && blockIdx.x == 0) a.a_out[(size_t)seq * a.K + i] = (int8_t)q;
+        // ---- stage this CTA's K range of the pre-quantised activations of SL sequences -----------
+        for (int idx = tid; idx < n_cta_sets * SL * 2; idx += kGemvThreads) {
+            const int half = idx & 1, n = (idx >> 1) % SL, sl = (idx >> 1) / SL;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (seq0 + n < a.batch)
+                v = __ldcg(reinterpret_cast<const uint4*>(L.act_words + ((size_t)(seq0 + n) * L.nsets + s_begin + sl) * 8) + half);
+            reinterpret_cast<uint4*>(s_b + ((size_t)sl * SL + n) * 8)[half] = v;
+            int sa4 = dp4a_ss(0x01010101u, v.x, 0);     // even-column words already carry the factor 4
+            sa4 = dp4a_ss(0x04040404u, v.y, sa4);
+            sa4 = dp4a_ss(0x01010101u, v.z, sa4);
+            sa4 = dp4a_ss(0x04040404u, v.w, sa4);
+            if (sa4) atomicAdd(&s_sa4[n], sa4);
         }
-        if (a.inv_out && blockIdx.x == 0 && tid == 0) a.inv_out[seq] = inv_act;
+        for (int n = tid; n < SL; n += kGemvThreads) s_inv[n] = seq0 + n < a.batch ? __ldcg(L.act_inv + seq0 + n) : 0.0f;
     }
     __syncthreads();
+    TZ_STAMP(3);
     if (a.use_pdl) pdl_launch_dependents();
 
-    // ---- main loop ---------------------------------------------------------------------------
-    int lo[16], hi[16], sa4 = 0;
+    // ---- main loop: weights from shared memory, four MMAs per set per 8 sequences -----------------
+    int acc[NT][4][4];
 #pragma unroll
-    for (int c = 0; c < 16; ++c) { lo[c] = 0; hi[c] = 0; }
-    for (int first = 0; first < my_tiles; first += kUnroll) {
-        if (first > 0) load_tiles(first);
+    for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-        for (int u = 0; u < kUnroll; ++u) {
-            if (first + u < my_tiles) {
-                const int t = t_begin + wi + (first + u) * wb;
-                consume_tile(r[u], s_ae[t * 16 + (lane >> 1)], s_ao[t * 16 + (lane >> 1)], lo, hi, sa4);
-            }
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[nt][j][e] = 0;
+    // Per-lane cursors advance by one stride per set: no index arithmetic in the loop. Words past the
+    // copied range (ragged K) are stale shared memory, but the activation bytes they meet are zero.
+    const uint32_t* wt = s_wt + my_blk * n_cta_sets * 128 + (16 * wi + t4) * 8 + g;      // column pair 16*sl + 4*i + t4, byte 4g
+    const uint32_t* bp = s_b + ((size_t)wi * SL + g) * 8 + t4 * 2;                        // B fragment words of sequence g
+    const int wt_step = 16 * wb * 8, bp_step = wb * SL * 8;
+    int next_wait = 0, chunk = 0;                                                         // first set of the next chunk to wait for
+    bool timed_out = false;
+    for (int u = 0, sl = wi; u < my_sets; ++u, sl += wb, wt += wt_step, bp += bp_step) {
+        while (sl >= next_wait) {
+            // one lane polls (operations on one mbarrier serialise); the warp barrier passes the
+            // acquired visibility on to the other lanes
+            if (lane == 0 && !mbar_wait_bounded(&s_bar[my_blk * kChunks + chunk], 0)) timed_out = true;
+            __syncwarp();
+            ++chunk;
+            next_wait += sets_per_chunk;
+        }
+        const uint32_t W0 = wt[0], W1 = wt[32], W2 = wt[64], W3 = wt[96];
+        // 4x4 byte transpose: T[j] = (W0.j, W1.j, W2.j, W3.j) = row pair 4g+j at this lane's four column pairs
+        const uint32_t p0 = prmt(W0, W1, 0x5140u), p1 = prmt(W2, W3, 0x5140u);
+        const uint32_t p2 = prmt(W0, W1, 0x7362u), p3 = prmt(W2, W3, 0x7362u);
+        const uint32_t T[4] = {prmt(p0, p1, 0x5410u), prmt(p0, p1, 0x7632u), prmt(p2, p3, 0x5410u), prmt(p2, p3, 0x7632u)};
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            uint2 b = make_uint2(0, 0);
+            if (nt * 8 + g < SL) b = *reinterpret_cast<const uint2*>(bp + nt * 64);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                mma_u8s8(acc[nt][j], T[j] & 0x03030303u, T[j] & 0x30303030u, T[j] & 0x0C0C0C0Cu, T[j] & 0xC0C0C0C0u, b.x, b.y);
         }
     }
+    if (timed_out) atomicExch(&g_tl1_timeouts, 1);
+    TZ_STAMP(4);
 
-    // ---- reduce across the 16 lanes of equal parity: halving butterfly -------------------------
-    int v[32];
+    // ---- warps of a row block meet in shared memory ---------------------------------------------
+    if (my_sets > 0) {
 #pragma unroll
-    for (int c = 0; c < 16; ++c) { v[c] = lo[c]; v[16 + c] = hi[c]; }
+        for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-    for (int h = 16; h >= 2; h >>= 1) {             // xor masks 16, 8, 4, 2
-        const bool up = (lane & h) != 0;
+            for (int e = 0; e < 2; ++e) {
+                const int n = nt * 8 + 2 * t4 + e;          // sequence (column of D) held in c[e] and c[2+e]
+                if (n < SL) {
 #pragma unroll
-        for (int i = 0; i < h; ++i) {
-            const int keep = up ? v[i + h] : v[i];
-            const int send = up ? v[i] : v[i + h];
-            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, h);
-        }
-    }
-#pragma unroll
-    for (int msk = 2; msk <= 16; msk <<= 1) sa4 += __shfl_xor_sync(0xffffffffu, sa4, msk);
-    const int sum_a = sa4 >> 2;                     // sum of a over this warp's columns (exact)
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        const int o = i + (lane & 30);              // index in the original lo|hi array
-        const int row = (o & 15) + 16 * (lane & 1) + 32 * (o >> 4);
-        const int val = (o < 16 ? (v[i] >> 2) : (v[i] >> 6)) - sum_a;
-        if (my_tiles > 0) atomicAdd(&s_red[my_blk * 64 + row], val);
+                    for (int j = 0; j < 4; ++j) {
+                        atomicAdd(&s_d[(my_blk * 64 + 4 * g + j) * SL + n], acc[nt][j][e]);            // x4
+                        atomicAdd(&s_d[(my_blk * 64 + 32 + 4 * g + j) * SL + n], acc[nt][j][2 + e]);   // x64
+                    }
+                }
+            }
     }
     __syncthreads();
 
-    // ---- cross-CTA split-K meeting point ------------------------------------------------------
-    const int rows_cta = nb_cta * 64;
-    int acc = tid < rows_cta ? s_red[tid] : 0;
+    // ---- split-K meeting point: the cluster leader's shared memory -----------------------------
     if (L.ksplit > 1) {
-        const size_t slot = (size_t)seq * L.units + unit;
-        int* gacc = a.splitk_acc + slot * rows_cta;
-        if (tid < rows_cta) atomicAdd(&gacc[tid], acc);
-        __threadfence();
-        __syncthreads();
-        if (tid == 0) *s_flag = (atomicAdd(&a.splitk_cnt[slot], 1u) == (unsigned)(L.ksplit - 1));
-        __syncthreads();
-        if (!*s_flag) return;
-        __threadfence();
-        if (tid < rows_cta) acc = atomicExch(&gacc[tid], 0);   // take the total and leave zero behind
-        if (tid == 0) a.splitk_cnt[slot] = 0;
+        cluster.barrier_wait();                     // every peer has zeroed its s_d (arrive above)
+        if (split != 0) {
+            int* remote = cluster.map_shared_rank(s_d, 0);
+            for (int i = tid; i < rows_cta * SL; i += kGemvThreads) {
+                const int v = s_d[i];
+                if (v) atomicAdd(remote + i, v);
+            }
+            for (int n = tid; n < SL; n += kGemvThreads) atomicAdd(remote + 128 * SL + n, s_sa4[n]);
+        }
+        cluster.sync();                             // all remote adds have landed in the leader
+        if (split != 0) return;
     }
 
+    TZ_STAMP(5);
     // ---- epilogue -----------------------------------------------------------------------------
-    if (tid < rows_cta) {
-        const int blk = glu ? (tid < 64 ? unit : unit + L.units) : unit;
-        const int row = blk * 64 + (tid & 63);
-        if (a.acc_out) a.acc_out[(size_t)seq * a.n_blocks * 64 + row] = acc;
-        const float val = (float)acc * (inv_act * seg_scale_for(a, blk));   // :1554, :118
+    for (int idx = tid; idx < 64 * SL; idx += kGemvThreads) {
+        const int r = idx / SL, n = idx % SL, seq = seq0 + n;
+        if (seq >= a.batch) continue;
+        const int sum_a = s_sa4[n] >> 2;
+        const float inv_act = s_inv[n];
+        float v[2];
+#pragma unroll
+        for (int bk = 0; bk < 2; ++bk) {
+            if (bk >= nb_cta) break;
+            const int blk = bk ? unit + L.units : unit;
+            const int raw = s_d[(bk * 64 + r) * SL + n];
+            const int accv = (r < 32 ? (raw >> 2) : (raw >> 6)) - sum_a;
+            if (a.acc_out) a.acc_out[(size_t)seq * a.n_blocks * 64 + blk * 64 + r] = accv;
+            v[bk] = (float)accv * (inv_act * seg_scale_for(a, blk));   // :1554, :118
+        }
+        const size_t o = (size_t)seq * a.out_stride + unit * 64 + r;
         if (a.epilogue == TENZO_EPI_STORE) {
-            a.out[(size_t)seq * a.out_stride + row] = val;
+            a.out[o] = v[0];
         } else if (a.epilogue == TENZO_EPI_RESIDUAL) {
-            a.out[(size_t)seq * a.out_stride + row] = __ldcg(a.resid + (size_t)seq * a.out_stride + row) + val;  // :1590
+            a.out[o] = (FUSED ? resid_v : __ldcg(a.resid + o)) + v[0];   // :1590
         } else {
-            reinterpret_cast<float*>(s_red)[tid] = val;
+            const float rl = fmaxf(0.0f, v[0]);
+            a.out[o] = (rl * rl) * v[1];                                 // :1618-1619
         }
     }
-    if (glu) {
-        __syncthreads();
-        if (tid < 64) {
-            const float g = reinterpret_cast<float*>(s_red)[tid], u = reinterpret_cast<float*>(s_red)[64 + tid];
-            const float rl = fmaxf(0.0f, g);
-            a.out[(size_t)seq * a.out_stride + unit * 64 + tid] = (rl * rl) * u;   // :1618-1619
-        }
-    }
+    TZ_STAMP(6);
+    TZ_TRACE_FLUSH;
 }
 
-static int pick_ksplit(int n_blocks, int K, int epilogue) {
-    const int tiles = ((K >> 1) + kTileGroups - 1) / kTileGroups;
+// Cluster size along K: 1, 2, 4 or 8. Enough CTAs to put one on every SM, few enough sets per warp
+// that a warp's loads are all in flight at once, a K range whose packed activations fit in shared
+// memory, never more CTAs than sets.
+static int pick_ksplit(int n_blocks, int K, int epilogue, int batch) {
+    const int nsets = ((K >> 1) + 15) / 16;
     const int nb_cta = epilogue == TENZO_EPI_RELU2_GLU ? 2 : 1;
-    const int units = n_blocks / nb_cta, wb = kGemvWarps / nb_cta;
-    int for_regs = (tiles + wb * kUnroll - 1) / (wb * kUnroll);   // at most kUnroll tiles per warp
-    int for_fill = (148 + units - 1) / units;                     // at least one CTA per SM
-    int ks = for_regs > for_fill ? for_regs : for_fill;
-    int cap = tiles / wb > 0 ? tiles / wb : 1;                    // keep >= one tile per warp
-    if (ks > cap) ks = cap;
-    if (ks < 1) ks = 1;
-    if (ks > 16) ks = 16;
+    const int units = n_blocks / nb_cta;
+    int ks = 1;
+    if (batch == 1) {
+        // one CTA per row block, two resident per SM: weights (512 B per set per row block) + x must fit ~100 KB
+        auto bytes = [&](int k) { return (size_t)((nsets + k - 1) / k + 1) * (512 * nb_cta + 32) + (size_t)K * 4 + 2048; };
+        while (ks < 8 && ks * 2 <= nsets && (units * ks < 32 || bytes(ks) > 100 * 1024)) ks *= 2;
+    } else {
+        const int sl = batch <= 8 ? 8 : 32, seq_tiles = (batch + sl - 1) / sl;
+        auto bytes = [&](int k) { return (size_t)((nsets + k - 1) / k + 1) * (512 * nb_cta + 32 * sl) + (size_t)sl * 520 + 1024; };
+        while (ks < 8 && ks * 2 <= nsets && (units * ks * seq_tiles < 148 || bytes(ks) > 200 * 1024)) ks *= 2;
+    }
     return ks;
+}
+
+// act_quant_kernel lives in norm_quant.cu
+cudaError_t launch_act_quant(const float* x, const float* norm_w, int do_norm, float eps, int K, int batch, int x_stride,
+                             uint32_t* words, float* inv, int8_t* a_out, int use_pdl, cudaStream_t st);
+
+template <int NT, bool FUSED>
+static cudaError_t launch_gemv(const GemvLaunch& L, cudaStream_t st) {
+    using Lay = GemvSmem<NT, FUSED>;
+    const tenzo_tl1_gemv_args& a = L.a;
+    const int sets_per_cta = (L.nsets + L.ksplit - 1) / L.ksplit + 1;
+    const size_t smem = Lay::bytes(sets_per_cta, a.K, a.epilogue == TENZO_EPI_RELU2_GLU ? 2 : 1);
+    if (smem > 220 * 1024) return cudaErrorInvalidValue;
+    if (smem > 48 * 1024) {
+        cudaError_t ea = cudaFuncSetAttribute(tl1_mma_kernel<NT, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (ea != cudaSuccess) return ea;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(L.units * L.ksplit), (unsigned)((a.batch + Lay::SL - 1) / Lay::SL), 1);
+    cfg.blockDim = dim3((FUSED ? kFusedWarps : kBatchedWarps) * 32, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    int n_attr = 0;
+    if (L.ksplit > 1) {
+        attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+        attr[n_attr].val.clusterDim.x = (unsigned)L.ksplit;
+        attr[n_attr].val.clusterDim.y = 1;
+        attr[n_attr].val.clusterDim.z = 1;
+        ++n_attr;
+    }
+    if (a.use_pdl) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        ++n_attr;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n_attr;
+    return cudaLaunchKernelEx(&cfg, tl1_mma_kernel<NT, FUSED>, L);
 }
 
 }  // namespace tz
 
 extern "C" int tenzo_cuda_tl1_gemv_ksplit(int n_blocks, int K, int epilogue) {
     if (n_blocks <= 0 || K <= 0) return 1;
-    return tz::pick_ksplit(n_blocks, K, epilogue);
+    return tz::pick_ksplit(n_blocks, K, epilogue, 1);
+}
+
+extern "C" int tenzo_cuda_tl1_gemv_take_timeouts(void) {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, tz::g_tl1_timeouts, sizeof v) != cudaSuccess) return -1;
+    if (v) cudaMemcpyToSymbol(tz::g_tl1_timeouts, &zero, sizeof zero);
+    return v;
+}
+
+extern "C" size_t tenzo_cuda_tl1_gemv_workspace_bytes(int batch, int K) {
+    if (batch <= 1 || K <= 0) return 0;
+    const size_t nsets = ((size_t)(K >> 1) + 15) / 16;
+    return (size_t)batch * nsets * 32 + (size_t)batch * sizeof(float) + 64;
 }
 
 extern "C" int tenzo_cuda_tl1_gemv(const tenzo_tl1_gemv_args* args, void* stream) {
@@ -269,34 +461,38 @@ extern "C" int tenzo_cuda_tl1_gemv(const tenzo_tl1_gemv_args* args, void* stream
     if (!args || !args->x || !args->w || !args->out) return -1;
     const tenzo_tl1_gemv_args& a = *args;
     if (a.n_blocks <= 0 || a.K <= 0 || (a.K & 1) || a.batch <= 0) return -1;
-    if ((reinterpret_cast<uintptr_t>(a.w) & 15) != 0) return -1;
+    if ((reinterpret_cast<uintptr_t>(a.w) & 15) != 0) return -1;   /* bulk copies start on 16-byte boundaries */
     if (a.epilogue < 0 || a.epilogue > 2) return -1;
     if (a.epilogue == TENZO_EPI_RESIDUAL && !a.resid) return -1;
     if (a.epilogue == TENZO_EPI_RELU2_GLU && (a.n_blocks & 1)) return -1;
     if (a.K > 16384) return -5;   /* same bound as the reference engine's scratch vectors (:1227) */
+    if (a.batch > 1 && (!a.workspace || (reinterpret_cast<uintptr_t>(a.workspace) & 15) != 0)) return -1;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
 
     GemvLaunch L;
     L.a = a;
-    L.tiles = ((a.K >> 1) + kTileGroups - 1) / kTileGroups;
+    L.nsets = ((a.K >> 1) + 15) / 16;
     L.units = a.epilogue == TENZO_EPI_RELU2_GLU ? a.n_blocks / 2 : a.n_blocks;
-    L.ksplit = pick_ksplit(a.n_blocks, a.K, a.epilogue);
-    if (L.ksplit > 1 && (!a.splitk_acc || !a.splitk_cnt)) return -1;
-
-    const size_t smem = (size_t)(2 * L.tiles * 16 + 128 + 32 + 4 + a.K) * sizeof(uint32_t);
-    if (smem > 48 * 1024) {   // staging for K > ~11k columns exceeds the default dynamic limit
-        cudaError_t ea = cudaFuncSetAttribute(tl1_gemv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-        if (ea != cudaSuccess) return (int)ea;
+    L.ksplit = pick_ksplit(a.n_blocks, a.K, a.epilogue, a.batch);
+    L.act_words = nullptr;
+    L.act_inv = nullptr;
+    cudaError_t e;
+    if (a.batch == 1) {
+        e = launch_gemv<1, true>(L, st);
+    } else {
+        uint32_t* words = static_cast<uint32_t*>(a.workspace);
+        float* inv = reinterpret_cast<float*>(words + (size_t)a.batch * L.nsets * 8);
+        e = launch_act_quant(a.x, a.norm_w, a.do_norm, a.eps, a.K, a.batch, a.x_stride, words, inv, a.a_out, a.use_pdl, st);
+        if (e != cudaSuccess) return (int)e;
+        if (a.inv_out) {
+            e = cudaMemcpyAsync(a.inv_out, inv, (size_t)a.batch * sizeof(float), cudaMemcpyDeviceToDevice, st);
+            if (e != cudaSuccess) return (int)e;
+        }
+        L.act_words = words;
+        L.act_inv = inv;
+        L.a.a_out = nullptr;
+        L.a.inv_out = nullptr;
+        e = a.batch <= 8 ? launch_gemv<1, false>(L, st) : launch_gemv<4, false>(L, st);
     }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(L.units * L.ksplit), (unsigned)a.batch, 1);
-    cfg.blockDim = dim3(kGemvThreads, 1, 1);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = static_cast<cudaStream_t>(stream);
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = a.use_pdl ? 1 : 0;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, tl1_gemv_kernel, L);
     return e == cudaSuccess ? 0 : (int)e;
 }

@@ -31,17 +31,8 @@ def _ok(rc: int, what: str):
         raise RuntimeError(f"{what} failed: rc={rc}" + (f" ({torch.cuda.get_device_name()})" if rc > 0 else " (bad arguments)"))
 
 
-class SplitKScratch:
-    """Zero-initialised int32 meeting buffer for split-K GEMV launches (left zero by every launch)."""
-
-    def __init__(self, batch: int, max_blocks: int, device="cuda"):
-        self.acc = torch.zeros(batch * max_blocks * 64, dtype=torch.int32, device=device)
-        self.cnt = torch.zeros(batch * max_blocks, dtype=torch.int32, device=device)
-
-
 def tl1_gemv(x: torch.Tensor, w: torch.Tensor, n_blocks: int, K: int, scales, seg_ends=None, *, epilogue=EPI_STORE,
-             resid=None, norm_w=None, do_norm=False, eps=1e-5, want_acc=False, want_act=False, scratch=None,
-             use_pdl=False, out=None):
+             resid=None, norm_w=None, do_norm=False, eps=1e-5, want_acc=False, want_act=False, use_pdl=False, out=None, prefetch=None):
     """x [batch, K] fp32, w TL1-packed uint8. Returns dict(out=..., acc=..., a=..., inv=...)."""
     lib = load_library()
     batch = x.shape[0]
@@ -51,8 +42,6 @@ def tl1_gemv(x: torch.Tensor, w: torch.Tensor, n_blocks: int, K: int, scales, se
     acc = torch.empty(batch, n_blocks * 64, dtype=torch.int32, device=x.device) if want_acc else None
     a8 = torch.empty(batch, K, dtype=torch.int8, device=x.device) if want_act else None
     inv = torch.empty(batch, dtype=torch.float32, device=x.device) if want_act else None
-    if scratch is None:
-        scratch = SplitKScratch(batch, n_blocks, x.device)
     scales = list(scales) + [0.0] * (3 - len(scales))
     seg_ends = list(seg_ends) if seg_ends is not None else [n_blocks] * 3
     seg_ends = seg_ends + [n_blocks] * (3 - len(seg_ends))
@@ -64,7 +53,12 @@ def tl1_gemv(x: torch.Tensor, w: torch.Tensor, n_blocks: int, K: int, scales, se
     g.epilogue, g.resid, g.out = epilogue, _ptr(resid), _ptr(out)
     g.acc_out, g.a_out, g.inv_out = _ptr(acc), _ptr(a8), _ptr(inv)
     g.batch, g.x_stride, g.out_stride = batch, x.stride(0), out.stride(0)
-    g.splitk_acc, g.splitk_cnt, g.use_pdl = _ptr(scratch.acc), _ptr(scratch.cnt), int(use_pdl)
+    ws = None
+    if batch > 1:
+        ws = torch.empty(lib.tenzo_cuda_tl1_gemv_workspace_bytes(batch, K), dtype=torch.uint8, device=x.device)
+    g.workspace, g.use_pdl = _ptr(ws), int(use_pdl)
+    if prefetch is not None:
+        g.prefetch, g.prefetch_bytes = _ptr(prefetch), prefetch.numel() * prefetch.element_size()
     _ok(lib.tenzo_cuda_tl1_gemv(C.byref(g), _stream()), "tenzo_cuda_tl1_gemv")
     return dict(out=out, acc=acc, a=a8, inv=inv)
 
