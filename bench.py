@@ -288,6 +288,7 @@ def main():
     ap.add_argument("--batch", type=int, default=256)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--pdl", type=int, default=1)
+    ap.add_argument("--heads-per-cta", type=int, default=0)
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)

@@ -97,7 +97,7 @@ TENZO_API int tenzo_cuda_rmsnorm_quant(const float* x, const float* norm_w, int 
  * expressions so rotations are bit-identical); NULL skips RoPE. head_dim must be 128.
  * The kernel reproduces the reference's fp32 operation order (sequential sums over t, glibc expf
  * bits), so its output is bit-identical, not merely close. No scratch memory: score vectors live
- * in shared memory, which bounds max_len at 40960 keys. */
+ * in shared memory, which bounds max_len at 36864 keys. */
 typedef struct {
     const float* q;        /* [batch][q_stride]  n_q*128 used, pre-RoPE */
     const float* k;        /* [batch][kv_stride] n_kv*128 used, pre-RoPE new key */
@@ -113,10 +113,13 @@ typedef struct {
     int max_len;           /* upper bound on pos[s]+1 for this launch (sizes the grid) */
     int append;            /* 1: quantise and store the new k,v at pos (normal decode); 0: the
                               cache already holds pos[s]+1 keys, k/v are ignored */
+    int heads_per_cta;     /* 0 = choose automatically; 1, 2, 4 or 8 forces the query heads one CTA processes */
     int use_pdl;
 } tenzo_attention_args;
 
 TENZO_API int tenzo_cuda_attention_int8(const tenzo_attention_args* args, void* stream);
+/* As tenzo_cuda_tl1_gemv_take_timeouts, for the attention kernel's bounded waits on its V-chunk copies. */
+TENZO_API int tenzo_cuda_attention_take_timeouts(void);
 /* Query heads one CTA will process for this shape (1..n_q/n_kv); informational. */
 TENZO_API int tenzo_cuda_attention_heads_per_cta(int batch, int n_q, int n_kv, int max_len);
 

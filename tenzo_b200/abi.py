@@ -63,7 +63,7 @@ class AttentionArgs(C.Structure):
         ("pos", C.c_void_p), ("rope_cos", C.c_void_p), ("rope_sin", C.c_void_p),
         ("layer", C.c_int), ("n_q", C.c_int), ("n_kv", C.c_int), ("head_dim", C.c_int), ("max_seq", C.c_int),
         ("batch", C.c_int), ("max_len", C.c_int), ("append", C.c_int),
-        ("use_pdl", C.c_int),
+        ("heads_per_cta", C.c_int), ("use_pdl", C.c_int),
     ]
 
 
@@ -81,7 +81,7 @@ EXT_SYMBOLS = [
 ]
 KERNEL_SYMBOLS = [
     "tenzo_cuda_tl1_gemv", "tenzo_cuda_tl1_gemv_ksplit", "tenzo_cuda_tl1_gemv_workspace_bytes", "tenzo_cuda_tl1_gemv_take_timeouts", "tenzo_cuda_rmsnorm_quant", "tenzo_cuda_attention_int8",
-    "tenzo_cuda_attention_heads_per_cta", "tenzo_cuda_lm_head_i8", "tenzo_cuda_lm_head_scratch_bytes",
+    "tenzo_cuda_attention_heads_per_cta", "tenzo_cuda_attention_take_timeouts", "tenzo_cuda_lm_head_i8", "tenzo_cuda_lm_head_scratch_bytes",
     "tenzo_cuda_embedding_i8", "tenzo_cuda_tl1_pack_rows2bit", "tenzo_cuda_lm_head_i8_static",
     "tenzo_cuda_lm_head_static_max_batch",
 ]
@@ -148,6 +148,7 @@ def declare_kernel_abi(L):
     L.tenzo_cuda_rmsnorm_quant.restype = i32
     L.tenzo_cuda_rmsnorm_quant.argtypes = [vp, vp, i32, f32, i32, i32, i32, i32, vp, vp, vp, vp]
     L.tenzo_cuda_attention_int8.restype, L.tenzo_cuda_attention_int8.argtypes = i32, [C.POINTER(AttentionArgs), vp]
+    L.tenzo_cuda_attention_take_timeouts.restype, L.tenzo_cuda_attention_take_timeouts.argtypes = i32, []
     L.tenzo_cuda_attention_heads_per_cta.restype, L.tenzo_cuda_attention_heads_per_cta.argtypes = i32, [i32, i32, i32, i32]
     L.tenzo_cuda_lm_head_i8.restype = i32
     L.tenzo_cuda_lm_head_i8.argtypes = [vp, vp, i32, f32, vp, vp, i32, i32, i32, i32, vp, vp, vp, vp, i32, vp]

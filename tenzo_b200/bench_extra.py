@@ -87,12 +87,12 @@ def run_attn(args):
     v = torch.randn(B, nkv * 128, generator=g, device="cuda")
     pos = torch.full((B,), T - 1, dtype=torch.int32, device="cuda")
     for _ in range(max(3, args.warmup)):
-        kernels.attention_int8(q, k, v, ck, cv, sk, sv, pos, layer=0, n_q=nq, n_kv=nkv, max_seq=T, max_len=T)
+        kernels.attention_int8(q, k, v, ck, cv, sk, sv, pos, layer=0, n_q=nq, n_kv=nkv, max_seq=T, max_len=T, heads_per_cta=args.heads_per_cta)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
     e0.record()
     for _ in range(args.steps):
-        kernels.attention_int8(q, k, v, ck, cv, sk, sv, pos, layer=0, n_q=nq, n_kv=nkv, max_seq=T, max_len=T)
+        kernels.attention_int8(q, k, v, ck, cv, sk, sv, pos, layer=0, n_q=nq, n_kv=nkv, max_seq=T, max_len=T, heads_per_cta=args.heads_per_cta)
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / args.steps

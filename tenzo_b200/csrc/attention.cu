@@ -24,10 +24,9 @@
 namespace tz {
 
 constexpr int kAttnThreads = 256;
-constexpr int kChunk = 256;          // keys staged in shared memory at a time
+constexpr int kChunk = 256;          // V rows per bulk copy (two in flight)
 constexpr int kHd = 128;             // head_dim (the reference hard-wires 16 x 8 lanes, :833-850)
-constexpr int kKRow = 144;           // padded smem row for K: 16-byte aligned, conflict-free 128-bit reads
-constexpr int kScoreSmemBytes = 160 * 1024;  // per-CTA budget for the score vectors [T][GH] (whole CTA stays under 227 KB)
+constexpr int kScoreSmemBytes = 144 * 1024;  // per-CTA budget for the score vectors [T][GH] (whole CTA stays under 227 KB)
 
 struct AttnLaunch {
     tenzo_attention_args a;
@@ -52,12 +51,17 @@ __device__ __forceinline__ void rope_pair(float x0, float x1, const float* cs, c
 
 template <int GH>
 struct AttnSmem {
+    // floats: s_q[GH*128] | s_new[256] | s_red[8*GH] | s_stat[2*GH+2]; then 16-byte aligned: s_new8[256 B] |
+    // mbarriers[2 x 8 B] | V double buffer [2][kChunk*128 B] | scores [T][GH] floats
     static constexpr int n_float = GH * kHd + 2 * kHd + 8 * GH + 2 * GH + 2;
     static constexpr int new8_off = (n_float * 4 + 15) & ~15;
-    static constexpr int stage_off = new8_off + 2 * kHd;
-    static constexpr int sc_off = stage_off + kChunk * kKRow;
+    static constexpr int bar_off = new8_off + 2 * kHd;
+    static constexpr int v_off = bar_off + 16;
+    static constexpr int sc_off = v_off + 2 * kChunk * kHd;
     static size_t bytes(int max_len) { return (size_t)sc_off + (size_t)max_len * GH * sizeof(float); }
 };
+
+__device__ int g_attn_timeouts = 0;   // set when a bounded wait on a V-chunk copy gave up
 
 template <int GH>
 __global__ void __launch_bounds__(kAttnThreads) attn_kernel(const AttnLaunch L) {
@@ -69,7 +73,8 @@ __global__ void __launch_bounds__(kAttnThreads) attn_kernel(const AttnLaunch L) 
     float* s_red = s_new + 2 * kHd;                                      // [8][GH] per-warp maxima
     float* s_stat = s_red + 8 * GH;                                      // [GH] max, [GH] 1/sum, [2] new-row scales
     int8_t* s_new8 = reinterpret_cast<int8_t*>(smem_raw + Lay::new8_off);   // [2][128] quantised new k, v
-    unsigned char* s_stage = smem_raw + Lay::stage_off;                  // [kChunk][kKRow] K rows, later [kChunk][128] V rows
+    uint64_t* s_bar = reinterpret_cast<uint64_t*>(smem_raw + Lay::bar_off); // [2] one per V buffer
+    unsigned char* s_v = smem_raw + Lay::v_off;                          // [2][kChunk][128] V rows as in memory
     float* s_sc = reinterpret_cast<float*>(smem_raw + Lay::sc_off);      // [T][GH] scores -> e_t -> weights
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -80,6 +85,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_kernel(const AttnLaunch L) 
     if (a.use_pdl) pdl_wait();
     const int pos = a.pos[seq];
     const int T = pos + 1;
+    const int n_chunks = (T + kChunk - 1) / kChunk;
 
     const size_t row_base = ((size_t)a.layer * a.n_kv + kvh) * a.max_seq;   // :509-510
     int8_t* ck = a.cache_k + (size_t)seq * a.seq_stride_kv + row_base * kHd;
@@ -88,6 +94,21 @@ __global__ void __launch_bounds__(kAttnThreads) attn_kernel(const AttnLaunch L) 
     float* sv = a.scale_v + (size_t)seq * a.seq_stride_sc + row_base;
     const float* cs = a.rope_cos ? a.rope_cos + (size_t)pos * (kHd / 2) : nullptr;
     const float* sn = a.rope_sin ? a.rope_sin + (size_t)pos * (kHd / 2) : nullptr;
+
+    // ---- V chunks travel by bulk copy into a double buffer; the first two leave now and overlap the
+    //      whole scoring phase. (Rows are contiguous in the cache, so a chunk is one copy.) -------------
+    auto issue_v = [&](int c) {
+        const int t0 = c * kChunk, nk = min(kChunk, T - t0);
+        mbar_expect_tx(&s_bar[c & 1], (unsigned)nk * kHd);
+        bulk_g2s(s_v + (size_t)(c & 1) * kChunk * kHd, cv + (size_t)t0 * kHd, (unsigned)nk * kHd, &s_bar[c & 1]);
+    };
+    if (tid == 0) {
+        mbar_init(&s_bar[0], 1);
+        mbar_init(&s_bar[1], 1);
+        mbar_init_fence();
+        issue_v(0);
+        if (n_chunks > 1) issue_v(1);
+    }
 
     // ---- RoPE on this CTA's query heads (pairs i, i+64; :459-480) ---------------------------------
     for (int idx = tid; idx < GH * (kHd / 2); idx += kAttnThreads) {
@@ -140,55 +161,57 @@ __global__ void __launch_bounds__(kAttnThreads) attn_kernel(const AttnLaunch L) 
     __syncthreads();
     if (a.use_pdl) pdl_launch_dependents();
 
-    // ---- scores (:678-694): one key per thread, all GH heads, the reference's eight FMA lanes ------
+    // ---- scores (:678-694): one key per thread straight from the cache (a row is 128 contiguous
+    //      bytes), the next key's row requested before the current one is used; all GH heads, the
+    //      reference's eight FMA lanes ------------------------------------------------------------------
     const float sm_scale = 1.0f / sqrtf((float)kHd);   // :660
     float tmax[GH];
 #pragma unroll
     for (int g = 0; g < GH; ++g) tmax[g] = -1e30f;     // :670
-    for (int t0 = 0; t0 < T; t0 += kChunk) {
-        const int nkeys = min(kChunk, T - t0);
-        for (int idx = tid; idx < nkeys * 8; idx += kAttnThreads) {
-            const int r = idx >> 3, c = idx & 7;
-            const bool is_new = a.append && (t0 + r == pos);
-            const uint4 v = is_new ? reinterpret_cast<const uint4*>(s_new8)[c] : ld_cg_u4(ck + (size_t)(t0 + r) * kHd + c * 16);
-            *reinterpret_cast<uint4*>(s_stage + r * kKRow + c * 16) = v;
-        }
-        __syncthreads();
-        if (tid < nkeys) {
-            float acc[GH][8];
+    auto load_row = [&](int t, uint4 (&r)[8]) {
+        const bool is_new = a.append && t == pos;
+        const uint4* src = is_new ? reinterpret_cast<const uint4*>(s_new8) : reinterpret_cast<const uint4*>(ck + (size_t)t * kHd);
 #pragma unroll
-            for (int g = 0; g < GH; ++g)
+        for (int c = 0; c < 8; ++c) r[c] = is_new ? src[c] : ld_cg_u4(src + c);
+    };
+    uint4 cur[8], nxt[8];
+    if (tid < T) load_row(tid, cur);
+    for (int t = tid; t < T; t += kAttnThreads) {
+        const bool more = t + kAttnThreads < T;
+        if (more) load_row(t + kAttnThreads, nxt);
+        float acc[GH][8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) acc[g][j] = 0.0f;
-            const unsigned char* krow = s_stage + tid * kKRow;
-#pragma unroll 2
-            for (int d = 0; d < kHd; d += 16) {
-                const uint4 kw = *reinterpret_cast<const uint4*>(krow + d);
-                const uint32_t w[4] = {kw.x ^ 0x80808080u, kw.y ^ 0x80808080u, kw.z ^ 0x80808080u, kw.w ^ 0x80808080u};
-                float kf[16];
+        for (int g = 0; g < GH; ++g)
 #pragma unroll
-                for (int e = 0; e < 16; ++e) kf[e] = s8_to_f(w[e >> 2], e & 3);
+            for (int j = 0; j < 8; ++j) acc[g][j] = 0.0f;
 #pragma unroll
-                for (int g = 0; g < GH; ++g) {
-                    const float4* q4 = reinterpret_cast<const float4*>(s_q + g * kHd + d);
-                    const float4 qa = q4[0], qb = q4[1], qc = q4[2], qd = q4[3];
-                    const float qv[16] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w,
-                                          qc.x, qc.y, qc.z, qc.w, qd.x, qd.y, qd.z, qd.w};
+        for (int c = 0; c < 8; ++c) {
+            const uint32_t w[4] = {cur[c].x ^ 0x80808080u, cur[c].y ^ 0x80808080u, cur[c].z ^ 0x80808080u, cur[c].w ^ 0x80808080u};
+            float kf[16];
 #pragma unroll
-                    for (int e = 0; e < 16; ++e) acc[g][e & 7] = __fmaf_rn(qv[e], kf[e], acc[g][e & 7]);
-                }
-            }
-            const int t = t0 + tid;
-            const float ksc = (a.append && t == pos) ? s_stat[2 * GH] : __ldcg(sk + t);
-            const float ks = ksc * sm_scale;
+            for (int e = 0; e < 16; ++e) kf[e] = s8_to_f(w[e >> 2], e & 3);
 #pragma unroll
             for (int g = 0; g < GH; ++g) {
-                const float dot = (acc[g][0] + acc[g][1] + acc[g][2] + acc[g][3] + acc[g][4] + acc[g][5] + acc[g][6] + acc[g][7]) * ks;   // :691
-                s_sc[(size_t)t * GH + g] = dot;
-                tmax[g] = fmaxf(tmax[g], dot);
+                const float4* q4 = reinterpret_cast<const float4*>(s_q + g * kHd + c * 16);
+                const float4 qa = q4[0], qb = q4[1], qc = q4[2], qd = q4[3];
+                const float qv[16] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w,
+                                      qc.x, qc.y, qc.z, qc.w, qd.x, qd.y, qd.z, qd.w};
+#pragma unroll
+                for (int e = 0; e < 16; ++e) acc[g][e & 7] = __fmaf_rn(qv[e], kf[e], acc[g][e & 7]);
             }
         }
-        __syncthreads();
+        const float ksc = (a.append && t == pos) ? s_stat[2 * GH] : __ldcg(sk + t);
+        const float ks = ksc * sm_scale;
+#pragma unroll
+        for (int g = 0; g < GH; ++g) {
+            const float dot = (acc[g][0] + acc[g][1] + acc[g][2] + acc[g][3] + acc[g][4] + acc[g][5] + acc[g][6] + acc[g][7]) * ks;   // :691
+            s_sc[(size_t)t * GH + g] = dot;
+            tmax[g] = fmaxf(tmax[g], dot);
+        }
+        if (more) {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) cur[c] = nxt[c];
+        }
     }
 #pragma unroll
     for (int g = 0; g < GH; ++g) {
@@ -209,8 +232,15 @@ __global__ void __launch_bounds__(kAttnThreads) attn_kernel(const AttnLaunch L) 
     // ---- sum_t e_t, left to right, one thread per head (:824-829) ----------------------------------
     if (tid < GH) {
         float sum = 0.0f;
-#pragma unroll 8
-        for (int t = 0; t < T; ++t) sum = __fadd_rn(sum, s_sc[(size_t)t * GH + tid]);
+        int t = 0;
+        for (; t + 16 <= T; t += 16) {          // loads first, then the dependent adds
+            float e[16];
+#pragma unroll
+            for (int u = 0; u < 16; ++u) e[u] = s_sc[(size_t)(t + u) * GH + tid];
+#pragma unroll
+            for (int u = 0; u < 16; ++u) sum = __fadd_rn(sum, e[u]);
+        }
+        for (; t < T; ++t) sum = __fadd_rn(sum, s_sc[(size_t)t * GH + tid]);
         s_stat[GH + tid] = 1.0f / sum;
     }
     __syncthreads();
@@ -221,32 +251,38 @@ __global__ void __launch_bounds__(kAttnThreads) attn_kernel(const AttnLaunch L) 
         const float vs = (a.append && t == pos) ? s_stat[2 * GH + 1] : __ldcg(sv + t);
         s_sc[idx] = p * vs;
     }
+    __syncthreads();
 
     // ---- output: thread d owns dim d of every head and walks t in order (:842-851) ------------------
     float o[GH];
 #pragma unroll
     for (int g = 0; g < GH; ++g) o[g] = 0.0f;
-    for (int t0 = 0; t0 < T; t0 += kChunk) {
-        const int nkeys = min(kChunk, T - t0);
-        __syncthreads();                                   // weights complete / previous chunk consumed
-        for (int idx = tid; idx < nkeys * 8; idx += kAttnThreads) {
-            const int r = idx >> 3, c = idx & 7;
-            const bool is_new = a.append && (t0 + r == pos);
-            const uint4 v = is_new ? reinterpret_cast<const uint4*>(s_new8 + kHd)[c] : ld_cg_u4(cv + (size_t)(t0 + r) * kHd + c * 16);
-            *reinterpret_cast<uint4*>(s_stage + r * kHd + c * 16) = v;
+    bool timed_out = false;
+    for (int c = 0; c < n_chunks; ++c) {
+        const int t0 = c * kChunk, nkeys = min(kChunk, T - t0);
+        unsigned char* vb = s_v + (size_t)(c & 1) * kChunk * kHd;
+        if (lane == 0 && !mbar_wait_bounded(&s_bar[c & 1], (unsigned)(c >> 1) & 1u)) timed_out = true;
+        __syncwarp();
+        if (a.append && pos >= t0 && pos < t0 + nkeys) {        // the new token's row is not in the cache copy: patch it in
+            __syncthreads();                                     // every warp has seen the copy complete
+            if (tid < 8) reinterpret_cast<uint4*>(vb + (size_t)(pos - t0) * kHd)[tid] = reinterpret_cast<const uint4*>(s_new8 + kHd)[tid];
+            __syncthreads();
         }
-        __syncthreads();
         if (tid < kHd) {
-#pragma unroll 4
+            const unsigned char* vcol = vb + tid;
+            const float* wg = s_sc + (size_t)t0 * GH;
+#pragma unroll 8
             for (int kl = 0; kl < nkeys; ++kl) {
-                const uint32_t b = s_stage[kl * kHd + tid];
+                const uint32_t b = vcol[kl * kHd];
                 const float vf = __uint_as_float((b ^ 0x80u) | 0x4B000000u) - 8388736.0f;
-                const float* wg = s_sc + (size_t)(t0 + kl) * GH;
 #pragma unroll
-                for (int g = 0; g < GH; ++g) o[g] = __fmaf_rn(vf, wg[g], o[g]);
+                for (int g = 0; g < GH; ++g) o[g] = __fmaf_rn(vf, wg[kl * GH + g], o[g]);
             }
         }
+        __syncthreads();                                         // buffer free again
+        if (tid == 0 && c + 2 < n_chunks) issue_v(c + 2);
     }
+    if (timed_out) atomicExch(&g_attn_timeouts, 1);
     if (tid < kHd) {
 #pragma unroll
         for (int g = 0; g < GH; ++g) a.out[(size_t)seq * a.n_q * kHd + (size_t)(head0 + g) * kHd + tid] = o[g];
@@ -281,6 +317,13 @@ static int pick_heads_per_cta(int batch, int n_q, int group, int max_len) {
 
 }  // namespace tz
 
+extern "C" int tenzo_cuda_attention_take_timeouts(void) {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, tz::g_attn_timeouts, sizeof v) != cudaSuccess) return -1;
+    if (v) cudaMemcpyToSymbol(tz::g_attn_timeouts, &zero, sizeof zero);
+    return v;
+}
+
 extern "C" int tenzo_cuda_attention_heads_per_cta(int batch, int n_q, int n_kv, int max_len) {
     if (batch <= 0 || n_q <= 0 || n_kv <= 0 || n_q % n_kv || max_len <= 0) return 0;
     return tz::pick_heads_per_cta(batch, n_q, n_q / n_kv, max_len);
@@ -303,6 +346,8 @@ extern "C" int tenzo_cuda_attention_int8(const tenzo_attention_args* args, void*
     if (L.a.q_stride <= 0) L.a.q_stride = a.n_q * kHd;
     if (L.a.kv_stride <= 0) L.a.kv_stride = a.n_kv * kHd;
     L.gh = pick_heads_per_cta(a.batch, a.n_q, group, a.max_len);
+    if (a.heads_per_cta == 1 || a.heads_per_cta == 2 || a.heads_per_cta == 4 || a.heads_per_cta == 8)
+        if (a.heads_per_cta <= group && (size_t)a.heads_per_cta * a.max_len * sizeof(float) <= (size_t)kScoreSmemBytes) L.gh = a.heads_per_cta;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     cudaError_t e;
     switch (L.gh) {
