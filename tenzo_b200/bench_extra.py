@@ -118,7 +118,8 @@ def run_decode_batch(args):
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))))
-    B = args.batch // world                      # sequences are sharded across ranks, no data-path collective
+    from .sharding import shard_sequences
+    _, B = shard_sequences(args.batch, world, rank)     # sequences are sharded across ranks, no data-path collective
     ctx = args.context
     cfg = dict(synth.BITNET_2B, max_seq_len=ctx + args.steps + max(3, args.warmup) + 8)
     model = synth.SyntheticModel(cfg, seed=0)
@@ -139,10 +140,10 @@ def run_decode_batch(args):
         ms = float(t.item())
     if rank == 0:
         print(json.dumps({
-            "metric": "decode_tokens_per_second_batched", "value": B * world * args.steps / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
+            "metric": "decode_tokens_per_second_batched", "value": args.batch * args.steps / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-            "config": {"workload": f"decode_batch: BitNet-2B shape, global batch {B * world}, context {ctx} (device-filled KV), "
+            "config": {"workload": f"decode_batch: BitNet-2B shape, global batch {args.batch}, context {ctx} (device-filled KV), "
                                    f"{B} sequences per GPU", "parallelism": f"dp{world}"},
             "gpu_launches": int(launches),
         }), flush=True)

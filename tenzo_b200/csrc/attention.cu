@@ -23,8 +23,8 @@
 
 namespace tz {
 
-constexpr int kAttnThreads = 256;
-constexpr int kChunk = 256;          // V rows per bulk copy (two in flight)
+constexpr int kAttnThreads = 512;
+constexpr int kChunk = 128;          // V rows per bulk copy (two in flight)
 constexpr int kHd = 128;             // head_dim (the reference hard-wires 16 x 8 lanes, :833-850)
 constexpr int kScoreSmemBytes = 144 * 1024;  // per-CTA budget for the score vectors [T][GH] (whole CTA stays under 227 KB)
 
@@ -53,7 +53,7 @@ template <int GH>
 struct AttnSmem {
     // floats: s_q[GH*128] | s_new[256] | s_red[8*GH] | s_stat[2*GH+2]; then 16-byte aligned: s_new8[256 B] |
     // mbarriers[2 x 8 B] | V double buffer [2][kChunk*128 B] | scores [T][GH] floats
-    static constexpr int n_float = GH * kHd + 2 * kHd + 8 * GH + 2 * GH + 2;
+    static constexpr int n_float = GH * kHd + 2 * kHd + 16 * GH + 2 * GH + 2;
     static constexpr int new8_off = (n_float * 4 + 15) & ~15;
     static constexpr int bar_off = new8_off + 2 * kHd;
     static constexpr int v_off = bar_off + 16;
@@ -70,8 +70,8 @@ __global__ void __launch_bounds__(kAttnThreads) attn_kernel(const AttnLaunch L) 
     using Lay = AttnSmem<GH>;
     float* s_q = reinterpret_cast<float*>(smem_raw);                     // [GH][128] rotated queries
     float* s_new = s_q + GH * kHd;                                       // [2][128] rotated k, v of the new token
-    float* s_red = s_new + 2 * kHd;                                      // [8][GH] per-warp maxima
-    float* s_stat = s_red + 8 * GH;                                      // [GH] max, [GH] 1/sum, [2] new-row scales
+    float* s_red = s_new + 2 * kHd;                                      // [16][GH] per-warp maxima
+    float* s_stat = s_red + 16 * GH;                                     // [GH] max, [GH] 1/sum, [2] new-row scales
     int8_t* s_new8 = reinterpret_cast<int8_t*>(smem_raw + Lay::new8_off);   // [2][128] quantised new k, v
     uint64_t* s_bar = reinterpret_cast<uint64_t*>(smem_raw + Lay::bar_off); // [2] one per V buffer
     unsigned char* s_v = smem_raw + Lay::v_off;                          // [2][kChunk][128] V rows as in memory
@@ -310,6 +310,8 @@ static cudaError_t launch_attn(const AttnLaunch& L, cudaStream_t st) {
 // Query heads per CTA: as many as share a kv head, halved while that leaves SMs idle or the score
 // vectors [max_len][GH] would not fit in shared memory.
 static int pick_heads_per_cta(int batch, int n_q, int group, int max_len) {
+    // As many heads as share the kv head (K and V bytes are then fetched once for all of them), fewer
+    // when that would leave SMs idle or the score vectors would not fit in shared memory.
     int gh = group;
     while (gh > 1 && ((long long)batch * (n_q / gh) < 148 || (size_t)gh * max_len * sizeof(float) > (size_t)kScoreSmemBytes)) gh >>= 1;
     return gh;
