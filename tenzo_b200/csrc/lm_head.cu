@@ -25,17 +25,47 @@ __device__ __forceinline__ bool better(float v, int i, float bv, int bi) {
     return v > bv || (v == bv && i < bi);
 }
 
+// Sum of squares in the reference's order (see common.cuh) computed by ONE warp over a vector in
+// shared memory: lanes 0-7 run the eight chains, the lane sums are then added left to right.
+__device__ __forceinline__ float warp_sumsq_reference_order(const float* x, int dim, int lane) {
+    const int n8 = dim & ~7;
+    float s = 0.0f;
+    if (lane < 8) {
+        int i = lane;
+        for (; i + 8 * 15 < n8; i += 8 * 16) {
+            float v[16];
+#pragma unroll
+            for (int u = 0; u < 16; ++u) v[u] = x[i + 8 * u];
+#pragma unroll
+            for (int u = 0; u < 16; ++u) v[u] = __fmul_rn(v[u], v[u]);
+#pragma unroll
+            for (int u = 0; u < 16; ++u) s = __fadd_rn(s, v[u]);
+        }
+        for (; i < n8; i += 8) s = __fadd_rn(s, __fmul_rn(x[i], x[i]));
+    }
+    float t = __shfl_sync(0xffffffffu, s, 0);
+#pragma unroll
+    for (int j = 1; j < 8; ++j) t = __fadd_rn(t, __shfl_sync(0xffffffffu, s, j));
+    for (int i = n8; i < dim; ++i) t = __fadd_rn(t, __fmul_rn(x[i], x[i]));
+    return t;
+}
+
+// NS sequences per CTA (1 or 8). With 8, warp n prepares sequence n (norm, quantise) and every
+// vocabulary row read from HBM is used for all eight sequences.
+template <int NS>
 __global__ void __launch_bounds__(kLmThreads) lm_head_kernel(
     const float* __restrict__ x, const float* __restrict__ norm_w, int do_norm, float eps,
-    const int8_t* __restrict__ w, const float* __restrict__ row_scales, int vocab, int hidden, int x_stride,
+    const int8_t* __restrict__ w, const float* __restrict__ row_scales, int vocab, int hidden, int x_stride, int batch,
     float* logits, int32_t* acc_out, LmBest* cta_best, int use_pdl) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    float* s_y = reinterpret_cast<float*>(smem_raw);                  // [hidden]
-    float* s_f = s_y + hidden;                                        // [32]
-    LmBest* s_best = reinterpret_cast<LmBest*>(s_f + 32);             // [kLmWarps]
-    int8_t* s_x8 = reinterpret_cast<int8_t*>(s_best + kLmWarps);      // [hidden rounded up to 16]
+    const int hpad = (hidden + 15) & ~15;
+    float* s_y = reinterpret_cast<float*>(smem_raw);                  // [NS][hidden]
+    float* s_sx = s_y + (size_t)NS * hidden;                          // [NS] activation scales (+ pad to 8 floats)
+    LmBest* s_best = reinterpret_cast<LmBest*>(s_sx + 8);             // [kLmWarps][NS]
+    int8_t* s_x8 = reinterpret_cast<int8_t*>(s_best + kLmWarps * NS); // [NS][hpad]
+    s_x8 = reinterpret_cast<int8_t*>((reinterpret_cast<uintptr_t>(s_x8) + 15) & ~uintptr_t(15));
 
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, seq = blockIdx.y;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, seq0 = blockIdx.y * NS;
     const int total_warps = gridDim.x * kLmWarps;
     const int gw = blockIdx.x * kLmWarps + warp;
     const int nvec = hidden >> 4;                                     // 16-byte pieces per row
@@ -43,64 +73,88 @@ __global__ void __launch_bounds__(kLmThreads) lm_head_kernel(
 
     if (use_pdl) pdl_wait();
 
-    // ---- prologue: final RMSNorm + absmax(127) quantiser (:1638, :1666-1678) -------------------
-    const float* xs = x + (size_t)seq * x_stride;
-    for (int i = tid; i < hidden; i += kLmThreads) s_y[i] = __ldcg(xs + i);
-    float m = 0.0f;
-    if (do_norm) {
-        __syncthreads();
-        const float ss = sumsq_reference_order(s_y, hidden, s_f);
-        const float inv_rms = rms_inv(ss, hidden, eps);
-        for (int i = tid; i < hidden; i += kLmThreads) {
-            const float y = rms_apply(s_y[i], inv_rms, norm_w, i);
-            s_y[i] = y;
-            m = fmaxf(m, fabsf(y));
+    // ---- prologue: final RMSNorm + absmax(127) quantiser (:1638, :1666-1678), one warp per sequence
+    for (int n = warp; n < NS; n += kLmWarps) {
+        float* y = s_y + (size_t)n * hidden;
+        int8_t* x8 = s_x8 + (size_t)n * hpad;
+        if (seq0 + n >= batch) {
+            for (int i = lane; i < hpad; i += 32) x8[i] = 0;
+            if (lane == 0) s_sx[n] = 0.0f;
+            continue;
         }
-    } else {
-        for (int i = tid; i < hidden; i += kLmThreads) m = fmaxf(m, fabsf(s_y[i]));
+        const float* xs = x + (size_t)(seq0 + n) * x_stride;
+        for (int i = lane; i < hidden; i += 32) y[i] = __ldcg(xs + i);
+        __syncwarp();
+        float m = 0.0f;
+        if (do_norm) {
+            const float ss = warp_sumsq_reference_order(y, hidden, lane);
+            const float inv_rms = rms_inv(ss, hidden, eps);
+            for (int i = lane; i < hidden; i += 32) {
+                const float v = rms_apply(y[i], inv_rms, norm_w, i);
+                y[i] = v;
+                m = fmaxf(m, fabsf(v));
+            }
+        } else {
+            for (int i = lane; i < hidden; i += 32) m = fmaxf(m, fabsf(y[i]));
+        }
+        m = fmaxf(warp_max(m), 1e-8f);
+        const float sx = m / 127.0f;                                  // :1671
+        const float inv_s = 1.0f / sx;                                // :1672
+        for (int i = lane; i < hpad; i += 32)
+            x8[i] = i < hidden ? (int8_t)(int)fminf(fmaxf(roundf(y[i] * inv_s), -128.0f), 127.0f) : (int8_t)0;
+        if (lane == 0) s_sx[n] = sx;
     }
-    m = fmaxf(block_max(m, s_f), 1e-8f);
-    const float s_x = m / 127.0f;                                     // :1671
-    const float inv_s = 1.0f / s_x;                                   // :1672
-    for (int i = tid; i < hidden; i += kLmThreads)
-        s_x8[i] = (int8_t)(int)fminf(fmaxf(roundf(s_y[i] * inv_s), -128.0f), 127.0f);
     __syncthreads();
     if (use_pdl) pdl_launch_dependents();
 
-    // ---- rows ------------------------------------------------------------------------------------
+    // ---- rows: lane n keeps the running best of sequence n ---------------------------------------
     float best_v = -INFINITY;
     int best_i = 0x7fffffff;
-    const uint4* x4 = reinterpret_cast<const uint4*>(s_x8);
+    const float my_sx = lane < NS ? s_sx[lane] : 0.0f;
     for (int v = gw; v < vocab; v += total_warps) {
         const int8_t* row = w + (size_t)v * hidden;
-        int acc = 0;
+        int acc[NS];
+#pragma unroll
+        for (int n = 0; n < NS; ++n) acc[n] = 0;
         if (vec_ok) {
             for (int p = lane; p < nvec; p += 32) {
                 const uint4 wv = ld_stream_u4(row + (size_t)p * 16);
-                const uint4 xv = x4[p];
-                acc = dp4a_ss(wv.x, xv.x, acc);
-                acc = dp4a_ss(wv.y, xv.y, acc);
-                acc = dp4a_ss(wv.z, xv.z, acc);
-                acc = dp4a_ss(wv.w, xv.w, acc);
+#pragma unroll
+                for (int n = 0; n < NS; ++n) {
+                    const uint4 xv = reinterpret_cast<const uint4*>(s_x8 + (size_t)n * hpad)[p];
+                    acc[n] = dp4a_ss(wv.x, xv.x, acc[n]);
+                    acc[n] = dp4a_ss(wv.y, xv.y, acc[n]);
+                    acc[n] = dp4a_ss(wv.z, xv.z, acc[n]);
+                    acc[n] = dp4a_ss(wv.w, xv.w, acc[n]);
+                }
             }
         } else {
-            for (int i = lane; i < hidden; i += 32) acc += (int)row[i] * (int)s_x8[i];
+            for (int i = lane; i < hidden; i += 32) {
+                const int wi = (int)row[i];
+#pragma unroll
+                for (int n = 0; n < NS; ++n) acc[n] += wi * (int)s_x8[(size_t)n * hpad + i];
+            }
         }
-        acc = warp_sum_i(acc);
-        if (lane == 0) {
-            const float lg = (float)acc * (s_x * row_scales[v]);      // :1717
-            if (logits) logits[(size_t)seq * vocab + v] = lg;
-            if (acc_out) acc_out[(size_t)seq * vocab + v] = acc;
+        int mine = 0;
+#pragma unroll
+        for (int n = 0; n < NS; ++n) {
+            const int t = warp_sum_i(acc[n]);
+            if (lane == n) mine = t;
+        }
+        if (lane < NS && seq0 + lane < batch) {
+            const float lg = (float)mine * (my_sx * row_scales[v]);   // :1717
+            if (logits) logits[(size_t)(seq0 + lane) * vocab + v] = lg;
+            if (acc_out) acc_out[(size_t)(seq0 + lane) * vocab + v] = mine;
             if (better(lg, v, best_v, best_i)) { best_v = lg; best_i = v; }
         }
     }
-    if (lane == 0) { s_best[warp].val = best_v; s_best[warp].idx = best_i; }
+    if (lane < NS) { s_best[warp * NS + lane].val = best_v; s_best[warp * NS + lane].idx = best_i; }
     __syncthreads();
-    if (tid == 0) {
-        LmBest b = s_best[0];
+    if (tid < NS && seq0 + tid < batch) {
+        LmBest b = s_best[tid];
         for (int i = 1; i < kLmWarps; ++i)
-            if (better(s_best[i].val, s_best[i].idx, b.val, b.idx)) b = s_best[i];
-        cta_best[(size_t)seq * gridDim.x + blockIdx.x] = b;
+            if (better(s_best[i * NS + tid].val, s_best[i * NS + tid].idx, b.val, b.idx)) b = s_best[i * NS + tid];
+        cta_best[(size_t)(seq0 + tid) * gridDim.x + blockIdx.x] = b;
     }
 }
 
@@ -152,22 +206,26 @@ extern "C" size_t tenzo_cuda_lm_head_scratch_bytes(int batch) {
     return batch > 0 ? (size_t)batch * tz::kLmCtas * sizeof(tz::LmBest) : 0;
 }
 
-extern "C" int tenzo_cuda_lm_head_i8(const float* x, const float* norm_w, int do_norm, float eps,
-                                     const int8_t* w, const float* row_scales, int vocab, int hidden,
-                                     int batch, int x_stride, float* logits, int32_t* acc_out,
-                                     int* argmax_out, void* scratch, int use_pdl, void* stream) {
+static int lm_head_launch(const float* x, const float* norm_w, int do_norm, float eps,
+                          const int8_t* w, const float* row_scales, int vocab, int hidden,
+                          int batch, int x_stride, float* logits, int32_t* acc_out,
+                          int* argmax_out, void* scratch, int use_pdl, void* stream, bool allow_batched) {
     using namespace tz;
     if (!x || !w || !row_scales || vocab <= 0 || hidden <= 0 || batch <= 0 || !scratch) return -1;
     if (hidden > 16384) return -5;
     if ((hidden & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) != 0) return -1;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const size_t smem = (size_t)(hidden + 32) * sizeof(float) + kLmWarps * sizeof(LmBest) + (((size_t)hidden + 15) & ~(size_t)15);
+    const size_t hpad = ((size_t)hidden + 15) & ~(size_t)15;
+    auto smem_for = [&](int ns) { return (size_t)ns * hidden * sizeof(float) + 8 * sizeof(float) + (size_t)kLmWarps * ns * sizeof(LmBest) + ns * hpad + 16; };
+    const bool eight = allow_batched && batch > 1 && smem_for(8) <= 200 * 1024;   // eight sequences share each row read
+    const size_t smem = smem_for(eight ? 8 : 1);
     if (smem > 48 * 1024) {
-        cudaError_t ea = cudaFuncSetAttribute(lm_head_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        cudaError_t ea = eight ? cudaFuncSetAttribute(lm_head_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                               : cudaFuncSetAttribute(lm_head_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (ea != cudaSuccess) return (int)ea;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(kLmCtas, (unsigned)batch, 1);
+    cfg.gridDim = dim3(kLmCtas, (unsigned)(eight ? (batch + 7) / 8 : batch), 1);
     cfg.blockDim = dim3(kLmThreads, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
@@ -176,14 +234,24 @@ extern "C" int tenzo_cuda_lm_head_i8(const float* x, const float* norm_w, int do
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = use_pdl ? 1 : 0;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, lm_head_kernel, x, norm_w, do_norm, eps, w, row_scales, vocab, hidden,
-                                       x_stride, logits, acc_out, static_cast<LmBest*>(scratch), use_pdl);
+    cudaError_t e = eight ? cudaLaunchKernelEx(&cfg, lm_head_kernel<8>, x, norm_w, do_norm, eps, w, row_scales, vocab, hidden, x_stride,
+                                               batch, logits, acc_out, static_cast<LmBest*>(scratch), use_pdl)
+                          : cudaLaunchKernelEx(&cfg, lm_head_kernel<1>, x, norm_w, do_norm, eps, w, row_scales, vocab, hidden, x_stride,
+                                               batch, logits, acc_out, static_cast<LmBest*>(scratch), use_pdl);
     if (e != cudaSuccess) return (int)e;
     if (argmax_out) {
         argmax_finish_kernel<<<batch, 256, 0, st>>>(static_cast<const LmBest*>(scratch), kLmCtas, argmax_out);
         e = cudaGetLastError();
     }
     return e == cudaSuccess ? 0 : (int)e;
+}
+
+extern "C" int tenzo_cuda_lm_head_i8(const float* x, const float* norm_w, int do_norm, float eps,
+                                     const int8_t* w, const float* row_scales, int vocab, int hidden,
+                                     int batch, int x_stride, float* logits, int32_t* acc_out,
+                                     int* argmax_out, void* scratch, int use_pdl, void* stream) {
+    return lm_head_launch(x, norm_w, do_norm, eps, w, row_scales, vocab, hidden, batch, x_stride, logits, acc_out, argmax_out,
+                          scratch, use_pdl, stream, true);
 }
 
 // ---- allocation-free variant ------------------------------------------------------------------
@@ -224,8 +292,8 @@ extern "C" int tenzo_cuda_lm_head_i8_static(const float* x, const float* norm_w,
     cudaError_t e = cudaSuccess;
     void* scratch = tz::lm_static_scratch_address(&e);
     if (!scratch) return (int)e;
-    return tenzo_cuda_lm_head_i8(x, norm_w, do_norm, eps, w, row_scales, vocab, hidden, batch, x_stride, logits,
-                                 acc_out, argmax_out, scratch, use_pdl, stream);
+    return lm_head_launch(x, norm_w, do_norm, eps, w, row_scales, vocab, hidden, batch, x_stride, logits,
+                          acc_out, argmax_out, scratch, use_pdl, stream, true);
 }
 
 extern "C" int tenzo_cuda_lm_head_static_max_batch(void) { return tz::kLmStaticMaxBatch; }
