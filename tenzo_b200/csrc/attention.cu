@@ -63,6 +63,127 @@ struct AttnSmem {
 
 __device__ int g_attn_timeouts = 0;   // set when a bounded wait on a V-chunk copy gave up
 
+#ifdef TZ_ATTN_TRACE
+__device__ unsigned long long g_attn_phase[8];
+#define TZ_PH(i) do { if (threadIdx.x == 0) { const long long now_ = clock64(); atomicAdd(&g_attn_phase[i], (unsigned long long)(now_ - ph_t_)); ph_t_ = now_; } } while (0)
+#define TZ_PH_DECL long long ph_t_ = clock64()
+#else
+#define TZ_PH(i) do {} while (0)
+#define TZ_PH_DECL do {} while (0)
+#endif
+
+template <int GH>
+__device__ __forceinline__ void load_weights(const float* p, float (&w)[GH]) {      // p is GH*4-byte aligned
+    if constexpr (GH == 1) {
+        w[0] = p[0];
+    } else if constexpr (GH == 2) {
+        const float2 v = *reinterpret_cast<const float2*>(p);
+        w[0] = v.x; w[1] = v.y;
+    } else {
+#pragma unroll
+        for (int h = 0; h < GH; h += 4) {
+            const float4 v = *reinterpret_cast<const float4*>(p + h);
+            w[h] = v.x; w[h + 1] = v.y; w[h + 2] = v.z; w[h + 3] = v.w;
+        }
+    }
+}
+
+// Value sum over one staged chunk for output dim `vcol - chunk base`: o[g] = fma(V[t][d], w[t][g], o[g])
+// for t in order (:842-851). Keys are taken eight at a time with the next eight already requested
+// from shared memory (two register sets, alternating), so the loads stay off the dependent chain.
+template <int GH>
+__device__ __forceinline__ void value_sum_chunk(const unsigned char* vcol, const float* wg, int nkeys, float (&o)[GH]) {
+    constexpr int U = 8;
+    uint32_t va[U], vb[U];
+    float wa[U][GH], wb[U][GH];
+    auto loadg = [&](int gi, uint32_t (&v)[U], float (&w)[U][GH]) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            v[u] = vcol[(gi * U + u) * kHd];
+            load_weights<GH>(wg + (size_t)(gi * U + u) * GH, w[u]);
+        }
+    };
+    auto compg = [&](const uint32_t (&v)[U], const float (&w)[U][GH]) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const float vf = __uint_as_float((v[u] ^ 0x80u) | 0x4B000000u) - 8388736.0f;
+#pragma unroll
+            for (int g = 0; g < GH; ++g) o[g] = __fmaf_rn(vf, w[u][g], o[g]);
+        }
+    };
+    const int full = nkeys / U;
+    int gi = 0;
+    if (full > 0) loadg(0, va, wa);
+    while (gi + 1 < full) {
+        loadg(gi + 1, vb, wb);
+        compg(va, wa);
+        if (gi + 2 < full) loadg(gi + 2, va, wa);
+        compg(vb, wb);
+        gi += 2;
+    }
+    if (gi < full) compg(va, wa);
+    for (int kl = full * U; kl < nkeys; ++kl) {
+        const uint32_t b = vcol[kl * kHd];
+        const float vf = __uint_as_float((b ^ 0x80u) | 0x4B000000u) - 8388736.0f;
+        float w[GH];
+        load_weights<GH>(wg + (size_t)kl * GH, w);
+#pragma unroll
+        for (int g = 0; g < GH; ++g) o[g] = __fmaf_rn(vf, w[g], o[g]);
+    }
+}
+
+// sum_t e[t*stride], left to right (:824-829): sixteen loads in flight while the previous sixteen are added.
+__device__ __forceinline__ float sequential_sum(const float* e, int T, int stride) {
+    constexpr int U = 16;
+    float a[U], b[U];
+    float sum = 0.0f;
+    auto loadg = [&](int gi, float (&v)[U]) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) v[u] = e[(size_t)(gi * U + u) * stride];
+    };
+    auto addg = [&](const float (&v)[U]) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) sum = __fadd_rn(sum, v[u]);
+    };
+    const int full = T / U;
+    int gi = 0;
+    if (full > 0) loadg(0, a);
+    while (gi + 1 < full) {
+        loadg(gi + 1, b);
+        addg(a);
+        if (gi + 2 < full) loadg(gi + 2, a);
+        addg(b);
+        gi += 2;
+    }
+    if (gi < full) addg(a);
+    for (int t = full * U; t < T; ++t) sum = __fadd_rn(sum, e[(size_t)t * stride]);
+    return sum;
+}
+
+// e[i] = expf(e[i] - max[i % GH]) for i < n, by all `n_threads` threads of the CTA (whole warps).
+template <int GH>
+__device__ __forceinline__ void exp_in_place(float* e, int n, const float* mx, int tid, int n_threads) {
+    const int lane = tid & 31;
+    const unsigned long long tab = kExp2fTab[lane];
+    const uint32_t tab_lo = (uint32_t)tab, tab_hi = (uint32_t)(tab >> 32);
+    constexpr int U = 4;
+    for (int base = 0; base < n; base += U * n_threads) {
+        float x[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int idx = base + u * n_threads + tid;
+            x[u] = idx < n ? e[idx] - mx[idx % GH] : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) x[u] = expf_reference_bits_lanes(x[u], tab_lo, tab_hi);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int idx = base + u * n_threads + tid;
+            if (idx < n) e[idx] = x[u];
+        }
+    }
+}
+
 template <int GH>
 __global__ void __launch_bounds__(kAttnThreads) attn_kernel(const AttnLaunch L) {
     const tenzo_attention_args& a = L.a;
@@ -83,6 +204,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_kernel(const AttnLaunch L) 
     const bool stores_new_row = (head0 % G) == 0;
 
     if (a.use_pdl) pdl_wait();
+    TZ_PH_DECL;
     const int pos = a.pos[seq];
     const int T = pos + 1;
     const int n_chunks = (T + kChunk - 1) / kChunk;
@@ -160,6 +282,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_kernel(const AttnLaunch L) 
     }
     __syncthreads();
     if (a.use_pdl) pdl_launch_dependents();
+    TZ_PH(0);
 
     // ---- scores (:678-694): one key per thread straight from the cache (a row is 128 contiguous
     //      bytes), the next key's row requested before the current one is used; all GH heads, the
@@ -225,25 +348,16 @@ __global__ void __launch_bounds__(kAttnThreads) attn_kernel(const AttnLaunch L) 
         s_stat[tid] = m;
     }
     __syncthreads();
+    TZ_PH(1);
 
     // ---- e_t = expf(score - max), in parallel (:826) -----------------------------------------------
-    for (int idx = tid; idx < T * GH; idx += kAttnThreads) s_sc[idx] = expf_reference_bits(s_sc[idx] - s_stat[idx % GH]);
+    exp_in_place<GH>(s_sc, T * GH, s_stat, tid, kAttnThreads);
     __syncthreads();
+    TZ_PH(2);
     // ---- sum_t e_t, left to right, one thread per head (:824-829) ----------------------------------
-    if (tid < GH) {
-        float sum = 0.0f;
-        int t = 0;
-        for (; t + 16 <= T; t += 16) {          // loads first, then the dependent adds
-            float e[16];
-#pragma unroll
-            for (int u = 0; u < 16; ++u) e[u] = s_sc[(size_t)(t + u) * GH + tid];
-#pragma unroll
-            for (int u = 0; u < 16; ++u) sum = __fadd_rn(sum, e[u]);
-        }
-        for (; t < T; ++t) sum = __fadd_rn(sum, s_sc[(size_t)t * GH + tid]);
-        s_stat[GH + tid] = 1.0f / sum;
-    }
+    if (tid < GH) s_stat[GH + tid] = 1.0f / sequential_sum(s_sc + tid, T, GH);
     __syncthreads();
+    TZ_PH(3);
     // ---- weights p_t * s_v[t] (:830, :844) ------------------------------------------------------------
     for (int idx = tid; idx < T * GH; idx += kAttnThreads) {
         const int t = idx / GH;
@@ -252,6 +366,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_kernel(const AttnLaunch L) 
         s_sc[idx] = p * vs;
     }
     __syncthreads();
+    TZ_PH(4);
 
     // ---- output: thread d owns dim d of every head and walks t in order (:842-851) ------------------
     float o[GH];
@@ -268,17 +383,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_kernel(const AttnLaunch L) 
             if (tid < 8) reinterpret_cast<uint4*>(vb + (size_t)(pos - t0) * kHd)[tid] = reinterpret_cast<const uint4*>(s_new8 + kHd)[tid];
             __syncthreads();
         }
-        if (tid < kHd) {
-            const unsigned char* vcol = vb + tid;
-            const float* wg = s_sc + (size_t)t0 * GH;
-#pragma unroll 8
-            for (int kl = 0; kl < nkeys; ++kl) {
-                const uint32_t b = vcol[kl * kHd];
-                const float vf = __uint_as_float((b ^ 0x80u) | 0x4B000000u) - 8388736.0f;
-#pragma unroll
-                for (int g = 0; g < GH; ++g) o[g] = __fmaf_rn(vf, wg[kl * GH + g], o[g]);
-            }
-        }
+        if (tid < kHd) value_sum_chunk<GH>(vb + tid, s_sc + (size_t)t0 * GH, nkeys, o);
         __syncthreads();                                         // buffer free again
         if (tid == 0 && c + 2 < n_chunks) issue_v(c + 2);
     }
@@ -287,6 +392,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_kernel(const AttnLaunch L) 
 #pragma unroll
         for (int g = 0; g < GH; ++g) a.out[(size_t)seq * a.n_q * kHd + (size_t)(head0 + g) * kHd + tid] = o[g];
     }
+    TZ_PH(5);
 }
 
 template <int GH>
@@ -319,6 +425,15 @@ static int pick_heads_per_cta(int batch, int n_q, int group, int max_len) {
 
 }  // namespace tz
 
+#ifdef TZ_ATTN_TRACE
+extern "C" __attribute__((visibility("default"))) int tenzo_cuda_attention_trace(unsigned long long* out8, int reset) {
+    unsigned long long z[8] = {0};
+    if (cudaMemcpyFromSymbol(out8, tz::g_attn_phase, sizeof z) != cudaSuccess) return -1;
+    if (reset) cudaMemcpyToSymbol(tz::g_attn_phase, z, sizeof z);
+    return 0;
+}
+#endif
+
 extern "C" int tenzo_cuda_attention_take_timeouts(void) {
     int v = 0, zero = 0;
     if (cudaMemcpyFromSymbol(&v, tz::g_attn_timeouts, sizeof v) != cudaSuccess) return -1;
@@ -347,10 +462,10 @@ extern "C" int tenzo_cuda_attention_int8(const tenzo_attention_args* args, void*
     L.a = a;
     if (L.a.q_stride <= 0) L.a.q_stride = a.n_q * kHd;
     if (L.a.kv_stride <= 0) L.a.kv_stride = a.n_kv * kHd;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
     L.gh = pick_heads_per_cta(a.batch, a.n_q, group, a.max_len);
     if (a.heads_per_cta == 1 || a.heads_per_cta == 2 || a.heads_per_cta == 4 || a.heads_per_cta == 8)
         if (a.heads_per_cta <= group && (size_t)a.heads_per_cta * a.max_len * sizeof(float) <= (size_t)kScoreSmemBytes) L.gh = a.heads_per_cta;
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
     cudaError_t e;
     switch (L.gh) {
         case 1: e = launch_attn<1>(L, st); break;

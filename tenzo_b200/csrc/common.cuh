@@ -204,4 +204,28 @@ __device__ __forceinline__ float expf_reference_bits(float x) {
     return __double2float_rn(y);
 }
 
+// Same bits as expf_reference_bits, with the 32-entry table held one entry per lane (tab_lo/tab_hi =
+// the two halves of kExp2fTab[lane]) and fetched by shuffle instead of a data-dependent constant
+// load. Every lane of the warp must make the call.
+__device__ __forceinline__ float expf_reference_bits_lanes(float x, uint32_t tab_lo, uint32_t tab_hi) {
+    const double inv_ln2_n = 0x1.71547652b82fep+0 * 32.0, shift = 0x1.8p+52;
+    const double c0 = 0x1.c6af84b912394p-5 / 32 / 32 / 32, c1 = 0x1.ebfce50fac4f3p-3 / 32 / 32, c2 = 0x1.62e42ff0c52d6p-1 / 32;
+    const double xd = (double)x;
+    const double z = __dmul_rn(inv_ln2_n, xd);
+    double kd = __dadd_rn(z, shift);
+    const unsigned long long ki = (unsigned long long)__double_as_longlong(kd);
+    kd = __dadd_rn(kd, -shift);
+    const double r = __fma_rn(inv_ln2_n, xd, -kd);
+    const int sel = (int)(ki & 31);
+    const uint32_t lo = __shfl_sync(0xffffffffu, tab_lo, sel), hi = __shfl_sync(0xffffffffu, tab_hi, sel);
+    const unsigned long long t = (((unsigned long long)hi << 32) | lo) + (ki << 47);
+    const double s = __longlong_as_double((long long)t);
+    const double zz = __fma_rn(c0, r, c1);
+    const double r2 = __dmul_rn(r, r);
+    double y = __fma_rn(c2, r, 1.0);
+    y = __fma_rn(zz, r2, y);
+    y = __dmul_rn(y, s);
+    return x < -0x1.9fe368p6f ? 0.0f : __double2float_rn(y);
+}
+
 }  // namespace tz

@@ -137,6 +137,41 @@ def test_attention_batched_ragged_lengths(cuda_lib):
         assert np.array_equal(host(dck)[b].reshape(-1), ock) and np.array_equal(host(dsv)[b].reshape(-1), osv)
 
 
+@pytest.mark.parametrize("B,lens_cycle,ms", [(3, [1, 256, 700], 768), (130, [1, 2, 127, 128, 129, 255, 257, 300, 384, 385, 511, 512], 512),
+                                             (4, [8192, 4097, 8000, 1], 8192)])
+def test_attention_many_sequences_and_long_context(cuda_lib, B, lens_cycle, ms):
+    """Bit for bit against the oracle: a few sequences, 130 sequences (more CTAs than SMs) with ragged lengths
+    around the 128-key chunk and 512-key pass boundaries, and an 8192-token context."""
+    from tenzo_b200 import kernels
+    O = ora.load_oracle()
+    nq, nkv, hd = 20, 5, 128
+    lens = [lens_cycle[i % len(lens_cycle)] for i in range(B)]
+    g = torch.Generator(device="cuda").manual_seed(77)
+    dck = torch.randint(-127, 128, (B, 1, nkv, ms, hd), generator=g, device="cuda", dtype=torch.int8)
+    dcv = torch.randint(-127, 128, (B, 1, nkv, ms, hd), generator=g, device="cuda", dtype=torch.int8)
+    dsk = 0.01 + 0.02 * torch.rand(B, 1, nkv, ms, generator=g, device="cuda")
+    dsv = 0.01 + 0.02 * torch.rand(B, 1, nkv, ms, generator=g, device="cuda")
+    ck, cv, sk, sv = host(dck), host(dcv), host(dsk), host(dsv)
+    rng = np.random.default_rng(53)
+    q = rng.standard_normal((B, nq * hd)).astype(np.float32)
+    k = rng.standard_normal((B, nkv * hd)).astype(np.float32)
+    v = rng.standard_normal((B, nkv * hd)).astype(np.float32)
+    cs, sn = rope_tables(ms, 10000.0)
+    pos = np.array([n - 1 for n in lens], np.int32)
+    out = kernels.attention_int8(dev(q), dev(k), dev(v), dck, dcv, dsk, dsv, dev(pos), layer=0, n_q=nq, n_kv=nkv, max_seq=ms,
+                                 rope_cos=dev(cs), rope_sin=dev(sn))
+    torch.cuda.synchronize()
+    assert cuda_lib.tenzo_cuda_attention_take_timeouts() == 0
+    got, gck, gsv = host(out), host(dck), host(dsv)
+    for b in range(B):
+        ock, ocv, osk, osv = ck[b].reshape(-1).copy(), cv[b].reshape(-1).copy(), sk[b].reshape(-1).copy(), sv[b].reshape(-1).copy()
+        qq, kk, vv, o = q[b].copy(), k[b].copy(), v[b].copy(), np.zeros(nq * hd, np.float32)
+        O.ora_attention_int8(0, int(pos[b]), nq, nkv, hd, ms, 10000.0, P(qq, ora.c_f32p), P(kk, ora.c_f32p), P(vv, ora.c_f32p),
+                             P(o, ora.c_f32p), P(ock, ora.c_i8p), P(ocv, ora.c_i8p), P(osk, ora.c_f32p), P(osv, ora.c_f32p))
+        assert np.array_equal(got[b], o), f"sequence {b} (length {lens[b]}): rel err {rel_err(got[b], o):.2e}"
+        assert np.array_equal(gck[b].reshape(-1), ock) and np.array_equal(gsv[b].reshape(-1), osv)
+
+
 def test_lm_head_golden_and_argmax(cuda_lib, golden):
     from tenzo_b200 import kernels
     g = golden["lm_head"]
