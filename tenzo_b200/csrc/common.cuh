@@ -77,6 +77,9 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, unsigned parity
     return false;
 }
 
+// Barrier among `count` threads (a multiple of 32) of the CTA; id 1..15 (0 is __syncthreads).
+__device__ __forceinline__ void named_barrier_sync(int id, int count) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory"); }
+
 // Programmatic dependent launch: wait until the kernels this one depends on have completed and
 // their memory is visible / allow the next kernel in the stream to begin its own prologue.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }

@@ -59,10 +59,11 @@ __global__ void __launch_bounds__(kNqThreads) rmsnorm_quant_kernel(
 // Batched front half of the TL1 GEMM: per sequence RMSNorm + absmax(31) quantiser, written as the
 // packed tensor-core B fragments tl1_mma_kernel consumes: words[seq][set][t][0] holds 4*a for the
 // even columns of column pairs 16*set + 4*i + t (byte i = 0..3), words[seq][set][t][1] the odd
-// columns unscaled; columns beyond K are zero. inv[seq] = max|y|/31.
+// columns unscaled; columns beyond K are zero. inv[seq] = max|y|/31. `words` may be null (tensor-core GEMM
+// path: it takes the plain int8 matrix a_out [batch][K] and sum_out[seq] = sum_k a_k instead).
 __global__ void __launch_bounds__(kNqThreads) act_quant_kernel(
     const float* x, const float* __restrict__ norm_w, int do_norm, float eps, int K, int x_stride,
-    uint32_t* words, float* inv, int8_t* a_out, int use_pdl) {
+    uint32_t* words, float* inv, int8_t* a_out, int* sum_out, int use_pdl) {
     extern __shared__ float s_y[];            // K floats + 32 scratch
     float* s_f = s_y + K;
     const int tid = threadIdx.x, seq = blockIdx.x;
@@ -86,7 +87,7 @@ __global__ void __launch_bounds__(kNqThreads) act_quant_kernel(
     const float to_q = 31.0f / m;             // :34
     if (use_pdl) pdl_launch_dependents();
     const int nsets = ((K >> 1) + 15) / 16;
-    for (int wd = tid; wd < nsets * 8; wd += kNqThreads) {
+    for (int wd = tid; words && wd < nsets * 8; wd += kNqThreads) {
         const int s = wd >> 3, tt = (wd >> 1) & 3, odd = wd & 1;
         uint32_t word = 0;
 #pragma unroll
@@ -98,12 +99,28 @@ __global__ void __launch_bounds__(kNqThreads) act_quant_kernel(
         words[(size_t)seq * nsets * 8 + wd] = word;
     }
     if (tid == 0) inv[seq] = m / 31.0f;       // :35
-    if (a_out)
-        for (int i = tid; i < K; i += kNqThreads) a_out[(size_t)seq * K + i] = (int8_t)(int)roundf(s_y[i] * to_q);
+    if (a_out || sum_out) {
+        int part = 0;
+        for (int i = tid; i < K; i += kNqThreads) {
+            const int q = (int)roundf(s_y[i] * to_q);
+            if (a_out) a_out[(size_t)seq * K + i] = (int8_t)q;
+            part += q;
+        }
+        if (sum_out) {                        // sum_k a_k, for kernels that multiply by the unsigned codes w+1
+            int* s_i = reinterpret_cast<int*>(s_f);
+            __syncthreads();
+            if (tid == 0) s_i[0] = 0;
+            __syncthreads();
+            part = __reduce_add_sync(0xffffffffu, part);
+            if ((tid & 31) == 0) atomicAdd(&s_i[0], part);
+            __syncthreads();
+            if (tid == 0) sum_out[seq] = s_i[0];
+        }
+    }
 }
 
 cudaError_t launch_act_quant(const float* x, const float* norm_w, int do_norm, float eps, int K, int batch, int x_stride,
-                             uint32_t* words, float* inv, int8_t* a_out, int use_pdl, cudaStream_t st) {
+                             uint32_t* words, float* inv, int8_t* a_out, int* sum_out, int use_pdl, cudaStream_t st) {
     const size_t smem = (size_t)(K + 32) * sizeof(float);
     if (smem > 48 * 1024) {
         cudaError_t ea = cudaFuncSetAttribute(act_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024);
@@ -119,7 +136,7 @@ cudaError_t launch_act_quant(const float* x, const float* norm_w, int do_norm, f
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = use_pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, act_quant_kernel, x, norm_w, do_norm, eps, K, x_stride, words, inv, a_out, use_pdl);
+    return cudaLaunchKernelEx(&cfg, act_quant_kernel, x, norm_w, do_norm, eps, K, x_stride, words, inv, a_out, sum_out, use_pdl);
 }
 
 }  // namespace tz

@@ -399,7 +399,11 @@ static int pick_ksplit(int n_blocks, int K, int epilogue, int batch) {
 
 // act_quant_kernel lives in norm_quant.cu
 cudaError_t launch_act_quant(const float* x, const float* norm_w, int do_norm, float eps, int K, int batch, int x_stride,
-                             uint32_t* words, float* inv, int8_t* a_out, int use_pdl, cudaStream_t st);
+                             uint32_t* words, float* inv, int8_t* a_out, int* sum_out, int use_pdl, cudaStream_t st);
+// tcgen05 GEMM for 16 or more sequences (tl1_umma.cu)
+bool tl1_umma_applicable(const tenzo_tl1_gemv_args& a);
+int launch_tl1_umma(const tenzo_tl1_gemv_args& a, const int8_t* a8, const float* inv, const int* sum_a, cudaStream_t st);
+int tl1_umma_take_timeouts();
 
 template <int NT, bool FUSED>
 static cudaError_t launch_gemv(const GemvLaunch& L, cudaStream_t st) {
@@ -447,13 +451,17 @@ extern "C" int tenzo_cuda_tl1_gemv_take_timeouts(void) {
     int v = 0, zero = 0;
     if (cudaMemcpyFromSymbol(&v, tz::g_tl1_timeouts, sizeof v) != cudaSuccess) return -1;
     if (v) cudaMemcpyToSymbol(tz::g_tl1_timeouts, &zero, sizeof zero);
-    return v;
+    const int u = tz::tl1_umma_take_timeouts();
+    if (u < 0) return -1;
+    return v | u;
 }
 
 extern "C" size_t tenzo_cuda_tl1_gemv_workspace_bytes(int batch, int K) {
     if (batch <= 1 || K <= 0) return 0;
     const size_t nsets = ((size_t)(K >> 1) + 15) / 16;
-    return (size_t)batch * nsets * 32 + (size_t)batch * sizeof(float) + 64;
+    // packed activations (words path) or the plain int8 matrix (tensor-core path), then inv[batch], then sum_a[batch]
+    const size_t act = (size_t)batch * nsets * 32 > (size_t)batch * K ? (size_t)batch * nsets * 32 : (size_t)batch * K;
+    return ((act + 15) & ~(size_t)15) + 2 * (size_t)batch * sizeof(float) + 64;
 }
 
 extern "C" int tenzo_cuda_tl1_gemv(const tenzo_tl1_gemv_args* args, void* stream) {
@@ -481,8 +489,18 @@ extern "C" int tenzo_cuda_tl1_gemv(const tenzo_tl1_gemv_args* args, void* stream
         e = launch_gemv<1, true>(L, st);
     } else {
         uint32_t* words = static_cast<uint32_t*>(a.workspace);
-        float* inv = reinterpret_cast<float*>(words + (size_t)a.batch * L.nsets * 8);
-        e = launch_act_quant(a.x, a.norm_w, a.do_norm, a.eps, a.K, a.batch, a.x_stride, words, inv, a.a_out, a.use_pdl, st);
+        const size_t act_bytes = (((size_t)a.batch * L.nsets * 32 > (size_t)a.batch * a.K ? (size_t)a.batch * L.nsets * 32 : (size_t)a.batch * a.K) + 15) & ~(size_t)15;
+        float* inv = reinterpret_cast<float*>(static_cast<unsigned char*>(a.workspace) + act_bytes);
+        if (tl1_umma_applicable(a)) {
+            int8_t* a8 = static_cast<int8_t*>(a.workspace);
+            int* sums = reinterpret_cast<int*>(inv + a.batch);
+            e = launch_act_quant(a.x, a.norm_w, a.do_norm, a.eps, a.K, a.batch, a.x_stride, nullptr, inv, a8, sums, a.use_pdl, st);
+            if (e != cudaSuccess) return (int)e;
+            if (a.inv_out && (e = cudaMemcpyAsync(a.inv_out, inv, (size_t)a.batch * sizeof(float), cudaMemcpyDeviceToDevice, st)) != cudaSuccess) return (int)e;
+            if (a.a_out && (e = cudaMemcpyAsync(a.a_out, a8, (size_t)a.batch * a.K, cudaMemcpyDeviceToDevice, st)) != cudaSuccess) return (int)e;
+            return launch_tl1_umma(a, a8, inv, sums, st);
+        }
+        e = launch_act_quant(a.x, a.norm_w, a.do_norm, a.eps, a.K, a.batch, a.x_stride, words, inv, a.a_out, nullptr, a.use_pdl, st);
         if (e != cudaSuccess) return (int)e;
         if (a.inv_out) {
             e = cudaMemcpyAsync(a.inv_out, inv, (size_t)a.batch * sizeof(float), cudaMemcpyDeviceToDevice, st);

@@ -1,0 +1,339 @@
+// Batched TL1 bitlinear on the 5th-generation tensor cores (tcgen05.mma kind::i8, accumulators in
+// tensor memory) for sm_100a. Used by tenzo_cuda_tl1_gemv when there are at least 16 sequences.
+//
+// Replaces, for many sequences at once, the same reference code as tl1_gemv.cu
+// (src/runtime/TenzoEngine.cpp:22-166 and the call shapes :1547-1628 of the reference): integer
+// accumulators are exact, so the result is bit-identical to the one-sequence path.
+//
+//   D[128 weight rows][N sequences] (int32, TMEM) += A[128][K] (u8 codes 0,1,2) * B[K][N] (s8 activations)
+//   sum_k w*a = sum_k code*a - sum_k a          (w = code - 1; the per-sequence sum comes from the quantiser)
+//
+// One CTA per 128-row tile (two 64-row TL1 blocks; for the GLU epilogue the gate block and its up
+// block, so the activation is applied inside the CTA). K is walked in 128-byte chunks through a
+// ring of stages; per stage
+//   warp 0 (one lane)   bulk-copies the packed 2-bit weights of the chunk (2 x 2 KB) and TMA-loads the
+//                       activation tile [N][128 B] with the 128-byte swizzle the tensor core expects;
+//   warps 2-5           expand the 2-bit codes to bytes and write the A tile [128][128 B] in the same
+//                       swizzled K-major layout (a 4x4 byte transpose per 4 column pairs with PRMT, then
+//                       mask/shift/interleave), fence it to the async proxy and arrive;
+//   warp 1 (one lane)   issues four tcgen05.mma (K = 32 each) and commits them to the stage's "empty"
+//                       barrier, which is what lets the producer refill the stage.
+// After the last chunk a final commit signals the epilogue (warps 2-5: one TMEM lane = one weight
+// row per thread, tcgen05.ld 16 sequences at a time, scale / residual / ReLU^2*GLU, coalesced stores).
+// Every mbarrier wait is bounded; a wait that gives up sets g_umma_timeouts, the roles fall through
+// to the end and the TMEM allocation is released on every path.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "../../include/tenzo_kernels.h"
+
+namespace tz {
+
+constexpr int kUmmaThreads = 192;
+constexpr int kUmmaStages = 4;
+constexpr int kKc = 128;                       // bytes of K per stage (one swizzle atom row)
+constexpr int kTileRows = 128;
+constexpr int kABytes = kTileRows * kKc;       // 16 KB
+constexpr int kPBytes = 2 * (kKc / 2) * 32;    // packed weights of one chunk, two row blocks: 4 KB
+constexpr int kMaxN = 256;
+
+struct UmmaLaunch {
+    tenzo_tl1_gemv_args a;
+    const float* inv;        // [batch] m/31
+    const int* sum_a;        // [batch] sum_k a_k
+    int units;               // tiles along the rows
+    int n_box;               // sequences per CTA, padded to a multiple of 16 (<= 256)
+    int tmem_cols;           // power of two >= max(32, n_box)
+};
+
+__device__ int g_umma_timeouts = 0;
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(smem_addr(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_addr(bar)) : "memory");
+}
+// K-major operand tile, 128-byte swizzle: rows 128 bytes apart, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr) {
+    return (uint64_t)((saddr >> 4) & 0x3FFFu) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ float umma_seg_scale(const tenzo_tl1_gemv_args& a, int block) {
+    return block < a.seg_end[0] ? a.seg_scale[0] : (block < a.seg_end[1] ? a.seg_scale[1] : a.seg_scale[2]);
+}
+
+struct UmmaSmem {
+    // [1024-aligned] stages x { A 16 KB | B n_box*128 | P 4 KB } | barriers | tmem slot | GLU exchange [16][64] floats
+    static __host__ __device__ int stage_bytes(int n_box) { return kABytes + n_box * kKc + kPBytes; }
+    static __host__ __device__ size_t bytes(int n_box) { return 1024 + (size_t)kUmmaStages * stage_bytes(n_box) + 8 * (3 * kUmmaStages + 1) + 16 + 16 * 64 * 4; }
+};
+
+__global__ void __launch_bounds__(kUmmaThreads, 1) tl1_umma_kernel(const UmmaLaunch L, const __grid_constant__ CUtensorMap amap) {
+    const tenzo_tl1_gemv_args& a = L.a;
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t base_off = ((smem_addr(smem_raw) + 1023u) & ~1023u) - smem_addr(smem_raw);
+    unsigned char* stages = smem_raw + base_off;
+    const int stage_bytes = UmmaSmem::stage_bytes(L.n_box);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(stages + (size_t)kUmmaStages * stage_bytes);
+    uint64_t* bar_raw = bars;                          // packed weights + activation tile have landed
+    uint64_t* bar_ready = bars + kUmmaStages;          // A tile expanded (128 arrivals)
+    uint64_t* bar_empty = bars + 2 * kUmmaStages;      // the stage's MMAs have completed
+    uint64_t* bar_accum = bars + 3 * kUmmaStages;      // all MMAs have completed
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * kUmmaStages + 1);
+    float* s_glu = reinterpret_cast<float*>(tmem_slot + 4);   // [16][64]
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const bool glu = a.epilogue == TENZO_EPI_RELU2_GLU;
+    const int tile = blockIdx.x, seq0 = blockIdx.y * kMaxN;
+    const int blk0 = glu ? tile : 2 * tile;
+    const int blk1 = glu ? tile + L.units : (2 * tile + 1 < a.n_blocks ? 2 * tile + 1 : -1);
+    const int n_chunks = a.K / kKc;
+    const int N = L.n_box;
+
+    if (tid == 0) {
+        for (int s = 0; s < kUmmaStages; ++s) {
+            mbar_init(&bar_raw[s], 1);
+            mbar_init(&bar_ready[s], 128);
+            mbar_init(&bar_empty[s], 1);
+        }
+        mbar_init(bar_accum, 1);
+        mbar_init_fence();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(L.tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+    if (a.use_pdl) {
+        pdl_wait();
+        pdl_launch_dependents();
+    }
+    bool timed_out = false;
+
+    if (warp == 0) {
+        // ---- producer -----------------------------------------------------------------------------
+        if (lane == 0) {
+            const size_t blk_bytes = (size_t)(a.K / 2) * 32;
+            for (int j = 0; j < n_chunks; ++j) {
+                const int s = j % kUmmaStages, use = j / kUmmaStages;
+                if (use > 0 && !mbar_wait_bounded(&bar_empty[s], (unsigned)(use - 1) & 1u)) { timed_out = true; break; }
+                unsigned char* st = stages + (size_t)s * stage_bytes;
+                unsigned char* sP = st + kABytes + N * kKc;
+                mbar_expect_tx(&bar_raw[s], (unsigned)(N * kKc + (blk1 >= 0 ? kPBytes : kPBytes / 2)));
+                bulk_g2s(sP, a.w + (size_t)blk0 * blk_bytes + (size_t)j * (kPBytes / 2), kPBytes / 2, &bar_raw[s]);
+                if (blk1 >= 0) bulk_g2s(sP + kPBytes / 2, a.w + (size_t)blk1 * blk_bytes + (size_t)j * (kPBytes / 2), kPBytes / 2, &bar_raw[s]);
+                tma_load_2d(st + kABytes, &amap, j * kKc, seq0, &bar_raw[s]);
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issue ------------------------------------------------------------------------------
+        if (lane == 0) {
+            // c = s32, a = u8, b = s8, both K-major, N at bit 17 (>>3), M at bit 24 (>>4)
+            const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(kTileRows >> 4) << 24);
+            for (int j = 0; j < n_chunks; ++j) {
+                const int s = j % kUmmaStages, use = j / kUmmaStages;
+                if (!mbar_wait_bounded(&bar_ready[s], (unsigned)use & 1u)) { timed_out = true; break; }
+                tc_fence_after();
+                const uint32_t sa = smem_addr(stages + (size_t)s * stage_bytes);
+                const uint64_t da = umma_desc_sw128(sa), db = umma_desc_sw128(sa + kABytes);
+#pragma unroll
+                for (int k4 = 0; k4 < kKc / 32; ++k4)
+                    umma_i8(tmem_base, da + (uint64_t)(2 * k4), db + (uint64_t)(2 * k4), idesc, (j > 0 || k4 > 0) ? 1u : 0u);
+                umma_commit(&bar_empty[s]);
+            }
+            umma_commit(bar_accum);
+        }
+    } else {
+        // ---- expand the 2-bit codes into the A tile ---------------------------------------------------
+        const int ut = tid - 64;                          // 0..127
+        const int c4 = ut & 7, kk8 = (ut >> 3) & 7, blk = ut >> 6;
+        for (int j = 0; j < n_chunks; ++j) {
+            const int s = j % kUmmaStages, use = j / kUmmaStages;
+            bool ok = true;
+            if (lane == 0) ok = mbar_wait_bounded(&bar_raw[s], (unsigned)use & 1u);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) { timed_out = true; break; }
+            unsigned char* st = stages + (size_t)s * stage_bytes;
+            const uint32_t* sP = reinterpret_cast<const uint32_t*>(st + kABytes + N * kKc) + blk * (kPBytes / 8);
+            uint32_t W[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) W[i] = (blk == 1 && blk1 < 0) ? 0u : sP[(8 * kk8 + i) * 8 + c4];
+            // 4x4 byte transposes: T[h][jj] = bytes (W[4h+0].jj, W[4h+1].jj, W[4h+2].jj, W[4h+3].jj): column pair 8*kk8+4h.. of byte column 4*c4+jj
+            uint32_t T[2][4];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint32_t p0 = prmt(W[4 * h], W[4 * h + 1], 0x5140u), p1 = prmt(W[4 * h + 2], W[4 * h + 3], 0x5140u);
+                const uint32_t p2 = prmt(W[4 * h], W[4 * h + 1], 0x7362u), p3 = prmt(W[4 * h + 2], W[4 * h + 3], 0x7362u);
+                T[h][0] = prmt(p0, p1, 0x5410u); T[h][1] = prmt(p0, p1, 0x7632u);
+                T[h][2] = prmt(p2, p3, 0x5410u); T[h][3] = prmt(p2, p3, 0x7632u);
+            }
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+#pragma unroll
+                for (int hi = 0; hi < 2; ++hi) {            // low nibble: row 4*c4+jj, high nibble: row 32+4*c4+jj
+                    uint4 o;
+                    uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const uint32_t n = T[h][jj] >> (4 * hi);
+                        const uint32_t e0 = n & 0x03030303u, e1 = (n >> 2) & 0x03030303u;   // codes of the even / odd columns
+                        ow[2 * h] = prmt(e0, e1, 0x5140u);
+                        ow[2 * h + 1] = prmt(e0, e1, 0x7362u);
+                    }
+                    const int row = blk * 64 + hi * 32 + 4 * c4 + jj;
+                    *reinterpret_cast<uint4*>(st + row * kKc + ((kk8 ^ (row & 7)) << 4)) = o;
+                }
+            }
+            fence_proxy_async_smem();
+            mbar_arrive(&bar_ready[s]);
+        }
+
+        // ---- epilogue: TMEM lane = weight row -------------------------------------------------------
+        bool ok = true;
+        if (lane == 0) ok = !timed_out && mbar_wait_bounded(bar_accum, 0u);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) timed_out = true;
+        tc_fence_after();
+        const int q = warp & 3;                              // this warp may touch TMEM lanes 32q..32q+31
+        const int row = 32 * q + lane, rblk = row >> 6, rr = row & 63;
+        const int block = rblk ? blk1 : blk0;
+        const float wscale = block >= 0 ? umma_seg_scale(a, block) : 0.0f;
+        for (int c0 = 0; c0 < N; c0 += 16) {
+            uint32_t r[16];
+            if (ok) tmem_ld16(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)c0, r);
+            float v[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int seq = seq0 + c0 + i;
+                v[i] = 0.0f;
+                if (ok && seq < a.batch && block >= 0) {
+                    const int accv = (int)r[i] - __ldg(L.sum_a + seq);
+                    if (a.acc_out) a.acc_out[(size_t)seq * a.n_blocks * 64 + block * 64 + rr] = accv;
+                    v[i] = (float)accv * (__ldg(L.inv + seq) * wscale);      // :1554, :118
+                }
+            }
+            if (glu) {
+                if (rblk == 1) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) s_glu[i * 64 + rr] = v[i];
+                }
+                named_barrier_sync(1, 128);
+                if (rblk == 0) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const int seq = seq0 + c0 + i;
+                        if (ok && seq < a.batch) {
+                            const float rl = fmaxf(0.0f, v[i]);
+                            a.out[(size_t)seq * a.out_stride + tile * 64 + rr] = (rl * rl) * s_glu[i * 64 + rr];   // :1618-1619
+                        }
+                    }
+                }
+                named_barrier_sync(1, 128);
+            } else if (block >= 0) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int seq = seq0 + c0 + i;
+                    if (ok && seq < a.batch) {
+                        const size_t o = (size_t)seq * a.out_stride + block * 64 + rr;
+                        a.out[o] = a.epilogue == TENZO_EPI_RESIDUAL ? __ldcg(a.resid + o) + v[i] : v[i];   // :1590
+                    }
+                }
+            }
+        }
+    }
+    if (timed_out) atomicExch(&g_umma_timeouts, 1);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(L.tmem_cols) : "memory");
+    }
+}
+
+// Activations [batch][K] int8 as a 2-D tensor for the B-operand tile loads.
+static int make_act_tensor_map(const int8_t* a8, int K, int batch, int n_box, CUtensorMap* out) {
+    typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = nullptr;
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr) != cudaSuccess || qr != cudaDriverEntryPointSuccess || !fn)
+            return -4;
+        encode = reinterpret_cast<EncodeFn>(fn);
+    }
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)batch};
+    const cuuint64_t strides[1] = {(cuuint64_t)K};
+    const cuuint32_t box[2] = {(cuuint32_t)kKc, (cuuint32_t)n_box};
+    const cuuint32_t estr[2] = {1u, 1u};
+    const CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(a8), dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : -4;
+}
+
+bool tl1_umma_applicable(const tenzo_tl1_gemv_args& a) { return a.batch >= 16 && a.K % kKc == 0 && a.K >= kKc; }
+
+// a8 [batch][K] int8 (16-byte aligned), inv [batch], sum_a [batch] already produced on `st`.
+int launch_tl1_umma(const tenzo_tl1_gemv_args& a, const int8_t* a8, const float* inv, const int* sum_a, cudaStream_t st) {
+    UmmaLaunch L;
+    L.a = a;
+    L.inv = inv;
+    L.sum_a = sum_a;
+    const bool glu = a.epilogue == TENZO_EPI_RELU2_GLU;
+    L.units = glu ? a.n_blocks / 2 : (a.n_blocks + 1) / 2;
+    const int per_cta = a.batch < kMaxN ? a.batch : kMaxN;
+    L.n_box = (per_cta + 15) & ~15;
+    L.tmem_cols = 32;
+    while (L.tmem_cols < L.n_box) L.tmem_cols *= 2;
+    CUtensorMap amap;
+    if (int rc = make_act_tensor_map(a8, a.K, a.batch, L.n_box, &amap)) return rc;
+    const size_t smem = UmmaSmem::bytes(L.n_box);
+    cudaError_t e = cudaFuncSetAttribute(tl1_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)L.units, (unsigned)((a.batch + kMaxN - 1) / kMaxN), 1);
+    cfg.blockDim = dim3(kUmmaThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = a.use_pdl ? 1 : 0;
+    e = cudaLaunchKernelEx(&cfg, tl1_umma_kernel, L, amap);
+    return e == cudaSuccess ? 0 : (int)e;
+}
+
+int tl1_umma_take_timeouts() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_umma_timeouts, sizeof v) != cudaSuccess) return -1;
+    if (v) cudaMemcpyToSymbol(g_umma_timeouts, &zero, sizeof zero);
+    return v;
+}
+
+}  // namespace tz

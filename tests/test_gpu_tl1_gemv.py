@@ -149,3 +149,57 @@ def test_argument_errors(cuda_lib):
         kernels.tl1_gemv(x, w[1:], 1, 64, [1.0])       # misaligned weights
     with pytest.raises(RuntimeError):
         kernels.tl1_gemv(x, w, 1, 64, [1.0], epilogue=kernels.EPI_RESIDUAL)   # residual missing
+
+
+@pytest.mark.parametrize("N,K,batch", [(128, 128, 16), (192, 256, 40), (640, 2560, 64), (2560, 6912, 256), (256, 384, 300), (128, 16384, 17)])
+def test_tensor_core_path_bit_exact(cuda_lib, N, K, batch):
+    """16 or more sequences with K a multiple of 128 run on tcgen05 (codes 0..2 as u8, activations s8,
+    int32 accumulators in tensor memory): accumulators, quantised activations and outputs equal the oracle's."""
+    from tenzo_b200 import kernels
+    rng = np.random.default_rng([45, N, K, batch])
+    w = synth.random_tl1_packed(rng, N, K)
+    x = (rng.standard_normal((batch, K)) * np.float32(10.0) ** rng.integers(-2, 3, (batch, 1))).astype(np.float32)
+    scale = float(synth.weight_scale(rng))
+    r = kernels.tl1_gemv(dev(x), dev(w), N // 64, K, [scale], want_acc=True, want_act=True)
+    torch.cuda.synchronize()
+    assert cuda_lib.tenzo_cuda_tl1_gemv_take_timeouts() == 0
+    O = ora.load_oracle()
+    check = range(batch) if N * K * batch <= 640 * 2560 * 64 else [0, 1, 15, 16, batch // 2, batch - 2, batch - 1]
+    for b in check:
+        out, acc, inv = cpu_bitlinear(x[b], w, N, K, scale)
+        a = np.zeros(K, np.int8)
+        O.ora_act_quant31(P(x[b], ora.c_f32p), K, P(a, ora.c_i8p))
+        assert np.array_equal(host(r["a"])[b], a), "quantised activations differ"
+        assert np.float32(host(r["inv"])[b]) == inv
+        assert np.array_equal(host(r["acc"])[b], acc), f"int32 accumulators differ (sequence {b})"
+        assert np.array_equal(host(r["out"])[b], out), "fp32 outputs differ"
+
+
+def test_tensor_core_path_epilogues_match_single_sequence_path(cuda_lib):
+    """Segment scales + fused norm, residual and ReLU^2*GLU epilogues at 48 sequences against the same
+    launches made one sequence at a time (already pinned to the oracle above)."""
+    from tenzo_b200 import kernels
+    h, f, B = 512, 704, 48
+    rng = np.random.default_rng(46)
+    x = rng.standard_normal((B, h)).astype(np.float32)
+    res = rng.standard_normal((B, h)).astype(np.float32)
+    nw = (1 + 0.1 * rng.standard_normal(h)).astype(np.float32)
+    wo = dev(synth.random_tl1_packed(rng, h, h))
+    wgu = dev(np.concatenate([synth.random_tl1_packed(rng, f, h), synth.random_tl1_packed(rng, f, h)]))
+    wqkv = dev(np.concatenate([synth.random_tl1_packed(rng, n, h) for n in (512, 128, 128)]))
+    dx, dres, dnw = dev(x), dev(res), dev(nw)
+
+    def launches(xs, rs):
+        o = kernels.tl1_gemv(xs, wo, h // 64, h, [0.02], epilogue=kernels.EPI_RESIDUAL, resid=rs, norm_w=dnw, do_norm=True)["out"]
+        g = kernels.tl1_gemv(xs, wgu, 2 * f // 64, h, [0.02, 0.03], [f // 64, 2 * f // 64, 2 * f // 64], epilogue=kernels.EPI_RELU2_GLU)["out"]
+        q = kernels.tl1_gemv(xs, wqkv, 12, h, [0.011, 0.017, 0.023], [8, 10, 12], norm_w=dnw, do_norm=True)["out"]
+        return o, g, q
+
+    big = launches(dx, dres)
+    torch.cuda.synchronize()
+    for b in [0, 7, 16, 33, 47]:
+        one = launches(dx[b:b + 1].contiguous(), dres[b:b + 1].contiguous())
+        torch.cuda.synchronize()
+        for got, want, name in zip(big, one, ("residual", "glu", "qkv")):
+            assert np.array_equal(host(got)[b], host(want)[0]), f"{name} epilogue differs at sequence {b}"
+    assert cuda_lib.tenzo_cuda_tl1_gemv_take_timeouts() == 0
