@@ -80,6 +80,22 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, unsigned parity
 // Barrier among `count` threads (a multiple of 32) of the CTA; id 1..15 (0 is __syncthreads).
 __device__ __forceinline__ void named_barrier_sync(int id, int count) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory"); }
 
+// One non-blocking look at phase `parity` of an mbarrier.
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, unsigned parity) {
+    uint32_t done;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(done) : "r"(smem_addr(bar)), "r"(parity) : "memory");
+    return done != 0;
+}
+
+// Bounded wait by polling test_wait (no hardware suspend between polls): lower wake-up latency than
+// mbar_wait_bounded, for the hand-offs inside a software pipeline. Returns false on give-up.
+__device__ __forceinline__ bool mbar_spin_bounded(uint64_t* bar, unsigned parity) {
+    for (int it = 0; it < (1 << 24); ++it)
+        if (mbar_test(bar, parity)) return true;
+    return false;
+}
+
 // Programmatic dependent launch: wait until the kernels this one depends on have completed and
 // their memory is visible / allow the next kernel in the stream to begin its own prologue.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }

@@ -9,11 +9,12 @@
 //   sum_k w*a = sum_k code*a - sum_k a          (w = code - 1; the per-sequence sum comes from the quantiser)
 //
 // One CTA per 128-row tile (two 64-row TL1 blocks; for the GLU epilogue the gate block and its up
-// block, so the activation is applied inside the CTA). K is walked in 128-byte chunks through a
-// ring of stages; per stage
-//   warp 0 (one lane)   bulk-copies the packed 2-bit weights of the chunk (2 x 2 KB) and TMA-loads the
-//                       activation tile [N][128 B] with the 128-byte swizzle the tensor core expects;
-//   warps 2-5           expand the 2-bit codes to bytes and write the A tile [128][128 B] in the same
+// block, so the activation is applied inside the CTA). K is walked in 128-byte chunks; per chunk
+//   warp 0 (one lane)   bulk-copies the packed 2-bit weights eight chunks at a time (2 x 16 KB; issuing a copy
+//                       costs a few hundred cycles, so few large ones) into a two-group ring (64 KB in flight
+//                       per CTA covers HBM latency) and TMA-loads the activation tile
+//                       [N][128 B] into a 3- or 4-stage ring with the 128-byte swizzle the tensor core expects;
+//   warps 2-5 / 6-9     (alternate chunks) expand the 2-bit codes to bytes and write the A tile [128][128 B] in the same
 //                       swizzled K-major layout (a 4x4 byte transpose per 4 column pairs with PRMT, then
 //                       mask/shift/interleave), fence it to the async proxy and arrive;
 //   warp 1 (one lane)   issues four tcgen05.mma (K = 32 each) and commits them to the stage's "empty"
@@ -29,8 +30,10 @@
 
 namespace tz {
 
-constexpr int kUmmaThreads = 192;
-constexpr int kUmmaStages = 4;
+constexpr int kUmmaThreads = 320;              // warp 0 producer, warp 1 MMA, warps 2-5 and 6-9 expand alternate chunks
+constexpr int kMaxStages = 4;                  // A/B tile stages (3 when the activation tile is 32 KB)
+constexpr int kPGroup = 8;                     // chunks of packed weights per bulk copy (16 KB per row block)
+constexpr int kPGroups = 2;                    // such groups in the ring: up to 64 KB of packed weights in flight
 constexpr int kKc = 128;                       // bytes of K per stage (one swizzle atom row)
 constexpr int kTileRows = 128;
 constexpr int kABytes = kTileRows * kKc;       // 16 KB
@@ -44,9 +47,11 @@ struct UmmaLaunch {
     int units;               // tiles along the rows
     int n_box;               // sequences per CTA, padded to a multiple of 16 (<= 256)
     int tmem_cols;           // power of two >= max(32, n_box)
+    int n_stages;            // A/B tile stages
 };
 
 __device__ int g_umma_timeouts = 0;
+
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
@@ -83,24 +88,34 @@ __device__ __forceinline__ float umma_seg_scale(const tenzo_tl1_gemv_args& a, in
 }
 
 struct UmmaSmem {
-    // [1024-aligned] stages x { A 16 KB | B n_box*128 | P 4 KB } | barriers | tmem slot | GLU exchange [16][64] floats
-    static __host__ __device__ int stage_bytes(int n_box) { return kABytes + n_box * kKc + kPBytes; }
-    static __host__ __device__ size_t bytes(int n_box) { return 1024 + (size_t)kUmmaStages * stage_bytes(n_box) + 8 * (3 * kUmmaStages + 1) + 16 + 16 * 64 * 4; }
+    // [1024-aligned] stages x { A 16 KB | B n_box*128 } | packed ring kPGroups x 2 blocks x 16 KB | barriers | tmem slot | GLU exchange [16][64] floats | inv[256] | sum_a[256]
+    static __host__ __device__ int stage_bytes(int n_box) { return kABytes + n_box * kKc; }
+    static __host__ __device__ int stages_for(int n_box) { return n_box > 128 ? 3 : kMaxStages; }
+    static constexpr int n_bars = 3 * kMaxStages + 2 * kPGroups + 1;
+    static __host__ __device__ size_t bytes(int n_box) {
+        return 1024 + (size_t)stages_for(n_box) * stage_bytes(n_box) + (size_t)kPGroups * kPGroup * kPBytes + ((8 * n_bars + 15) & ~15) + 16 + 16 * 64 * 4 + 2 * kMaxN * 4;
+    }
 };
 
-__global__ void __launch_bounds__(kUmmaThreads, 1) tl1_umma_kernel(const UmmaLaunch L, const __grid_constant__ CUtensorMap amap) {
+__global__ void __launch_bounds__(kUmmaThreads, 1) tl1_umma_kernel(const UmmaLaunch L, const __grid_constant__ CUtensorMap amap,
+                                                                   const __grid_constant__ CUtensorMap omap) {
     const tenzo_tl1_gemv_args& a = L.a;
     extern __shared__ unsigned char smem_raw[];
     const uint32_t base_off = ((smem_addr(smem_raw) + 1023u) & ~1023u) - smem_addr(smem_raw);
     unsigned char* stages = smem_raw + base_off;
-    const int stage_bytes = UmmaSmem::stage_bytes(L.n_box);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(stages + (size_t)kUmmaStages * stage_bytes);
-    uint64_t* bar_raw = bars;                          // packed weights + activation tile have landed
-    uint64_t* bar_ready = bars + kUmmaStages;          // A tile expanded (128 arrivals)
-    uint64_t* bar_empty = bars + 2 * kUmmaStages;      // the stage's MMAs have completed
-    uint64_t* bar_accum = bars + 3 * kUmmaStages;      // all MMAs have completed
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * kUmmaStages + 1);
+    const int stage_bytes = UmmaSmem::stage_bytes(L.n_box), S = L.n_stages;
+    unsigned char* pring = stages + (size_t)S * stage_bytes;                  // [kPGroups][2 row blocks][kPGroup chunks][64][32] packed weights
+    uint64_t* bars = reinterpret_cast<uint64_t*>(pring + (size_t)kPGroups * kPGroup * kPBytes);
+    uint64_t* bar_raw = bars;                          // [S] activation tile has landed
+    uint64_t* bar_ready = bars + kMaxStages;           // [S] A tile expanded (one arrival per expanding warp)
+    uint64_t* bar_empty = bars + 2 * kMaxStages;       // [S] the stage's MMAs have completed
+    uint64_t* bar_p = bars + 3 * kMaxStages;           // [kPGroups] packed weights have landed
+    uint64_t* bar_pfree = bar_p + kPGroups;            // [kPGroups] packed weights consumed (one arrival per expanding warp per chunk)
+    uint64_t* bar_accum = bar_pfree + kPGroups;        // all MMAs have completed
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned char*>(bars) + ((8 * UmmaSmem::n_bars + 15) & ~15));   // 16-byte aligned
     float* s_glu = reinterpret_cast<float*>(tmem_slot + 4);   // [16][64]
+    float* s_inv = s_glu + 16 * 64;                           // [kMaxN] m/31 of this CTA's sequences
+    int* s_sum = reinterpret_cast<int*>(s_inv + kMaxN);       // [kMaxN] sum_k a_k
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const bool glu = a.epilogue == TENZO_EPI_RELU2_GLU;
@@ -111,14 +126,19 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) tl1_umma_kernel(const UmmaLau
     const int N = L.n_box;
 
     if (tid == 0) {
-        for (int s = 0; s < kUmmaStages; ++s) {
+        for (int s = 0; s < S; ++s) {
             mbar_init(&bar_raw[s], 1);
-            mbar_init(&bar_ready[s], 128);
+            mbar_init(&bar_ready[s], 4);
             mbar_init(&bar_empty[s], 1);
+        }
+        for (int s = 0; s < kPGroups; ++s) {
+            mbar_init(&bar_p[s], 1);
+            mbar_init(&bar_pfree[s], 4 * kPGroup);
         }
         mbar_init(bar_accum, 1);
         mbar_init_fence();
     }
+    l2_prefetch_slice(a.prefetch, a.prefetch_bytes);       // the next kernel's weights
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(L.tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -132,20 +152,38 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) tl1_umma_kernel(const UmmaLau
         pdl_launch_dependents();
     }
     bool timed_out = false;
+    for (int i = tid; i < N; i += kUmmaThreads) {              // per-sequence epilogue operands (read after the final barrier)
+        const int seq = seq0 + i;
+        s_inv[i] = seq < a.batch ? __ldcg(L.inv + seq) : 0.0f;
+        s_sum[i] = seq < a.batch ? __ldcg(L.sum_a + seq) : 0;
+    }
+    __syncthreads();
 
     if (warp == 0) {
         // ---- producer -----------------------------------------------------------------------------
         if (lane == 0) {
             const size_t blk_bytes = (size_t)(a.K / 2) * 32;
-            for (int j = 0; j < n_chunks; ++j) {
-                const int s = j % kUmmaStages, use = j / kUmmaStages;
-                if (use > 0 && !mbar_wait_bounded(&bar_empty[s], (unsigned)(use - 1) & 1u)) { timed_out = true; break; }
-                unsigned char* st = stages + (size_t)s * stage_bytes;
-                unsigned char* sP = st + kABytes + N * kKc;
-                mbar_expect_tx(&bar_raw[s], (unsigned)(N * kKc + (blk1 >= 0 ? kPBytes : kPBytes / 2)));
-                bulk_g2s(sP, a.w + (size_t)blk0 * blk_bytes + (size_t)j * (kPBytes / 2), kPBytes / 2, &bar_raw[s]);
-                if (blk1 >= 0) bulk_g2s(sP + kPBytes / 2, a.w + (size_t)blk1 * blk_bytes + (size_t)j * (kPBytes / 2), kPBytes / 2, &bar_raw[s]);
-                tma_load_2d(st + kABytes, &amap, j * kKc, seq0, &bar_raw[s]);
+            int gp = 0;                                   // next group of packed chunks to request
+            const int n_groups = (n_chunks + kPGroup - 1) / kPGroup;
+            for (int j = 0; j < n_chunks && !timed_out; ++j) {
+                for (; gp < n_groups && gp <= j / kPGroup + 1; ++gp) {
+                    const int slot = gp % kPGroups, guse = gp / kPGroups;
+                    if (guse > 0 && !mbar_test(&bar_pfree[slot], (unsigned)(guse - 1) & 1u)) {
+                        if (gp > j / kPGroup) break;               // the group after the current one: do not hold up the activation tiles
+                        if (!mbar_spin_bounded(&bar_pfree[slot], (unsigned)(guse - 1) & 1u)) { timed_out = true; break; }
+                    }
+                    const int chunks = min(kPGroup, n_chunks - gp * kPGroup);
+                    const unsigned bytes = (unsigned)chunks * (kPBytes / 2);
+                    unsigned char* sP = pring + (size_t)slot * kPGroup * kPBytes;
+                    mbar_expect_tx(&bar_p[slot], blk1 >= 0 ? 2 * bytes : bytes);
+                    bulk_g2s(sP, a.w + (size_t)blk0 * blk_bytes + (size_t)gp * kPGroup * (kPBytes / 2), bytes, &bar_p[slot]);
+                    if (blk1 >= 0) bulk_g2s(sP + kPGroup * (kPBytes / 2), a.w + (size_t)blk1 * blk_bytes + (size_t)gp * kPGroup * (kPBytes / 2), bytes, &bar_p[slot]);
+                }
+                if (timed_out) break;
+                const int s = j % S, use = j / S;
+                if (use > 0 && !mbar_spin_bounded(&bar_empty[s], (unsigned)(use - 1) & 1u)) { timed_out = true; break; }
+                mbar_expect_tx(&bar_raw[s], (unsigned)(N * kKc));
+                tma_load_2d(stages + (size_t)s * stage_bytes + kABytes, &amap, j * kKc, seq0, &bar_raw[s]);
             }
         }
     } else if (warp == 1) {
@@ -154,8 +192,9 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) tl1_umma_kernel(const UmmaLau
             // c = s32, a = u8, b = s8, both K-major, N at bit 17 (>>3), M at bit 24 (>>4)
             const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(kTileRows >> 4) << 24);
             for (int j = 0; j < n_chunks; ++j) {
-                const int s = j % kUmmaStages, use = j / kUmmaStages;
-                if (!mbar_wait_bounded(&bar_ready[s], (unsigned)use & 1u)) { timed_out = true; break; }
+                const int s = j % S, use = j / S;
+                if (!mbar_spin_bounded(&bar_ready[s], (unsigned)use & 1u)) { timed_out = true; break; }
+                if (!mbar_spin_bounded(&bar_raw[s], (unsigned)use & 1u)) { timed_out = true; break; }
                 tc_fence_after();
                 const uint32_t sa = smem_addr(stages + (size_t)s * stage_bytes);
                 const uint64_t da = umma_desc_sw128(sa), db = umma_desc_sw128(sa + kABytes);
@@ -168,16 +207,22 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) tl1_umma_kernel(const UmmaLau
         }
     } else {
         // ---- expand the 2-bit codes into the A tile ---------------------------------------------------
-        const int ut = tid - 64;                          // 0..127
-        const int c4 = ut & 7, kk8 = (ut >> 3) & 7, blk = ut >> 6;
-        for (int j = 0; j < n_chunks; ++j) {
-            const int s = j % kUmmaStages, use = j / kUmmaStages;
+        // lane bits 0-1: kk8 & 3, bit 2: c4 & 1, bits 3-4: c4 >> 1; warp: kk8 >> 2 and the row block. A quarter
+        // warp then stores eight different 16-byte chunk positions (no bank conflicts on the A tile).
+        const int uw = (warp - 2) & 3, grp = (warp - 2) >> 2;   // two groups of four warps take alternate chunks
+        const int kk8 = (lane & 3) | ((uw & 1) << 2), c4 = ((lane >> 2) & 1) | (((lane >> 3) & 3) << 1), blk = uw >> 1;
+        int seen_group = -1;
+        for (int j = grp; j < n_chunks; j += 2) {
+            const int s = j % S, use = j / S, ps = (j / kPGroup) % kPGroups, puse = (j / kPGroup) / kPGroups;
             bool ok = true;
-            if (lane == 0) ok = mbar_wait_bounded(&bar_raw[s], (unsigned)use & 1u);
+            if (lane == 0 && (j / kPGroup != seen_group)) ok = mbar_spin_bounded(&bar_p[ps], (unsigned)puse & 1u);
+            seen_group = j / kPGroup;
+            if (lane == 0 && ok) ok = (use == 0 || mbar_spin_bounded(&bar_empty[s], (unsigned)(use - 1) & 1u));
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) { timed_out = true; break; }
             unsigned char* st = stages + (size_t)s * stage_bytes;
-            const uint32_t* sP = reinterpret_cast<const uint32_t*>(st + kABytes + N * kKc) + blk * (kPBytes / 8);
+            const uint32_t* sP = reinterpret_cast<const uint32_t*>(pring + (size_t)ps * kPGroup * kPBytes + (size_t)blk * kPGroup * (kPBytes / 2) +
+                                                                   (size_t)(j % kPGroup) * (kPBytes / 2));
             uint32_t W[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) W[i] = (blk == 1 && blk1 < 0) ? 0u : sP[(8 * kk8 + i) * 8 + c4];
@@ -190,6 +235,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) tl1_umma_kernel(const UmmaLau
                 T[h][0] = prmt(p0, p1, 0x5410u); T[h][1] = prmt(p0, p1, 0x7632u);
                 T[h][2] = prmt(p2, p3, 0x5410u); T[h][3] = prmt(p2, p3, 0x7632u);
             }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar_pfree[ps]);   // the packed chunk has been consumed into registers
 #pragma unroll
             for (int jj = 0; jj < 4; ++jj) {
 #pragma unroll
@@ -208,12 +255,14 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) tl1_umma_kernel(const UmmaLau
                 }
             }
             fence_proxy_async_smem();
-            mbar_arrive(&bar_ready[s]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar_ready[s]);
         }
+        if (grp == 0) {
 
         // ---- epilogue: TMEM lane = weight row -------------------------------------------------------
         bool ok = true;
-        if (lane == 0) ok = !timed_out && mbar_wait_bounded(bar_accum, 0u);
+        if (lane == 0) ok = !timed_out && mbar_spin_bounded(bar_accum, 0u);
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) timed_out = true;
         tc_fence_after();
@@ -221,19 +270,40 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) tl1_umma_kernel(const UmmaLau
         const int row = 32 * q + lane, rblk = row >> 6, rr = row & 63;
         const int block = rblk ? blk1 : blk0;
         const float wscale = block >= 0 ? umma_seg_scale(a, block) : 0.0f;
+        // Output tile [N sequences][128 rows] (GLU: [N][64]) is assembled in the stage memory the
+        // pipeline no longer needs, one row per thread, and leaves through one TMA store: rows of
+        // 512 (256) contiguous bytes per sequence, clipped at the matrix edge by the tensor map.
+        float* s_out = reinterpret_cast<float*>(stages);
         for (int c0 = 0; c0 < N; c0 += 16) {
             uint32_t r[16];
             if (ok) tmem_ld16(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)c0, r);
+            int sums[16];
+            float invs[16], res[16];
+#pragma unroll
+            for (int i = 0; i < 16; i += 4) {
+                const int4 sv = *reinterpret_cast<const int4*>(s_sum + c0 + i);
+                const float4 iv = *reinterpret_cast<const float4*>(s_inv + c0 + i);
+                sums[i] = sv.x; sums[i + 1] = sv.y; sums[i + 2] = sv.z; sums[i + 3] = sv.w;
+                invs[i] = iv.x; invs[i + 1] = iv.y; invs[i + 2] = iv.z; invs[i + 3] = iv.w;
+            }
+            if (a.epilogue == TENZO_EPI_RESIDUAL) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int seq = seq0 + c0 + i;
+                    res[i] = (seq < a.batch && block >= 0) ? __ldcg(a.resid + (size_t)seq * a.out_stride + block * 64 + rr) : 0.0f;
+                }
+            }
             float v[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-                const int seq = seq0 + c0 + i;
-                v[i] = 0.0f;
-                if (ok && seq < a.batch && block >= 0) {
-                    const int accv = (int)r[i] - __ldg(L.sum_a + seq);
-                    if (a.acc_out) a.acc_out[(size_t)seq * a.n_blocks * 64 + block * 64 + rr] = accv;
-                    v[i] = (float)accv * (__ldg(L.inv + seq) * wscale);      // :1554, :118
-                }
+                const int accv = (int)r[i] - sums[i];
+                r[i] = (uint32_t)accv;
+                v[i] = (float)accv * (invs[i] * wscale);      // :1554, :118
+            }
+            if (a.acc_out && ok && block >= 0) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                    if (seq0 + c0 + i < a.batch) a.acc_out[(size_t)(seq0 + c0 + i) * a.n_blocks * 64 + block * 64 + rr] = (int)r[i];
             }
             if (glu) {
                 if (rblk == 1) {
@@ -244,24 +314,25 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) tl1_umma_kernel(const UmmaLau
                 if (rblk == 0) {
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
-                        const int seq = seq0 + c0 + i;
-                        if (ok && seq < a.batch) {
-                            const float rl = fmaxf(0.0f, v[i]);
-                            a.out[(size_t)seq * a.out_stride + tile * 64 + rr] = (rl * rl) * s_glu[i * 64 + rr];   // :1618-1619
-                        }
+                        const float rl = fmaxf(0.0f, v[i]);
+                        s_out[(c0 + i) * 64 + rr] = (rl * rl) * s_glu[i * 64 + rr];   // :1618-1619
                     }
                 }
                 named_barrier_sync(1, 128);
-            } else if (block >= 0) {
+            } else {
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const int seq = seq0 + c0 + i;
-                    if (ok && seq < a.batch) {
-                        const size_t o = (size_t)seq * a.out_stride + block * 64 + rr;
-                        a.out[o] = a.epilogue == TENZO_EPI_RESIDUAL ? __ldcg(a.resid + o) + v[i] : v[i];   // :1590
-                    }
-                }
+                for (int i = 0; i < 16; ++i)
+                    s_out[(c0 + i) * 128 + row] = a.epilogue == TENZO_EPI_RESIDUAL ? res[i] + v[i] : v[i];   // :1590
             }
+        }
+        fence_proxy_async_smem();
+        named_barrier_sync(1, 128);
+        if (tid == 64 && ok) {
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                         ::"l"(&omap), "r"((glu ? tile : blk0) * 64), "r"(seq0), "r"(smem_addr(s_out)) : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");     // the tile has left shared memory
+        }
         }
     }
     if (timed_out) atomicExch(&g_umma_timeouts, 1);
@@ -273,8 +344,9 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) tl1_umma_kernel(const UmmaLau
     }
 }
 
-// Activations [batch][K] int8 as a 2-D tensor for the B-operand tile loads.
-static int make_act_tensor_map(const int8_t* a8, int K, int batch, int n_box, CUtensorMap* out) {
+// 2-D row-major tensor map: `inner` elements per row, `rows` rows `row_stride_bytes` apart, box {box_inner, box_rows}.
+static int encode_2d(CUtensorMap* out, CUtensorMapDataType type, const void* base, uint64_t inner, uint64_t rows, uint64_t row_stride_bytes,
+                     uint32_t box_inner, uint32_t box_rows, CUtensorMapSwizzle swizzle) {
     typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -286,17 +358,18 @@ static int make_act_tensor_map(const int8_t* a8, int K, int batch, int n_box, CU
             return -4;
         encode = reinterpret_cast<EncodeFn>(fn);
     }
-    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)batch};
-    const cuuint64_t strides[1] = {(cuuint64_t)K};
-    const cuuint32_t box[2] = {(cuuint32_t)kKc, (cuuint32_t)n_box};
+    const cuuint64_t dims[2] = {inner, rows};
+    const cuuint64_t strides[1] = {row_stride_bytes};
+    const cuuint32_t box[2] = {box_inner, box_rows};
     const cuuint32_t estr[2] = {1u, 1u};
-    const CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(a8), dims, strides, box, estr,
-                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    const CUresult r = encode(out, type, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : -4;
 }
 
-bool tl1_umma_applicable(const tenzo_tl1_gemv_args& a) { return a.batch >= 16 && a.K % kKc == 0 && a.K >= kKc; }
+bool tl1_umma_applicable(const tenzo_tl1_gemv_args& a) {
+    return a.batch >= 16 && a.K % kKc == 0 && a.K >= kKc && a.out_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(a.out) & 15) == 0;
+}
 
 // a8 [batch][K] int8 (16-byte aligned), inv [batch], sum_a [batch] already produced on `st`.
 int launch_tl1_umma(const tenzo_tl1_gemv_args& a, const int8_t* a8, const float* inv, const int* sum_a, cudaStream_t st) {
@@ -310,8 +383,15 @@ int launch_tl1_umma(const tenzo_tl1_gemv_args& a, const int8_t* a8, const float*
     L.n_box = (per_cta + 15) & ~15;
     L.tmem_cols = 32;
     while (L.tmem_cols < L.n_box) L.tmem_cols *= 2;
-    CUtensorMap amap;
-    if (int rc = make_act_tensor_map(a8, a.K, a.batch, L.n_box, &amap)) return rc;
+    L.n_stages = UmmaSmem::stages_for(L.n_box);
+    CUtensorMap amap, omap;
+    // activations [batch][K] int8: B-operand tiles {128 bytes of K, n_box sequences}, 128-byte swizzle
+    if (int rc = encode_2d(&amap, CU_TENSOR_MAP_DATA_TYPE_UINT8, a8, (uint64_t)a.K, (uint64_t)a.batch, (uint64_t)a.K, kKc, (uint32_t)L.n_box,
+                           CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+    // output [batch][n_out] fp32: store tiles {128 (GLU: 64) rows of the weight matrix, n_box sequences}
+    const uint64_t n_out = (uint64_t)(glu ? a.n_blocks / 2 : a.n_blocks) * 64;
+    if (int rc = encode_2d(&omap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a.out, n_out, (uint64_t)a.batch, (uint64_t)a.out_stride * 4, glu ? 64u : 128u,
+                           (uint32_t)L.n_box, CU_TENSOR_MAP_SWIZZLE_NONE)) return rc;
     const size_t smem = UmmaSmem::bytes(L.n_box);
     cudaError_t e = cudaFuncSetAttribute(tl1_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -325,9 +405,10 @@ int launch_tl1_umma(const tenzo_tl1_gemv_args& a, const int8_t* a8, const float*
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = a.use_pdl ? 1 : 0;
-    e = cudaLaunchKernelEx(&cfg, tl1_umma_kernel, L, amap);
+    e = cudaLaunchKernelEx(&cfg, tl1_umma_kernel, L, amap, omap);
     return e == cudaSuccess ? 0 : (int)e;
 }
+
 
 int tl1_umma_take_timeouts() {
     int v = 0, zero = 0;
