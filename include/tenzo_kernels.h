@@ -126,12 +126,16 @@ TENZO_API int tenzo_cuda_attention_heads_per_cta(int batch, int n_q, int n_kv, i
 /* ---- INT8 LM head GEMV with fused final RMSNorm + absmax(127) quantiser + argmax --------------
  * Replaces compute_logits' int8 branch (:1634-1638, :1661-1719) and the greedy branch of
  * sample_top_k_top_p (:1745-1755: first maximum wins). logits/argmax_out/acc_out optional.
- * scratch: tenzo_cuda_lm_head_scratch_bytes(batch) bytes. */
+ * scratch: tenzo_cuda_lm_head_scratch_bytes(batch) bytes, 16-byte aligned. With 16 or more sequences, hidden a
+ * multiple of 128 and vocab <= 262144 the product runs on the tensor cores (tcgen05 kind::i8): the activations are
+ * normalised and quantised once, the vocabulary matrix is read once for all sequences; results are identical. */
 TENZO_API int tenzo_cuda_lm_head_i8(const float* x, const float* norm_w, int do_norm, float eps,
                                     const int8_t* w, const float* row_scales, int vocab, int hidden,
                                     int batch, int x_stride, float* logits, int32_t* acc_out,
                                     int* argmax_out, void* scratch, int use_pdl, void* stream);
 TENZO_API size_t tenzo_cuda_lm_head_scratch_bytes(int batch);
+/* As tenzo_cuda_tl1_gemv_take_timeouts, for the bounded waits of the tensor-core LM head (16 or more sequences). */
+TENZO_API int tenzo_cuda_lm_head_take_timeouts(void);
 
 /* ---- LM head without any allocation -------------------------------------------------------------
  * No counterpart in the reference. Same computation and results as tenzo_cuda_lm_head_i8, for

@@ -83,7 +83,7 @@ KERNEL_SYMBOLS = [
     "tenzo_cuda_tl1_gemv", "tenzo_cuda_tl1_gemv_ksplit", "tenzo_cuda_tl1_gemv_workspace_bytes", "tenzo_cuda_tl1_gemv_take_timeouts", "tenzo_cuda_rmsnorm_quant", "tenzo_cuda_attention_int8",
     "tenzo_cuda_attention_heads_per_cta", "tenzo_cuda_attention_take_timeouts", "tenzo_cuda_lm_head_i8", "tenzo_cuda_lm_head_scratch_bytes",
     "tenzo_cuda_embedding_i8", "tenzo_cuda_tl1_pack_rows2bit", "tenzo_cuda_lm_head_i8_static",
-    "tenzo_cuda_lm_head_static_max_batch",
+    "tenzo_cuda_lm_head_static_max_batch", "tenzo_cuda_lm_head_take_timeouts",
 ]
 HAL_SYMBOLS = ["tenzo_hal_initialize", "tenzo_hal_bitlinear_tl1_host", "tenzo_hal_rmsnorm_host", "tenzo_hal_gemm_f32_host"]
 
@@ -155,6 +155,7 @@ def declare_kernel_abi(L):
     L.tenzo_cuda_lm_head_i8_static.restype = i32
     L.tenzo_cuda_lm_head_i8_static.argtypes = [vp, vp, i32, f32, vp, vp, i32, i32, i32, i32, vp, vp, vp, i32, vp]
     L.tenzo_cuda_lm_head_static_max_batch.restype, L.tenzo_cuda_lm_head_static_max_batch.argtypes = i32, []
+    L.tenzo_cuda_lm_head_take_timeouts.restype, L.tenzo_cuda_lm_head_take_timeouts.argtypes = i32, []
     L.tenzo_cuda_lm_head_scratch_bytes.restype, L.tenzo_cuda_lm_head_scratch_bytes.argtypes = sz, [i32]
     L.tenzo_cuda_embedding_i8.restype, L.tenzo_cuda_embedding_i8.argtypes = i32, [vp, vp, i32, vp, i32, vp, i32, vp]
     L.tenzo_cuda_tl1_pack_rows2bit.restype, L.tenzo_cuda_tl1_pack_rows2bit.argtypes = i32, [vp, i32, i32, vp, vp]

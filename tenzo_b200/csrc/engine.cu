@@ -400,6 +400,7 @@ void Engine::push_state(const int* tokens) {
 void Engine::check_device_status(bool force) {
     if (!force && (++status_poll & 31) != 0) return;
     if (tenzo_cuda_attention_take_timeouts() > 0) throw std::runtime_error("an attention kernel gave up waiting for a KV copy; results are invalid");
+    if (tenzo_cuda_lm_head_take_timeouts() > 0) throw std::runtime_error("the LM head kernel gave up waiting for a tile copy; results are invalid");
     if (tenzo_cuda_tl1_gemv_take_timeouts() > 0) throw std::runtime_error("a TL1 kernel gave up waiting for its weight copy; results are invalid");
 }
 

@@ -10,6 +10,7 @@
 // memory, dp4a accumulates in int32 (exact), and the fp32 logit is (float)acc * (s_x * scale_v)
 // with the product of scales formed first, as the reference does (:1717).
 #include "common.cuh"
+#include "lm_head.cuh"
 #include "../../include/tenzo_kernels.h"
 
 namespace tz {
@@ -18,12 +19,6 @@ constexpr int kLmThreads = 256;
 constexpr int kLmWarps = kLmThreads / 32;
 constexpr int kLmCtas = 148 * 4;
 
-struct LmBest { float val; int idx; };
-
-__device__ __forceinline__ bool better(float v, int i, float bv, int bi) {
-    // greedy argmax keeps the first maximum (:1749 strict '>'): larger value, or same value at a lower index
-    return v > bv || (v == bv && i < bi);
-}
 
 // Sum of squares in the reference's order (see common.cuh) computed by ONE warp over a vector in
 // shared memory: lanes 0-7 run the eight chains, the lane sums are then added left to right.
@@ -202,19 +197,46 @@ __global__ void tl1_pack_rows2bit_kernel(const uint8_t* __restrict__ raw, int N,
 
 }  // namespace tz
 
-extern "C" size_t tenzo_cuda_lm_head_scratch_bytes(int batch) {
-    return batch > 0 ? (size_t)batch * tz::kLmCtas * sizeof(tz::LmBest) : 0;
+namespace tz {
+// tensor-core path for 16 or more sequences (lm_head_umma.cu)
+bool lm_head_umma_applicable(int vocab, int hidden, int batch, const int8_t* w, const float* logits);
+int launch_lm_head_umma(const int8_t* q8, const float* sx, const int8_t* w, const float* row_scales, int vocab, int hidden, int batch,
+                        float* logits, int32_t* acc_out, LmBest* cand, int use_pdl, cudaStream_t st);
+int lm_head_umma_take_timeouts();
 }
+
+// Per sequence: argmax candidates for up to kLmuMaxTiles vocabulary tiles (covers the kLmCtas candidates of the
+// warp-per-row kernel), the quantised activation vector (hidden <= 16384) and its scale.
+extern "C" size_t tenzo_cuda_lm_head_scratch_bytes(int batch) {
+    return batch > 0 ? (size_t)batch * (tz::kLmuMaxTiles * sizeof(tz::LmBest) + 16384 + 16) + 64 : 0;
+}
+
+extern "C" int tenzo_cuda_lm_head_take_timeouts(void) { return tz::lm_head_umma_take_timeouts(); }
 
 static int lm_head_launch(const float* x, const float* norm_w, int do_norm, float eps,
                           const int8_t* w, const float* row_scales, int vocab, int hidden,
                           int batch, int x_stride, float* logits, int32_t* acc_out,
-                          int* argmax_out, void* scratch, int use_pdl, void* stream, bool allow_batched) {
+                          int* argmax_out, void* scratch, int use_pdl, void* stream, bool allow_batched, bool allow_umma) {
     using namespace tz;
     if (!x || !w || !row_scales || vocab <= 0 || hidden <= 0 || batch <= 0 || !scratch) return -1;
     if (hidden > 16384) return -5;
     if ((hidden & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) != 0) return -1;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (allow_umma && lm_head_umma_applicable(vocab, hidden, batch, w, logits)) {
+        const int n_tiles = (vocab + 127) / 128;
+        LmBest* cand = static_cast<LmBest*>(scratch);
+        int8_t* q8 = reinterpret_cast<int8_t*>(static_cast<unsigned char*>(scratch) + (((size_t)batch * n_tiles * sizeof(LmBest) + 15) & ~(size_t)15));
+        float* sx = reinterpret_cast<float*>(q8 + (size_t)batch * hidden);
+        int rc = tenzo_cuda_rmsnorm_quant(x, norm_w, do_norm, eps, hidden, 127, batch, x_stride, nullptr, q8, sx, stream);
+        if (rc) return rc;
+        rc = launch_lm_head_umma(q8, sx, w, row_scales, vocab, hidden, batch, logits, acc_out, argmax_out ? cand : nullptr, use_pdl, st);
+        if (rc) return rc;
+        if (argmax_out) {
+            argmax_finish_kernel<<<batch, 256, 0, st>>>(cand, n_tiles, argmax_out);
+            if (cudaGetLastError() != cudaSuccess) return (int)cudaErrorLaunchFailure;
+        }
+        return 0;
+    }
     const size_t hpad = ((size_t)hidden + 15) & ~(size_t)15;
     auto smem_for = [&](int ns) { return (size_t)ns * hidden * sizeof(float) + 8 * sizeof(float) + (size_t)kLmWarps * ns * sizeof(LmBest) + ns * hpad + 16; };
     const bool eight = allow_batched && batch > 1 && smem_for(8) <= 200 * 1024;   // eight sequences share each row read
@@ -251,7 +273,7 @@ extern "C" int tenzo_cuda_lm_head_i8(const float* x, const float* norm_w, int do
                                      int batch, int x_stride, float* logits, int32_t* acc_out,
                                      int* argmax_out, void* scratch, int use_pdl, void* stream) {
     return lm_head_launch(x, norm_w, do_norm, eps, w, row_scales, vocab, hidden, batch, x_stride, logits, acc_out, argmax_out,
-                          scratch, use_pdl, stream, true);
+                          scratch, use_pdl, stream, true, true);
 }
 
 // ---- allocation-free variant ------------------------------------------------------------------
@@ -293,7 +315,7 @@ extern "C" int tenzo_cuda_lm_head_i8_static(const float* x, const float* norm_w,
     void* scratch = tz::lm_static_scratch_address(&e);
     if (!scratch) return (int)e;
     return lm_head_launch(x, norm_w, do_norm, eps, w, row_scales, vocab, hidden, batch, x_stride, logits,
-                          acc_out, argmax_out, scratch, use_pdl, stream, true);
+                          acc_out, argmax_out, scratch, use_pdl, stream, true, false);   // built-in scratch: warp-per-row kernel only
 }
 
 extern "C" int tenzo_cuda_lm_head_static_max_batch(void) { return tz::kLmStaticMaxBatch; }

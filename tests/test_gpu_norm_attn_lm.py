@@ -224,6 +224,39 @@ def test_full_vocab_lm_head_properties(cuda_lib):
     assert np.array_equal(l[rows], host(acc)[0][rows].astype(np.float32) * (np.float32(host(sx)[0]) * s[rows]))
 
 
+@pytest.mark.parametrize("V,H,B", [(5000, 256, 16), (1028, 128, 40), (128256, 2560, 64), (32000, 4096, 300)])
+def test_lm_head_tensor_core_path_matches_single_sequence_path(cuda_lib, V, H, B):
+    """16 or more sequences run on tcgen05: logits, accumulators and argmax (with duplicated best rows, so the
+    first-maximum rule matters) equal the one-sequence kernel's, which the tests above pin to the reference."""
+    from tenzo_b200 import kernels
+    rng = np.random.default_rng([55, V, H, B])
+    w = rng.integers(-127, 128, (V, H), dtype=np.int8)
+    s = (0.001 + 0.001 * rng.random(V)).astype(np.float32)
+    fn = (1 + 0.1 * rng.standard_normal(H)).astype(np.float32)
+    x = rng.standard_normal((B, H)).astype(np.float32)
+    dw, ds, dfn, dx = dev(w), dev(s), dev(fn), dev(x)
+    _, _, arg0 = kernels.lm_head_i8(dx[:1].contiguous(), dw, ds, norm_w=dfn)
+    b0 = int(host(arg0)[0])
+    w[(b0 + 129) % V] = w[b0]
+    s[(b0 + 129) % V] = s[b0]                      # a later duplicate of sequence 0's best row, in another 128-row tile
+    dw, ds = dev(w), dev(s)
+    lg, acc, arg = kernels.lm_head_i8(dx, dw, ds, norm_w=dfn, want_acc=True)
+    _, _, arg_only = kernels.lm_head_i8(dx, dw, ds, norm_w=dfn, want_logits=False)
+    torch.cuda.synchronize()
+    assert cuda_lib.tenzo_cuda_lm_head_take_timeouts() == 0
+    assert np.array_equal(host(arg), host(arg_only))
+    L, A, G = host(lg), host(acc), host(arg)
+    for b in sorted({0, 1, 15, min(16, B - 1), B // 2, B - 1}):
+        l1, a1, g1 = kernels.lm_head_i8(dx[b:b + 1].contiguous(), dw, ds, norm_w=dfn, want_acc=True)
+        torch.cuda.synchronize()
+        assert np.array_equal(A[b], host(a1)[0]), f"accumulators differ (sequence {b})"
+        assert np.array_equal(L[b], host(l1)[0]), f"logits differ (sequence {b})"
+        assert int(G[b]) == int(host(g1)[0])
+    for b in range(B):
+        assert int(G[b]) == int(np.argmax(L[b]))   # numpy's argmax also keeps the first maximum
+    assert int(G[0]) == min(b0, (b0 + 129) % V)
+
+
 def test_embedding_and_repack(cuda_lib):
     from tenzo_b200 import kernels
     O = ora.load_oracle()
