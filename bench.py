@@ -18,7 +18,7 @@ explicit L2 flush is needed between steps.
   cpu_baseline  the reference's own CPU engine (compiled from its sources into oracle/_ref) on this
          box's host cores, same model, same prompt, bounded sample.
 
-Other workloads (`gemv`, `attn`, `decode_batch`) measure BASELINE configs 0, 2 and 3.
+Other workloads (`gemv`, `gemm`, `attn`, `decode_batch`) measure BASELINE configs 0, 0 at 256 sequences, 2 and 3.
 With N > 1 every rank decodes its own independent sequence(s) (no data-path collective).
 """
 from __future__ import annotations
@@ -194,7 +194,7 @@ def gemv_stack_roofline(engine, model, iters, peak):
     bytes_per_launch = per_stack * iters / launches
     sec_per_launch = ms * 1e-3 / launches
     achieved = bytes_per_launch / sec_per_launch / 1e9
-    return {"bound": "hbm", "kernel": "tl1_gemv_kernel", "achieved": achieved, "peak": peak[0], "peak_source": peak[1],
+    return {"bound": "hbm", "kernel": "tl1_mma_kernel", "achieved": achieved, "peak": peak[0], "peak_source": peak[1],
             "unit": "GB/s", "frac": achieved / peak[0], "traffic": None, "bytes_per_launch": bytes_per_launch,
             "us_per_launch": sec_per_launch * 1e6, "launches_timed": launches}
 

@@ -2,6 +2,8 @@
 
   gemv          config 0: one TL1 bitlinear GEMV 6912 x 2560 at batch 1, cycled over 64 distinct
                 seeded matrices (283 MB, larger than L2) captured in one CUDA graph.
+  gemm          the batched form of config 0: TL1 bitlinear GEMM 13824 x 2560 (gate|up of the 2B shape) for 256
+                sequences on tcgen05, cycled over 16 distinct matrices (141 MB, larger than L2).
   attn          config 2: fused INT8-KV GQA decode attention alone, batch 64, 20/5 heads, ctx 8192.
   decode_batch  config 3: batched greedy decode of the BitNet-2B shape, KV prefilled on the device.
 
@@ -68,8 +70,57 @@ def run_gemv(args):
         "data": "synthetic", "config": {"workload": f"gemv: TL1 bitlinear {N}x{K}, batch 1, {n_mat} distinct matrices per step "
                                                     f"({n_mat * N * K // 4 / 1e6:.0f} MB > L2), one graph per step", "pdl": int(args.pdl)},
         "gpu_launches": launches,
-        "roofline": {"bound": "hbm", "kernel": "tl1_gemv_kernel", "achieved": gbs, "peak": peak[0], "peak_source": peak[1], "unit": "GB/s",
+        "roofline": {"bound": "hbm", "kernel": "tl1_mma_kernel", "achieved": gbs, "peak": peak[0], "peak_source": peak[1], "unit": "GB/s",
                      "frac": gbs / peak[0], "traffic": None, "bytes_per_launch": bytes_per, "us_per_launch": ms * 1e3 / launches},
+    }), flush=True)
+
+
+def _peak_tensor():
+    from pathlib import Path
+    p = Path(__file__).resolve().parents[1] / "MEASURED_PEAKS.json"
+    if p.exists():
+        return 2.0 * float(json.loads(p.read_text())["bf16_tflops"]), "2 x measured bf16 burst (int8 is twice bf16 on this part; no int8 GEMM peak was measured)"
+    return 2.0 * 1590.0, "2 x fallback bf16"
+
+
+def run_gemm(args):
+    import torch
+    from . import kernels
+    N, K, n_mat = 13824, 2560, 16
+    B = args.batch
+    ws = [_random_tl1_device(N * K // 4, 200 + i) for i in range(n_mat)]
+    x = torch.randn(B, K, device="cuda", generator=torch.Generator(device="cuda").manual_seed(3))
+    out = torch.empty(B, N, device="cuda")
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        for w in ws[:2]:
+            kernels.tl1_gemv(x, w, N // 64, K, [0.016], out=out, use_pdl=bool(args.pdl))
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for i, w in enumerate(ws):
+                kernels.tl1_gemv(x, w, N // 64, K, [0.016], out=out, use_pdl=bool(args.pdl), prefetch=ws[(i + 1) % n_mat])
+        for _ in range(max(3, args.warmup)):
+            graph.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        stream.synchronize()
+        e0.record(stream)
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record(stream)
+        stream.synchronize()
+    ms = e0.elapsed_time(e1)
+    calls = args.steps * n_mat
+    tops = 2.0 * N * K * B * calls / (ms * 1e-3) / 1e12
+    peak = _peak_tensor()
+    print(json.dumps({
+        "metric": "tl1_gemm_tops", "value": tops, "unit": "TOP/s", "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup),
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8 x s8 -> s32",
+        "data": "synthetic", "config": {"workload": f"gemm: TL1 bitlinear {N}x{K} for {B} sequences (absmax quantiser + tcgen05 GEMM), "
+                                                    f"{n_mat} distinct matrices per step ({n_mat * N * K // 4 / 1e6:.0f} MB > L2)", "pdl": int(args.pdl)},
+        "gpu_launches": 2 * calls,
+        "roofline": {"bound": "tensor", "kernel": "act_quant_kernel + tl1_umma_kernel", "achieved": tops, "peak": peak[0], "peak_source": peak[1],
+                     "unit": "TOP/s", "frac": tops / peak[0], "traffic": None, "ops_per_launch": 2.0 * N * K * B, "us_per_launch": ms * 1e3 / calls},
     }), flush=True)
 
 
@@ -153,7 +204,7 @@ def run_decode_batch(args):
 
 
 def run(args):
-    fn = {"gemv": run_gemv, "attn": run_attn, "decode_batch": run_decode_batch}.get(args.workload)
+    fn = {"gemv": run_gemv, "gemm": run_gemm, "attn": run_attn, "decode_batch": run_decode_batch}.get(args.workload)
     if fn is None:
         raise SystemExit(f"unknown workload {args.workload!r}")
     return fn(args)
