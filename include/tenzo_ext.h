@@ -74,6 +74,11 @@ TENZO_API float tenzo_ext_bench_gemv_stack(tenzo_engine_t engine, int iters, uns
 /* Number of kernels launched (or replayed through a graph) since the engine was created. */
 TENZO_API unsigned long long tenzo_ext_kernel_launches(tenzo_engine_t engine);
 /* Message for the most recent failure on this thread ("" if none). */
+/* RoPE tables cos/sin [max_seq][head_dim/2] as the engine builds them (the reference's float expressions,
+ * TenzoEngine.cpp:466-469), written to host memory: for callers that drive the per-kernel entry points
+ * themselves (tensor-parallel decode) and need the same bits. */
+TENZO_API tenzo_status_t tenzo_ext_rope_tables(int max_seq, int head_dim, float rope_theta, float* cos_host, float* sin_host);
+
 TENZO_API const char* tenzo_ext_last_error(void);
 
 #ifdef __cplusplus

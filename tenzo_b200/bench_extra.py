@@ -7,6 +7,9 @@
   attn          config 2: fused INT8-KV GQA decode attention alone, batch 64, 20/5 heads, ctx 8192.
   decode_batch  config 3: batched greedy decode of the BitNet-2B shape, KV prefilled on the device.
 
+  decode_tp     config 4: greedy decode of the synthetic 8B shape (32 layers, 4096/14336, 32q/8kv, vocab 128256), batch 32,
+                context 2048, tensor-parallel over the launched ranks (row splits + NCCL all-gathers; tenzo_b200/tp.py).
+
 Each prints one JSON line in the same format as the default workload.
 """
 from __future__ import annotations
@@ -203,8 +206,54 @@ def run_decode_batch(args):
         dist.destroy_process_group()
 
 
+def run_decode_tp(args):
+    import torch
+    from . import tp
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    B = 32 if args.batch == 256 else args.batch
+    ctx = 2048 if args.context == 4096 else args.context
+    warm = max(3, args.warmup)
+    cfg = dict(synth.SYNTH_8B)
+    dec = tp.TensorParallelDecoder(cfg, B, ctx + args.steps + warm + 8, use_graph=True).load_random(seed=0, context=ctx)
+    first = torch.from_numpy(synth.prompt_tokens(2000, B, cfg["vocab_size"])).cuda()
+    dec.step(first)
+    for _ in range(warm - 1):
+        dec.step()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        dec.step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    if rank == 0:
+        print(json.dumps({
+            "metric": "decode_tokens_per_second_batched", "value": B * args.steps / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
+            "steps": args.steps, "warmup": warm, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": {"workload": f"decode_tp: synthetic 8B shape (32L, 4096/14336, 32q/8kv, vocab 128256), batch {B}, context {ctx} "
+                                   f"(device-filled KV), device-generated random shards", "parallelism": f"tp{world}",
+                       "collectives_per_step": dec.collectives_per_step},
+            "gpu_launches": int(dec.kernels_per_step * args.steps),
+        }), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run(args):
-    fn = {"gemv": run_gemv, "gemm": run_gemm, "attn": run_attn, "decode_batch": run_decode_batch}.get(args.workload)
+    fn = {"gemv": run_gemv, "gemm": run_gemm, "attn": run_attn, "decode_batch": run_decode_batch, "decode_tp": run_decode_tp}.get(args.workload)
     if fn is None:
         raise SystemExit(f"unknown workload {args.workload!r}")
     return fn(args)

@@ -32,6 +32,20 @@
 
 namespace tz {
 
+// cos/sin [max_seq][head_dim/2] with the reference's float expressions (TenzoEngine.cpp:466-469).
+void rope_tables_host(int max_seq, int head_dim, float theta, float* cs, float* sn) {
+    const int half = head_dim / 2;
+    std::vector<float> freq(half);
+    for (int i = 0; i < half; ++i) freq[i] = 1.0f / std::pow(theta, static_cast<float>(2 * i) / head_dim);
+    for (int p = 0; p < max_seq; ++p)
+        for (int i = 0; i < half; ++i) {
+            const float ang = static_cast<float>(p) * freq[i];
+            cs[(size_t)p * half + i] = std::cos(ang);
+            sn[(size_t)p * half + i] = std::sin(ang);
+        }
+}
+
+
 thread_local std::string g_last_error;
 void set_error(const std::string& m) { g_last_error = m; }
 
@@ -149,14 +163,7 @@ Engine::Engine(const tenzo_config_t& c, const tenzo_ext_options_t& o) : cfg(c) {
     {
         const int half = cfg.head_dim / 2;
         std::vector<float> cs((size_t)cfg.max_seq_len * half), sn(cs.size());
-        std::vector<float> freq(half);
-        for (int i = 0; i < half; ++i) freq[i] = 1.0f / std::pow(rope_theta, static_cast<float>(2 * i) / cfg.head_dim);
-        for (int p = 0; p < cfg.max_seq_len; ++p)
-            for (int i = 0; i < half; ++i) {
-                const float ang = static_cast<float>(p) * freq[i];
-                cs[(size_t)p * half + i] = std::cos(ang);
-                sn[(size_t)p * half + i] = std::sin(ang);
-            }
+        rope_tables_host(cfg.max_seq_len, cfg.head_dim, rope_theta, cs.data(), sn.data());
         rope_cos = (float*)dalloc(cs.size() * 4);
         rope_sin = (float*)dalloc(sn.size() * 4);
         TZ_CUDA(cudaMemcpyAsync(rope_cos, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice, stream));

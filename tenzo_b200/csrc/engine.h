@@ -12,6 +12,9 @@
 
 namespace tz {
 
+void rope_tables_host(int max_seq, int head_dim, float theta, float* cs, float* sn);
+
+
 extern thread_local std::string g_last_error;
 void set_error(const std::string& m);
 

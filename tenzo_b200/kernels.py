@@ -26,13 +26,22 @@ def _ptr(t: torch.Tensor | None) -> int | None:
     return t.data_ptr()
 
 
+def _rows(t: torch.Tensor | None) -> int | None:
+    """Pointer of a 2-D tensor whose rows are contiguous but may be strided (a column slice of a wider buffer)."""
+    if t is None:
+        return None
+    assert t.is_cuda and t.dim() == 2 and t.stride(1) == 1
+    return t.data_ptr()
+
+
 def _ok(rc: int, what: str):
     if rc != 0:
         raise RuntimeError(f"{what} failed: rc={rc}" + (f" ({torch.cuda.get_device_name()})" if rc > 0 else " (bad arguments)"))
 
 
 def tl1_gemv(x: torch.Tensor, w: torch.Tensor, n_blocks: int, K: int, scales, seg_ends=None, *, epilogue=EPI_STORE,
-             resid=None, norm_w=None, do_norm=False, eps=1e-5, want_acc=False, want_act=False, use_pdl=False, out=None, prefetch=None):
+             resid=None, norm_w=None, do_norm=False, eps=1e-5, want_acc=False, want_act=False, use_pdl=False, out=None, prefetch=None,
+             workspace=None):
     """x [batch, K] fp32, w TL1-packed uint8. Returns dict(out=..., acc=..., a=..., inv=...)."""
     lib = load_library()
     batch = x.shape[0]
@@ -53,8 +62,8 @@ def tl1_gemv(x: torch.Tensor, w: torch.Tensor, n_blocks: int, K: int, scales, se
     g.epilogue, g.resid, g.out = epilogue, _ptr(resid), _ptr(out)
     g.acc_out, g.a_out, g.inv_out = _ptr(acc), _ptr(a8), _ptr(inv)
     g.batch, g.x_stride, g.out_stride = batch, x.stride(0), out.stride(0)
-    ws = None
-    if batch > 1:
+    ws = workspace
+    if batch > 1 and ws is None:
         ws = torch.empty(lib.tenzo_cuda_tl1_gemv_workspace_bytes(batch, K), dtype=torch.uint8, device=x.device)
     g.workspace, g.use_pdl = _ptr(ws), int(use_pdl)
     if prefetch is not None:
@@ -75,16 +84,17 @@ def rmsnorm_quant(x: torch.Tensor, norm_w=None, *, do_norm=True, eps=1e-5, qmax=
 
 
 def attention_int8(q, k, v, cache_k, cache_v, scale_k, scale_v, pos, *, layer, n_q, n_kv, max_seq, rope_cos=None,
-                   rope_sin=None, append=True, max_len=None, use_pdl=False, heads_per_cta=0):
+                   rope_sin=None, append=True, max_len=None, use_pdl=False, heads_per_cta=0, out=None):
     """q [batch, n_q*128], k/v [batch, n_kv*128]; caches [batch, layers, n_kv, max_seq, 128] int8 and
     [batch, layers, n_kv, max_seq] fp32; pos int32 [batch]. Returns out [batch, n_q*128]."""
     lib = load_library()
     batch = q.shape[0]
     if max_len is None:
         max_len = int(pos.max().item()) + 1
-    out = torch.empty(batch, n_q * 128, dtype=torch.float32, device=q.device)
+    if out is None:
+        out = torch.empty(batch, n_q * 128, dtype=torch.float32, device=q.device)
     a = abi.AttentionArgs()
-    a.q, a.k, a.v, a.out = _ptr(q), _ptr(k), _ptr(v), _ptr(out)
+    a.q, a.k, a.v, a.out = _rows(q), _rows(k), _rows(v), _ptr(out)
     a.q_stride, a.kv_stride = q.stride(0), (k.stride(0) if k is not None else 0)
     a.cache_k, a.cache_v, a.scale_k, a.scale_v = _ptr(cache_k), _ptr(cache_v), _ptr(scale_k), _ptr(scale_v)
     a.seq_stride_kv, a.seq_stride_sc = cache_k.stride(0), scale_k.stride(0)
@@ -95,11 +105,12 @@ def attention_int8(q, k, v, cache_k, cache_v, scale_k, scale_v, pos, *, layer, n
     return out
 
 
-def lm_head_i8(x, w, row_scales, *, norm_w=None, do_norm=True, eps=1e-5, want_logits=True, want_acc=False, use_pdl=False):
+def lm_head_i8(x, w, row_scales, *, norm_w=None, do_norm=True, eps=1e-5, want_logits=True, want_acc=False, use_pdl=False, logits=None):
     lib = load_library()
     batch, hidden = x.shape
     vocab = w.shape[0]
-    logits = torch.empty(batch, vocab, dtype=torch.float32, device=x.device) if want_logits else None
+    if logits is None and want_logits:
+        logits = torch.empty(batch, vocab, dtype=torch.float32, device=x.device)
     acc = torch.empty(batch, vocab, dtype=torch.int32, device=x.device) if want_acc else None
     arg = torch.empty(batch, dtype=torch.int32, device=x.device)
     scratch = torch.empty(lib.tenzo_cuda_lm_head_scratch_bytes(batch), dtype=torch.uint8, device=x.device)
