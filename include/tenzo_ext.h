@@ -79,6 +79,12 @@ TENZO_API unsigned long long tenzo_ext_kernel_launches(tenzo_engine_t engine);
  * themselves (tensor-parallel decode) and need the same bits. */
 TENZO_API tenzo_status_t tenzo_ext_rope_tables(int max_seq, int head_dim, float rope_theta, float* cos_host, float* sin_host);
 
+/* The manifest reader of tenzo_load_model on its own (host only): byte offsets of the memref.view constants and the
+ * f32 scale constants feeding "tenzo.bitlinear_elut", in order of appearance (TenzoEngine.cpp:1946-1963 of the
+ * reference). Writes at most max_* entries; the counts found are always returned. */
+TENZO_API int tenzo_ext_parse_manifest(const char* text, unsigned long long* views, int max_views, int* n_views,
+                                       float* scales, int max_scales, int* n_scales);
+
 TENZO_API const char* tenzo_ext_last_error(void);
 
 #ifdef __cplusplus

@@ -49,15 +49,6 @@ void rope_tables_host(int max_seq, int head_dim, float theta, float* cs, float* 
 thread_local std::string g_last_error;
 void set_error(const std::string& m) { g_last_error = m; }
 
-struct CudaError : std::runtime_error {
-    cudaError_t code;
-    CudaError(cudaError_t c, const char* what) : std::runtime_error(std::string(what) + ": " + cudaGetErrorString(c)), code(c) {}
-};
-#define TZ_CUDA(expr)                                            \
-    do {                                                         \
-        cudaError_t _e = (expr);                                 \
-        if (_e != cudaSuccess) throw CudaError(_e, #expr);       \
-    } while (0)
 #define TZ_KERNEL(expr)                                                                         \
     do {                                                                                        \
         int _r = (expr);                                                                        \

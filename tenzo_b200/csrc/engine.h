@@ -18,6 +18,17 @@ void rope_tables_host(int max_seq, int head_dim, float theta, float* cs, float* 
 extern thread_local std::string g_last_error;
 void set_error(const std::string& m);
 
+struct CudaError : std::runtime_error {
+    cudaError_t code;
+    CudaError(cudaError_t c, const char* what) : std::runtime_error(std::string(what) + ": " + cudaGetErrorString(c)), code(c) {}
+};
+#define TZ_CUDA(expr)                                            \
+    do {                                                         \
+        cudaError_t _e = (expr);                                 \
+        if (_e != cudaSuccess) throw tz::CudaError(_e, #expr);   \
+    } while (0)
+
+
 struct LayerDev {
     uint8_t* qkv = nullptr;      // q|k|v row blocks back to back, TL1 layout
     uint8_t* o = nullptr;

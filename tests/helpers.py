@@ -127,3 +127,63 @@ def rel_err(a: np.ndarray, b: np.ndarray) -> float:
     """max|a-b| normalised by max|b| (tensor-level relative error used for every fp32 comparison)."""
     d = float(np.abs(a.astype(np.float64) - b.astype(np.float64)).max())
     return d / max(float(np.abs(b).max()), 1e-30)
+
+
+# ---- checkpoint files in the reference's format (weights.bin + model.mlir) ---------------------------------
+def tl1_to_export_rows(packed: np.ndarray, n: int, k: int) -> np.ndarray:
+    """TL1-packed ternary matrix -> the exporter's [N/4][K] bytes (four rows per byte, 2-bit value+1; TenzoEngine.cpp:1849-1859)."""
+    code = (synth.unpack_tl1(packed, n, k).astype(np.int16) + 1).astype(np.uint8).reshape(n // 4, 4, k)
+    return (code[:, 0] | (code[:, 1] << 2) | (code[:, 2] << 4) | (code[:, 3] << 6)).astype(np.uint8)
+
+
+def loader_quantised_embedding(emb: np.ndarray):
+    """What the loader makes of an fp32 embedding table: per-row absmax/127 scales and rounded int8 (TenzoEngine.cpp:1932-1943)."""
+    amax = np.maximum(np.abs(emb).max(axis=1), np.float32(1e-8)).astype(np.float32)
+    scale = (amax / np.float32(127.0)).astype(np.float32)
+    inv = (np.float32(1.0) / scale).astype(np.float32)
+    y = (emb * inv[:, None]).astype(np.float32)
+    q = np.clip(np.sign(y) * np.floor(np.abs(y) + np.float32(0.5)), -127, 127)
+    return q.astype(np.int8), scale
+
+
+def write_checkpoint(model: synth.SyntheticModel, weights_path, mlir_path, with_manifest: bool = True, gap: int = 0):
+    """Write `model` as weights.bin + model.mlir. The embedding table is the dequantised tied LM head. With a manifest
+    every tensor gets a memref.view offset (tensors `gap` bytes apart) and every matrix its scale constant; without,
+    the tensors sit back to back and the loader's scales default to 1. Returns the fp32 embedding table written."""
+    c = model.cfg
+    emb = (model.lm_w.astype(np.float32) * model.lm_scales[:, None]).astype(np.float32)
+    blobs = [emb.tobytes()]
+    order = [("in_norm", None), ("q", "q"), ("k", "k"), ("v", "v"), ("attn_sub_norm", None), ("out", "out"), ("post_norm", None),
+             ("gate", "gate"), ("up", "up"), ("ffn_sub_norm", None), ("down", "down")]
+    scales = []
+    for lw in model.layers:
+        for name, mat in order:
+            if mat is None:
+                blobs.append(lw[name].astype(np.float32).tobytes())
+            else:
+                n, k = model.shapes[mat]
+                blobs.append(tl1_to_export_rows(lw[mat + "_w"], n, k).tobytes())
+                scales.append(np.float32(lw[mat + "_scale"]))
+    blobs.append(model.final_norm.astype(np.float32).tobytes())
+    offsets, data, pos = [], bytearray(), 0
+    for i, b in enumerate(blobs):
+        pad = gap if (with_manifest and i > 0) else 0
+        data += b"\xAA" * pad
+        pos += pad
+        offsets.append(pos)
+        data += b
+        pos += len(b)
+    with open(weights_path, "wb") as f:
+        f.write(bytes(data))
+    lines = ["module {", "  func.func @main(%buf: memref<?xi8>) {"]
+    if with_manifest:
+        for i, off in enumerate(offsets):
+            lines.append(f"    %c{i} = arith.constant {off} : index")
+            lines.append(f"    %v{i} = memref.view %buf[%c{i}][] : memref<?xi8> to memref<{len(blobs[i])}xi8>")
+        for i, s in enumerate(scales):
+            lines.append(f"    %s{i} = arith.constant {float(s):.9e} : f32")
+            lines.append(f"    %y{i} = \"tenzo.bitlinear_elut\"(%x{i}, %v{i}, %s{i}) : (memref<?xf32>, memref<?xi8>, f32) -> memref<?xf32>")
+    lines += ["    return", "  }", "}"]
+    with open(mlir_path, "w") as f:
+        f.write("\n".join(lines) + "\n")
+    return emb

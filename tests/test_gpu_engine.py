@@ -210,3 +210,38 @@ def test_backend_class_host_pointer_calls(cuda_lib):
     assert lib.tenzo_hal_gemm_f32_host(A.ctypes.data_as(abi.c_f32p), Bm.ctypes.data_as(abi.c_f32p), Cm.ctypes.data_as(abi.c_f32p), 5, 70, 33) == 1
     assert rel_err(Cm, A @ Bm) < 1e-5
     assert lib.tenzo_hal_bitlinear_tl1_host(x.ctypes.data_as(abi.c_f32p), w.ctypes.data_as(abi.c_u8p), out.ctypes.data_as(abi.c_f32p), 1, 3, N, 1.0) == 0
+
+
+@pytest.mark.parametrize("with_manifest", [True, False])
+def test_load_model_from_files_matches_the_cpu_engine(tmp_path, with_manifest):
+    """tenzo_load_model on a checkpoint in the reference's format (writer pinned to the reference's own loader in
+    tests/test_loader_host.py): device-side embedding quantisation and TL1 repack, then the same greedy stream as the
+    CPU engine fed the same tensors through its setters. A short file loads with the reference's fallbacks, an
+    unreadable one reports TENZO_ERROR_IO."""
+    from helpers import best_cpu_engine, greedy_stream, loader_quantised_embedding, write_checkpoint
+    cfg = dict(synth.BITNET_2B, num_layers=2, vocab_size=768, max_seq_len=48)
+    model = synth.SyntheticModel(cfg, seed=11)
+    w, m = tmp_path / "weights.bin", tmp_path / "model.mlir"
+    emb = write_checkpoint(model, w, m, with_manifest=with_manifest, gap=48)
+    if not with_manifest:
+        for lw in model.layers:
+            for name in model.shapes:
+                lw[name + "_scale"] = np.float32(1.0)
+    model.lm_w, model.lm_scales = loader_quantised_embedding(emb)
+    prompt = synth.prompt_tokens(4, 5, cfg["vocab_size"])
+    cpu = best_cpu_engine(model, max_seq_len=48)
+    want = greedy_stream(cpu, prompt, 8)
+    cpu.close()
+    with Engine(model.config_struct(max_seq_len=48)) as e:
+        e.load_model(str(w), str(m))
+        for t in prompt[:-1]:
+            e.prefill_token(int(t))
+        cur, got = int(prompt[-1]), []
+        for _ in range(8):
+            cur = e.generate_step(cur, abi.TenzoSampling(0.0, 0.9, 40, 1.0))
+            got.append(cur)
+        assert np.array_equal(np.asarray(got, np.int32), want)
+        short = tmp_path / "short.bin"
+        short.write_bytes(w.read_bytes()[: cfg["vocab_size"] * cfg["hidden_size"] * 4 + 1000])
+        e.load_model(str(short), str(m))                   # tensors past the end become ones / zero weights, as in the reference
+        assert e.lib.tenzo_load_model(e.get_raw_handle(), str(tmp_path / "missing.bin").encode(), str(m).encode()) == abi.ERR_IO
