@@ -19,7 +19,7 @@ def run_worker(n_ranks, graph):
     else:
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n_ranks}", "--master-addr", "127.0.0.1",
                "--master-port", "29533", str(ROOT / "tests" / "tp_worker.py")]
-    r = subprocess.run(cmd, env=env, cwd=ROOT, capture_output=True, text=True, timeout=900)
+    r = subprocess.run(cmd, env=env, cwd=ROOT, capture_output=True, text=True, timeout=240)
     assert r.returncode == 0 and "TP_OK" in r.stdout, (r.stdout[-2000:], r.stderr[-3000:])
 
 

@@ -25,6 +25,8 @@ def main():
     model = synth.SyntheticModel(cfg, seed=5)
     prompts = np.stack([synth.prompt_tokens(100 + b, prompt_len, cfg["vocab_size"]) for b in range(B)])     # [B, prompt_len]
 
+    say = lambda m: print(f"[rank {rank}] {m}", file=sys.stderr, flush=True)
+    say("model built")
     eng = Engine(model.config_struct(), batch=B).load_synthetic(model)
     for t in range(prompt_len - 1):
         eng.prefill_tokens(prompts[:, t])
@@ -34,9 +36,13 @@ def main():
     want_logits = np.stack([eng.read_buffer(15, seq=b, count=cfg["vocab_size"]) for b in (0, B - 1)])
     eng.close()
 
+    say("single-GPU reference done")
     dec = tp.TensorParallelDecoder(model, B, cfg["max_seq_len"], use_graph=bool(use_graph))
+    say("shards loaded")
     for t in range(prompt_len - 1):
         dec.step(prompts[:, t])
+        torch.cuda.synchronize()
+        say(f"prompt step {t} done")
     got = []
     nxt = dec.step(prompts[:, -1])
     got.append(nxt.cpu().numpy().copy())
@@ -44,6 +50,7 @@ def main():
         nxt = dec.step()
         got.append(nxt.cpu().numpy().copy())
     got = np.stack(got)
+    say("decode done")
     v0, vn = dec.p.vocab_rows
     mine = dec.logits_slice().cpu().numpy()
     ok = np.array_equal(got, want) and np.array_equal(mine[0], want_logits[0, v0:v0 + vn]) and np.array_equal(mine[B - 1], want_logits[1, v0:v0 + vn])
