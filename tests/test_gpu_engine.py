@@ -219,6 +219,7 @@ def test_load_model_from_files_matches_the_cpu_engine(tmp_path, with_manifest):
     CPU engine fed the same tensors through its setters. A short file loads with the reference's fallbacks, an
     unreadable one reports TENZO_ERROR_IO."""
     from helpers import loader_quantised_embedding, write_checkpoint
+    from tenzo_b200 import abi
     from tenzo_b200.engine import Engine
     cfg = dict(synth.BITNET_2B, num_layers=2, vocab_size=768, max_seq_len=48)
     model = synth.SyntheticModel(cfg, seed=11)
