@@ -219,7 +219,7 @@ def run_decode_tp(args):
     ctx = 2048 if args.context == 4096 else args.context
     warm = max(3, args.warmup)
     cfg = dict(synth.SYNTH_8B)
-    dec = tp.TensorParallelDecoder(cfg, B, ctx + args.steps + warm + 8, use_graph=True).load_random(seed=0, context=ctx)
+    dec = tp.TensorParallelDecoder(cfg, B, ctx + args.steps + warm + 8).load_random(seed=0, context=ctx)
     first = torch.from_numpy(synth.prompt_tokens(2000, B, cfg["vocab_size"])).cuda()
     dec.step(first)
     for _ in range(warm - 1):
@@ -245,7 +245,7 @@ def run_decode_tp(args):
             "vs_baseline": None, "dtype": "int8", "data": "synthetic",
             "config": {"workload": f"decode_tp: synthetic 8B shape (32L, 4096/14336, 32q/8kv, vocab 128256), batch {B}, context {ctx} "
                                    f"(device-filled KV), device-generated random shards", "parallelism": f"tp{world}",
-                       "collectives_per_step": dec.collectives_per_step},
+                       "collectives_per_step": dec.collectives_per_step, "cuda_graph": bool(dec.use_graph)},
             "gpu_launches": int(dec.kernels_per_step * args.steps),
         }), flush=True)
     if world > 1:

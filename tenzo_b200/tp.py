@@ -16,7 +16,7 @@ two GPUs). No floating-point reduction crosses ranks. The greedy argmax combines
 pairs and keeps the first maximum, as the reference's sampler does (TenzoEngine.cpp:1745-1755).
 
 The per-kernel work goes through the library's C entry points (kernels.py); torch.distributed only
-moves the slices. One decode step can be captured in a CUDA graph (collectives included).
+moves the slices. With one rank the step is captured in a CUDA graph; with several it is enqueued call by call.
 """
 from __future__ import annotations
 
@@ -92,8 +92,11 @@ class TensorParallelDecoder:
     """Greedy batched decode with the weights of `model` (synth.SyntheticModel-like: .cfg, .layers, .final_norm,
     .lm_w, .lm_scales) sharded as in `plan`. `group` is a torch.distributed process group (None: the default)."""
 
-    def __init__(self, model, batch: int, max_seq: int, group=None, rope_theta: float = 10000.0, use_graph: bool = True):
-        """`model`: a synth.SyntheticModel-like object, or a plain config dict (then call load_random)."""
+    def __init__(self, model, batch: int, max_seq: int, group=None, rope_theta: float = 10000.0, use_graph: bool | None = None):
+        """`model`: a synth.SyntheticModel-like object, or a plain config dict (then call load_random).
+        `use_graph`: capture the step in a CUDA graph; default: only without collectives (one rank). Capturing the
+        NCCL all-gathers together with the kernels did not complete on the test machines (the replay never returned),
+        so with several ranks the step is enqueued call by call unless the caller asks otherwise."""
         import torch
         import torch.distributed as dist
         from . import kernels, load_library
@@ -103,7 +106,8 @@ class TensorParallelDecoder:
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         cfg = self.cfg = dict(model if isinstance(model, dict) else model.cfg)
         self.p = p = plan(cfg, self.world, self.rank)
-        self.B, self.max_seq, self.use_graph = batch, max_seq, use_graph
+        self.B, self.max_seq = batch, max_seq
+        self.use_graph = (self.world == 1) if use_graph is None else bool(use_graph)
         h, f, hd = cfg["hidden_size"], cfg["ffn_dim"], cfg["head_dim"]
         nq, nkv = cfg["num_q_heads"], cfg["num_kv_heads"]
         self.dev = dev = torch.device("cuda", torch.cuda.current_device())
