@@ -271,8 +271,9 @@ void Engine::enqueue_layer(int l, int max_len, bool gemv_only) {
     g.seg_scale[0] = d.s_q; g.seg_scale[1] = d.s_k; g.seg_scale[2] = d.s_v;
     g.epilogue = TENZO_EPI_STORE; g.out = b_qkv; g.out_stride = qd + 2 * kvd;
     g.prefetch = d.o; g.prefetch_bytes = (size_t)h * h / 4;
+    const int gemv_kernels = batch > 1 ? 2 : 1;      // several sequences: quantiser kernel + GEMM kernel
     TZ_KERNEL(tenzo_cuda_tl1_gemv(&g, stream));
-    launches += 1;
+    launches += gemv_kernels;
 
     tenzo_attention_args a;
     std::memset(&a, 0, sizeof a);
@@ -298,7 +299,7 @@ void Engine::enqueue_layer(int l, int max_len, bool gemv_only) {
     if (d.has_mlp) { g.prefetch = d.gateup; g.prefetch_bytes = (size_t)2 * ffn * h / 4; }
     else { g.prefetch = nxt ? nxt->qkv : nullptr; g.prefetch_bytes = (size_t)(qd + 2 * kvd) * h / 4; }
     TZ_KERNEL(tenzo_cuda_tl1_gemv(&g, stream));
-    launches += 1;
+    launches += gemv_kernels;
 
     if (d.has_mlp) {
         g.x = b_h1; g.x_stride = h; g.norm_w = d.post_norm; g.w = d.gateup; g.K = h;
@@ -314,7 +315,7 @@ void Engine::enqueue_layer(int l, int max_len, bool gemv_only) {
         if (nxt) { g.prefetch = nxt->qkv; g.prefetch_bytes = (size_t)(qd + 2 * kvd) * h / 4; }
         else { g.prefetch = lm_w; g.prefetch_bytes = (size_t)64 << 20; if ((size_t)V * h < g.prefetch_bytes) g.prefetch_bytes = (size_t)V * h; }
         TZ_KERNEL(tenzo_cuda_tl1_gemv(&g, stream));
-        launches += 2;
+        launches += 2 * gemv_kernels;
     } else {
         TZ_CUDA(cudaMemcpyAsync(b_x, b_h1, (size_t)batch * h * 4, cudaMemcpyDeviceToDevice, stream));   // :1630
     }
@@ -328,7 +329,7 @@ void Engine::enqueue_step(bool with_logits, bool feed_back, int max_len) {
     if (with_logits) {
         TZ_KERNEL(tenzo_cuda_lm_head_i8(b_x, final_norm, 1, 1e-5f, lm_w, lm_scales, V, h, batch, h, b_logits, nullptr,
                                         d_next, lm_scratch, use_pdl, stream));
-        launches += 2;
+        launches += batch >= 16 && h % 128 == 0 ? 3 : 2;   // (quantiser +) LM head + argmax finish
     }
     advance_kernel<<<(batch + 127) / 128, 128, 0, stream>>>(d_pos, d_tokens, d_next, batch, feed_back ? 1 : 0);
     TZ_CUDA(cudaGetLastError());

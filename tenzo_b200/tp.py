@@ -16,7 +16,7 @@ two GPUs). No floating-point reduction crosses ranks. The greedy argmax combines
 pairs and keeps the first maximum, as the reference's sampler does (TenzoEngine.cpp:1745-1755).
 
 The per-kernel work goes through the library's C entry points (kernels.py); torch.distributed only
-moves the slices. With one rank the step is captured in a CUDA graph; with several it is enqueued call by call.
+moves the slices. The kernels between two collectives are replayed as one CUDA graph; the collectives are direct calls.
 """
 from __future__ import annotations
 
@@ -94,9 +94,9 @@ class TensorParallelDecoder:
 
     def __init__(self, model, batch: int, max_seq: int, group=None, rope_theta: float = 10000.0, use_graph: bool | None = None):
         """`model`: a synth.SyntheticModel-like object, or a plain config dict (then call load_random).
-        `use_graph`: capture the step in a CUDA graph; default: only without collectives (one rank). Capturing the
-        NCCL all-gathers together with the kernels did not complete on the test machines (the replay never returned),
-        so with several ranks the step is enqueued call by call unless the caller asks otherwise."""
+        `use_graph`: replay the kernels between two collectives as CUDA graphs (default) instead of launching them one
+        by one. The NCCL calls stay outside the graphs: capturing them together with the kernels did not complete on
+        the test machines (the first replay never returned)."""
         import torch
         import torch.distributed as dist
         from . import kernels, load_library
@@ -107,7 +107,7 @@ class TensorParallelDecoder:
         cfg = self.cfg = dict(model if isinstance(model, dict) else model.cfg)
         self.p = p = plan(cfg, self.world, self.rank)
         self.B, self.max_seq = batch, max_seq
-        self.use_graph = (self.world == 1) if use_graph is None else bool(use_graph)
+        self.use_graph = True if use_graph is None else bool(use_graph)
         h, f, hd = cfg["hidden_size"], cfg["ffn_dim"], cfg["head_dim"]
         nq, nkv = cfg["num_q_heads"], cfg["num_kv_heads"]
         self.dev = dev = torch.device("cuda", torch.cuda.current_device())
@@ -141,7 +141,7 @@ class TensorParallelDecoder:
         self.tokens = torch.zeros(B, dtype=torch.int32, device=dev)
         self.next_tokens = torch.zeros(B, dtype=torch.int32, device=dev)
         self.logits_loc = torch.empty(B, vn, **f32)
-        self.graph = None
+        self.prog, self.graphs = None, None
         self.collectives_per_step = (4 * L + 2) if self.world > 1 else 0
         self.kernels_per_step = 5 * L + 4      # TL1 x4 (+ quantiser when batched) and attention per layer; embedding, LM head (+ quantiser, argmax)
 
@@ -204,71 +204,128 @@ class TensorParallelDecoder:
             self.pos.fill_(context)
         return self
 
-    def _all_gather_cols(self, loc, full):
-        all_gather_cols(loc, full, self.b_gather, self.world, self.group)
-
     # ---- one token for every sequence ---------------------------------------------------------------
-    def _enqueue_step(self):
-        k, p, cfg = self.k, self.p, self.cfg
+    def _program(self):
+        """The step as a list of ("compute", fn) and ("comm", fn) items: compute items only launch kernels on the
+        current stream (capturable), comm items are the NCCL all-gathers between them."""
+        k, p, cfg, torch, dist = self.k, self.p, self.cfg, self.torch, self.dist
         h, f, hd = cfg["hidden_size"], cfg["ffn_dim"], cfg["head_dim"]
         qn, kn = p.q_heads[1] * hd, p.kv_heads[1] * hd
         h0, hn = p.hidden_rows
-        x = k.embedding_i8(self.emb_w, self.emb_s, self.tokens)                      # [B, h], identical on every rank
-        self.b_x.copy_(x)
-        self.b_x_loc.copy_(self.b_x[:, h0:h0 + hn])
+        fn = p.ffn_rows[1]
+        R, B = self.world, self.B
+        prog = []
+
+        def gather(loc, full):
+            """comm: slices -> scratch [R][B][S]; the following compute item starts by transposing them into `full`."""
+            S = loc.shape[1]
+            tmp = self.b_gather[: R * B * S].view(R, B, S)
+            if R > 1:
+                prog.append(("comm", lambda: dist.all_gather_into_tensor(tmp, loc, group=self.group)))
+                return lambda: full.view(B, R, S).copy_(tmp.transpose(0, 1))
+            return lambda: full.copy_(loc)
+
+        def embed():
+            x = k.embedding_i8(self.emb_w, self.emb_s, self.tokens)                  # [B, h], identical on every rank
+            self.b_x.copy_(x)
+            self.b_x_loc.copy_(self.b_x[:, h0:h0 + hn])
+        pending = [embed]
         assert len(self.layers) == cfg["num_layers"], "no weights loaded"
         for l, d in enumerate(self.layers):
             nb = (qn + 2 * kn) // 64
-            k.tl1_gemv(self.b_x, d["qkv"], nb, h, d["qkv_scales"], [qn // 64, (qn + kn) // 64, nb], norm_w=d["in_norm"], do_norm=True,
-                       out=self.b_qkv, workspace=self.ws)
-            k.attention_int8(self.b_qkv[:, :qn], self.b_qkv[:, qn:qn + kn], self.b_qkv[:, qn + kn:], self.ck, self.cv, self.sk, self.sv,
-                             self.pos, layer=l, n_q=p.q_heads[1], n_kv=p.kv_heads[1], max_seq=self.max_seq, rope_cos=self.rope_cos,
-                             rope_sin=self.rope_sin, max_len=self.max_seq, out=self.b_attn_loc)
-            self._all_gather_cols(self.b_attn_loc, self.b_attn)
-            k.tl1_gemv(self.b_attn, d["o"], hn // 64, cfg["num_q_heads"] * hd, [d["o_scale"]], norm_w=d["attn_sub_norm"], do_norm=True,
-                       epilogue=k.EPI_RESIDUAL, resid=self.b_x_loc, out=self.b_h1_loc, workspace=self.ws)
-            self._all_gather_cols(self.b_h1_loc, self.b_h1)
-            fn = p.ffn_rows[1]
-            k.tl1_gemv(self.b_h1, d["gu"], 2 * fn // 64, h, d["gu_scales"], [fn // 64, 2 * fn // 64, 2 * fn // 64], norm_w=d["post_norm"],
-                       do_norm=True, epilogue=k.EPI_RELU2_GLU, out=self.b_act_loc, workspace=self.ws)
-            self._all_gather_cols(self.b_act_loc, self.b_act)
-            k.tl1_gemv(self.b_act, d["down"], hn // 64, f, [d["down_scale"]], norm_w=d["ffn_sub_norm"], do_norm=True,
-                       epilogue=k.EPI_RESIDUAL, resid=self.b_h1_loc, out=self.b_x_loc, workspace=self.ws)
-            self._all_gather_cols(self.b_x_loc, self.b_x)
-        self.pos.add_(1)
-        torch = self.torch
-        _, _, arg = k.lm_head_i8(self.b_x, self.lm_w, self.lm_s, norm_w=self.final_norm, logits=self.logits_loc)
-        val = self.logits_loc.gather(1, arg.to(torch.int64).unsqueeze(1)).squeeze(1)
-        idx = arg + p.vocab_rows[0]
-        if self.world > 1:
-            vals = torch.empty(self.world, self.B, dtype=torch.float32, device=val.device)
-            idxs = torch.empty(self.world, self.B, dtype=torch.int32, device=val.device)
-            self.dist.all_gather_into_tensor(vals, val.contiguous(), group=self.group)
-            self.dist.all_gather_into_tensor(idxs, idx.contiguous(), group=self.group)
-            idx = combine_argmax(vals, idxs.to(torch.int64)).to(torch.int32)
-        self.next_tokens.copy_(idx)
+
+            def attn_block(l=l, d=d, nb=nb):
+                k.tl1_gemv(self.b_x, d["qkv"], nb, h, d["qkv_scales"], [qn // 64, (qn + kn) // 64, nb], norm_w=d["in_norm"], do_norm=True,
+                           out=self.b_qkv, workspace=self.ws)
+                k.attention_int8(self.b_qkv[:, :qn], self.b_qkv[:, qn:qn + kn], self.b_qkv[:, qn + kn:], self.ck, self.cv, self.sk, self.sv,
+                                 self.pos, layer=l, n_q=p.q_heads[1], n_kv=p.kv_heads[1], max_seq=self.max_seq, rope_cos=self.rope_cos,
+                                 rope_sin=self.rope_sin, max_len=self.max_seq, out=self.b_attn_loc)
+            pending.append(attn_block)
+            prog.append(("compute", pending))
+            pending = [gather(self.b_attn_loc, self.b_attn)]
+            pending.append(lambda d=d: k.tl1_gemv(self.b_attn, d["o"], hn // 64, cfg["num_q_heads"] * hd, [d["o_scale"]], norm_w=d["attn_sub_norm"],
+                                                  do_norm=True, epilogue=k.EPI_RESIDUAL, resid=self.b_x_loc, out=self.b_h1_loc, workspace=self.ws))
+            prog.append(("compute", pending))
+            pending = [gather(self.b_h1_loc, self.b_h1)]
+            pending.append(lambda d=d: k.tl1_gemv(self.b_h1, d["gu"], 2 * fn // 64, h, d["gu_scales"], [fn // 64, 2 * fn // 64, 2 * fn // 64],
+                                                  norm_w=d["post_norm"], do_norm=True, epilogue=k.EPI_RELU2_GLU, out=self.b_act_loc, workspace=self.ws))
+            prog.append(("compute", pending))
+            pending = [gather(self.b_act_loc, self.b_act)]
+            pending.append(lambda d=d: k.tl1_gemv(self.b_act, d["down"], hn // 64, f, [d["down_scale"]], norm_w=d["ffn_sub_norm"], do_norm=True,
+                                                  epilogue=k.EPI_RESIDUAL, resid=self.b_h1_loc, out=self.b_x_loc, workspace=self.ws))
+            prog.append(("compute", pending))
+            pending = [gather(self.b_x_loc, self.b_x)]
+
+        vals = torch.empty(R, B, dtype=torch.float32, device=self.dev)
+        idxs = torch.empty(R, B, dtype=torch.int32, device=self.dev)
+        val_loc = torch.empty(B, dtype=torch.float32, device=self.dev)
+        idx_loc = torch.empty(B, dtype=torch.int32, device=self.dev)
+
+        def head():
+            self.pos.add_(1)
+            _, _, arg = k.lm_head_i8(self.b_x, self.lm_w, self.lm_s, norm_w=self.final_norm, logits=self.logits_loc)
+            val_loc.copy_(self.logits_loc.gather(1, arg.to(torch.int64).unsqueeze(1)).squeeze(1))
+            idx_loc.copy_(arg + p.vocab_rows[0])
+        pending.append(head)
+        prog.append(("compute", pending))
+        if R > 1:
+            prog.append(("comm", lambda: (dist.all_gather_into_tensor(vals, val_loc, group=self.group),
+                                          dist.all_gather_into_tensor(idxs, idx_loc, group=self.group))))
+            prog.append(("compute", [lambda: self.next_tokens.copy_(combine_argmax(vals, idxs.to(torch.int64)).to(torch.int32))]))
+        else:
+            prog.append(("compute", [lambda: self.next_tokens.copy_(idx_loc)]))
+        # merge neighbouring compute items
+        merged = []
+        for kind, item in prog:
+            if kind == "compute" and merged and merged[-1][0] == "compute":
+                merged[-1][1].extend(item)
+            else:
+                merged.append((kind, list(item) if kind == "compute" else item))
+        return merged
+
+    def _run_eager(self, prog):
+        for kind, item in prog:
+            if kind == "compute":
+                for fn in item:
+                    fn()
+            else:
+                item()
 
     def step(self, tokens=None):
         """Feed one token per sequence (device or host int32 [B]; None: the previous step's argmax) and return the
-        device tensor of next tokens (valid after the stream reaches this point)."""
+        device tensor of next tokens (valid after the stream reaches this point). With `use_graph` every run of
+        kernels between two collectives is one CUDA graph; the collectives themselves are issued directly."""
         torch = self.torch
         if tokens is None:
             self.tokens.copy_(self.next_tokens)
         else:
             self.tokens.copy_(torch.as_tensor(tokens, dtype=torch.int32).to(self.tokens.device, non_blocking=True))
+        if self.prog is None:
+            self.prog = self._program()
         if not self.use_graph:
-            self._enqueue_step()
-        else:
-            if self.graph is None:
-                pos0 = self.pos.clone()
-                self._enqueue_step()        # warm-up outside capture (function attributes, NCCL channels); the cache row it
-                torch.cuda.synchronize()    # appends at pos0 is rewritten with the same bytes by the captured step
-                self.pos.copy_(pos0)
-                self.graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(self.graph):
-                    self._enqueue_step()
-                self.pos.copy_(pos0)
-            self.graph.replay()
+            self._run_eager(self.prog)
+            return self.next_tokens
+        if self.graphs is None:
+            pos0 = self.pos.clone()
+            self._run_eager(self.prog)      # warm-up outside capture (function attributes, NCCL channels); the cache row it
+            torch.cuda.synchronize()        # appends at pos0 is rewritten with the same bytes by the captured step
+            self.pos.copy_(pos0)
+            self.graphs, pool = [], None
+            for kind, item in self.prog:
+                if kind != "compute":
+                    self.graphs.append(None)
+                    continue
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, pool=pool):
+                    for fn in item:
+                        fn()
+                pool = pool or g.pool()
+                self.graphs.append(g)
+        for (kind, item), g in zip(self.prog, self.graphs):
+            if g is not None:
+                g.replay()
+            else:
+                item()
         return self.next_tokens
 
     def logits_slice(self):

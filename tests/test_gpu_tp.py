@@ -1,6 +1,6 @@
 """Tensor-parallel decode against the single-GPU engine (bit-identical token streams and logits).
 The worker runs in child processes: alone (world 1: the sharding code with one shard) and, when two GPUs are
-visible, as two NCCL ranks (enqueued call by call: see TensorParallelDecoder on graph capture with collectives)."""
+visible, as two NCCL ranks (kernel runs between collectives replayed as CUDA graphs)."""
 import os
 import subprocess
 import sys
@@ -32,4 +32,4 @@ def test_two_ranks_equal_engine():
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    run_worker(2, 0)
+    run_worker(2, 1)
