@@ -41,6 +41,7 @@ sys.path.insert(0, str(ROOT))
 
 PROMPT_LEN = 64
 SEED = 0
+NCU_DRAM_RATIO = 8.906 / 4.462     # measured DRAM bytes per algorithmic byte of the TL1 kernel (profiles/tl1_mma_kernel_gemv_6912x2560.md)
 
 
 def measured_peaks():
@@ -195,7 +196,10 @@ def gemv_stack_roofline(engine, model, iters, peak):
     sec_per_launch = ms * 1e-3 / launches
     achieved = bytes_per_launch / sec_per_launch / 1e9
     return {"bound": "hbm", "kernel": "tl1_mma_kernel", "achieved": achieved, "peak": peak[0], "peak_source": peak[1],
-            "unit": "GB/s", "frac": achieved / peak[0], "traffic": None, "bytes_per_launch": bytes_per_launch,
+            "unit": "GB/s", "frac": achieved / peak[0], "traffic": NCU_DRAM_RATIO * bytes_per_launch,
+            "traffic_source": "ncu dram__bytes_read+write of the 6912x2560 launch (8.906 MB for 4.462 MB algorithmic: each launch also "
+                              "prefetches the next matrix into L2 and ncu flushes caches between replays), scaled to this launch mix",
+            "bytes_per_launch": bytes_per_launch,
             "us_per_launch": sec_per_launch * 1e6, "launches_timed": launches}
 
 
