@@ -115,6 +115,10 @@ typedef struct {
                               cache already holds pos[s]+1 keys, k/v are ignored */
     int heads_per_cta;     /* 0 = choose automatically; 1, 2, 4 or 8 forces the query heads one CTA processes */
     int use_pdl;
+    int tiles;             /* 0 = choose automatically; 1 = force the variant whose scoring warps read K through TMA tiles
+                              (two keys per lane; for many (sequence, kv head) items; returns -5 if it does not fit:
+                              needs four 16 KB tile rings beside the weights, n_q/n_kv <= 4 heads per CTA, cache_k and
+                              seq_stride_kv 16-byte aligned); 2 = force per-lane global loads */
 } tenzo_attention_args;
 
 TENZO_API int tenzo_cuda_attention_int8(const tenzo_attention_args* args, void* stream);

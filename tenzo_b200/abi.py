@@ -63,7 +63,7 @@ class AttentionArgs(C.Structure):
         ("pos", C.c_void_p), ("rope_cos", C.c_void_p), ("rope_sin", C.c_void_p),
         ("layer", C.c_int), ("n_q", C.c_int), ("n_kv", C.c_int), ("head_dim", C.c_int), ("max_seq", C.c_int),
         ("batch", C.c_int), ("max_len", C.c_int), ("append", C.c_int),
-        ("heads_per_cta", C.c_int), ("use_pdl", C.c_int),
+        ("heads_per_cta", C.c_int), ("use_pdl", C.c_int), ("tiles", C.c_int),
     ]
 
 

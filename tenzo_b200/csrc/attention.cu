@@ -18,12 +18,20 @@
 // all of them. With few sequences GH drops (down to 1) to put more CTAs on the machine; every CTA
 // then re-derives the new token's quantised K/V row itself (same arithmetic, same bits) and only
 // the CTA holding the group's first head stores it to the cache.
+#include <cuda.h>
+
+#include <cstring>
+
 #include "common.cuh"
 #include "../../include/tenzo_kernels.h"
 
 namespace tz {
 
 constexpr int kAttnThreads = 512;
+constexpr int kTileThreads = 384;    // block size of the variant whose scoring warps read K through TMA tiles
+constexpr int kTileKeys = 64;        // keys per tile: two per lane
+constexpr int kTileBytes = kTileKeys * 128;
+constexpr int kMaxTileWarps = kTileThreads / 32;
 constexpr int kChunk = 128;          // V rows per bulk copy (two in flight)
 constexpr int kHd = 128;             // head_dim (the reference hard-wires 16 x 8 lanes, :833-850)
 constexpr int kScoreSmemBytes = 144 * 1024;  // per-CTA budget for the score vectors [T][GH] (whole CTA stays under 227 KB)
@@ -31,6 +39,7 @@ constexpr int kScoreSmemBytes = 144 * 1024;  // per-CTA budget for the score vec
 struct AttnLaunch {
     tenzo_attention_args a;
     int gh;                          // query heads per CTA
+    int n_tile_warps;                // TMA-tile variant: warps that score (each owns a two-stage ring of 8 KB tiles)
 };
 
 // signed byte -> float without I2F: place (b ^ 0x80) in the mantissa of 2^23, subtract 2^23+128.
@@ -51,15 +60,31 @@ __device__ __forceinline__ void rope_pair(float x0, float x1, const float* cs, c
 
 template <int GH>
 struct AttnSmem {
-    // floats: s_q[GH*128] | s_new[256] | s_red[8*GH] | s_stat[2*GH+2]; then 16-byte aligned: s_new8[256 B] |
-    // mbarriers[2 x 8 B] | V double buffer [2][kChunk*128 B] | scores [T][GH] floats
+    // floats: s_q[GH*128] | s_new[256] | s_red[16*GH] | s_stat[2*GH+2]; then 16-byte aligned: s_new8[256 B] |
+    // mbarriers[2 for V + 2 per tile warp] | V double buffer [2][kChunk*128 B] | scores [T][GH] floats.
+    // TMA-tile variant: the V double buffer is the start of a 1024-byte-aligned region that first holds the scoring
+    // warps' K-tile rings (n_tile_warps x 2 x 8 KB) and is handed to the V chunks once scoring is over.
     static constexpr int n_float = GH * kHd + 2 * kHd + 16 * GH + 2 * GH + 2;
     static constexpr int new8_off = (n_float * 4 + 15) & ~15;
     static constexpr int bar_off = new8_off + 2 * kHd;
-    static constexpr int v_off = bar_off + 16;
+    static constexpr int v_off = bar_off + 16 + 16 * kMaxTileWarps;
     static constexpr int sc_off = v_off + 2 * kChunk * kHd;
     static size_t bytes(int max_len) { return (size_t)sc_off + (size_t)max_len * GH * sizeof(float); }
+    static __host__ __device__ int ring_bytes(int n_warps) { const int r = n_warps * 2 * kTileBytes; return r > 2 * kChunk * kHd ? r : 2 * kChunk * kHd; }
+    static size_t bytes_tiled(int max_len, int n_warps) { return (size_t)v_off + 1024 + ring_bytes(n_warps) + (size_t)max_len * GH * sizeof(float); }
+    static int tile_warps_that_fit(int max_len) {
+        const long long room = 227LL * 1024 - ((long long)v_off + 1024 + (long long)max_len * GH * 4);
+        const long long n = room / (2 * kTileBytes);
+        return (int)(n > kMaxTileWarps ? kMaxTileWarps : n);
+    }
 };
+
+// One 64-row x 128-byte box of the K cache (rows row0.. of sequence `seq`) into shared memory at `dst`
+// (1024-byte aligned; rows land 128 bytes apart with their 16-byte chunks XORed by row & 7).
+__device__ __forceinline__ void tma_load_k_tile(void* dst, const CUtensorMap* map, int row0, int seq, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(smem_addr(dst)), "l"(map), "r"(0), "r"(row0), "r"(seq), "r"(smem_addr(bar)) : "memory");
+}
 
 __device__ int g_attn_timeouts = 0;   // set when a bounded wait on a V-chunk copy gave up
 
@@ -184,8 +209,14 @@ __device__ __forceinline__ void exp_in_place(float* e, int n, const float* mx, i
     }
 }
 
-template <int GH>
-__global__ void __launch_bounds__(kAttnThreads) attn_kernel(const AttnLaunch L) {
+// TILED = false: 512 threads, every thread scores keys it loads itself from global memory (lowest latency; few items).
+// TILED = true:  384 threads; the first n_tile_warps warps score two keys per lane from K tiles that TMA brings into
+//                per-warp rings with the 128-byte swizzle. Direct per-lane loads of 128-byte rows cost 32 data-pipe
+//                wavefronts per instruction, and the query vector is then re-read once per key; a tile costs four
+//                wavefronts per 16-byte column and each query load serves two keys. Same arithmetic, same bits.
+template <int GH, bool TILED>
+__global__ void __launch_bounds__(TILED ? kTileThreads : kAttnThreads) attn_kernel(const AttnLaunch L, const __grid_constant__ CUtensorMap kmap) {
+    constexpr int NT = TILED ? kTileThreads : kAttnThreads;
     const tenzo_attention_args& a = L.a;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     using Lay = AttnSmem<GH>;
@@ -195,8 +226,10 @@ __global__ void __launch_bounds__(kAttnThreads) attn_kernel(const AttnLaunch L) 
     float* s_stat = s_red + 16 * GH;                                     // [GH] max, [GH] 1/sum, [2] new-row scales
     int8_t* s_new8 = reinterpret_cast<int8_t*>(smem_raw + Lay::new8_off);   // [2][128] quantised new k, v
     uint64_t* s_bar = reinterpret_cast<uint64_t*>(smem_raw + Lay::bar_off); // [2] one per V buffer
-    unsigned char* s_v = smem_raw + Lay::v_off;                          // [2][kChunk][128] V rows as in memory
-    float* s_sc = reinterpret_cast<float*>(smem_raw + Lay::sc_off);      // [T][GH] scores -> e_t -> weights
+    uint64_t* s_kbar = s_bar + 2;                                        // [n_tile_warps][2] one per K-tile stage
+    const uint32_t ring_off = TILED ? ((smem_addr(smem_raw) + (uint32_t)Lay::v_off + 1023u) & ~1023u) - smem_addr(smem_raw) : (uint32_t)Lay::v_off;
+    unsigned char* s_v = smem_raw + ring_off;                            // [2][kChunk][128] V rows as in memory (TILED: K rings first)
+    float* s_sc = reinterpret_cast<float*>(smem_raw + (TILED ? ring_off + (uint32_t)Lay::ring_bytes(L.n_tile_warps) : (uint32_t)Lay::sc_off));   // [T][GH]
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int G = a.n_q / a.n_kv;
@@ -227,13 +260,17 @@ __global__ void __launch_bounds__(kAttnThreads) attn_kernel(const AttnLaunch L) 
     if (tid == 0) {
         mbar_init(&s_bar[0], 1);
         mbar_init(&s_bar[1], 1);
+        if (TILED)
+            for (int i = 0; i < 2 * L.n_tile_warps; ++i) mbar_init(&s_kbar[i], 1);
         mbar_init_fence();
-        issue_v(0);
-        if (n_chunks > 1) issue_v(1);
+        if (!TILED) {                          // TILED: the buffers hold K tiles first; the V chunks leave after scoring
+            issue_v(0);
+            if (n_chunks > 1) issue_v(1);
+        }
     }
 
     // ---- RoPE on this CTA's query heads (pairs i, i+64; :459-480) ---------------------------------
-    for (int idx = tid; idx < GH * (kHd / 2); idx += kAttnThreads) {
+    for (int idx = tid; idx < GH * (kHd / 2); idx += NT) {
         const int g = idx / (kHd / 2), i = idx % (kHd / 2);
         const float* qh = a.q + (size_t)seq * a.q_stride + (size_t)(head0 + g) * kHd;
         float r0, r1;
@@ -291,49 +328,129 @@ __global__ void __launch_bounds__(kAttnThreads) attn_kernel(const AttnLaunch L) 
     float tmax[GH];
 #pragma unroll
     for (int g = 0; g < GH; ++g) tmax[g] = -1e30f;     // :670
-    auto load_row = [&](int t, uint4 (&r)[8]) {
-        const bool is_new = a.append && t == pos;
-        const uint4* src = is_new ? reinterpret_cast<const uint4*>(s_new8) : reinterpret_cast<const uint4*>(ck + (size_t)t * kHd);
+    bool timed_out = false;
+    if constexpr (TILED) {
+        // warp w takes tiles w, w + n_tile_warps, ...; lane l scores rows l and l + 32 of a tile (same row & 7)
+        const int n_sc = L.n_tile_warps;
+        if (warp < n_sc) {
+            const int n_tiles = (T + kTileKeys - 1) / kTileKeys;
+            const int my_tiles = warp < n_tiles ? (n_tiles - warp + n_sc - 1) / n_sc : 0;
+            unsigned char* ring = s_v + (size_t)warp * 2 * kTileBytes;
+            uint64_t* kbar = s_kbar + 2 * warp;
+            auto issue_tile = [&](int k) {
+                mbar_expect_tx(&kbar[k & 1], (unsigned)kTileBytes);
+                tma_load_k_tile(ring + (size_t)(k & 1) * kTileBytes, &kmap, (int)row_base + (warp + k * n_sc) * kTileKeys, seq, &kbar[k & 1]);
+            };
+            if (lane == 0) {
+                if (my_tiles > 0) issue_tile(0);
+                if (my_tiles > 1) issue_tile(1);
+            }
+            for (int k = 0; k < my_tiles; ++k) {
+                const int t0 = (warp + k * n_sc) * kTileKeys;
+                const unsigned char* tile = ring + (size_t)(k & 1) * kTileBytes;
+                if (lane == 0 && !mbar_wait_bounded(&kbar[k & 1], (unsigned)(k >> 1) & 1u)) timed_out = true;
+                __syncwarp();
+                const int tA = t0 + lane, tB = tA + 32;
+                const bool newA = a.append && tA == pos, newB = a.append && tB == pos;
+                const unsigned char* rowA = newA ? reinterpret_cast<const unsigned char*>(s_new8) : tile + lane * kHd;
+                const unsigned char* rowB = newB ? reinterpret_cast<const unsigned char*>(s_new8) : tile + (lane + 32) * kHd;
+                const uint32_t xa = newA ? 0u : (uint32_t)(lane & 7), xb = newB ? 0u : (uint32_t)(lane & 7);
+                float acc[2][GH][8];
 #pragma unroll
-        for (int c = 0; c < 8; ++c) r[c] = is_new ? src[c] : ld_cg_u4(src + c);
-    };
-    uint4 cur[8], nxt[8];
-    if (tid < T) load_row(tid, cur);
-    for (int t = tid; t < T; t += kAttnThreads) {
-        const bool more = t + kAttnThreads < T;
-        if (more) load_row(t + kAttnThreads, nxt);
-        float acc[GH][8];
+                for (int s2 = 0; s2 < 2; ++s2)
 #pragma unroll
-        for (int g = 0; g < GH; ++g)
+                    for (int g = 0; g < GH; ++g)
 #pragma unroll
-            for (int j = 0; j < 8; ++j) acc[g][j] = 0.0f;
+                        for (int j = 0; j < 8; ++j) acc[s2][g][j] = 0.0f;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-            const uint32_t w[4] = {cur[c].x ^ 0x80808080u, cur[c].y ^ 0x80808080u, cur[c].z ^ 0x80808080u, cur[c].w ^ 0x80808080u};
-            float kf[16];
+                for (int c = 0; c < 8; ++c) {
+                    const uint4 ka = *reinterpret_cast<const uint4*>(rowA + (((uint32_t)c ^ xa) << 4));
+                    const uint4 kb = *reinterpret_cast<const uint4*>(rowB + (((uint32_t)c ^ xb) << 4));
+                    const uint32_t wa[4] = {ka.x ^ 0x80808080u, ka.y ^ 0x80808080u, ka.z ^ 0x80808080u, ka.w ^ 0x80808080u};
+                    const uint32_t wb[4] = {kb.x ^ 0x80808080u, kb.y ^ 0x80808080u, kb.z ^ 0x80808080u, kb.w ^ 0x80808080u};
+                    float kfa[16], kfb[16];
 #pragma unroll
-            for (int e = 0; e < 16; ++e) kf[e] = s8_to_f(w[e >> 2], e & 3);
+                    for (int e = 0; e < 16; ++e) {
+                        kfa[e] = s8_to_f(wa[e >> 2], e & 3);
+                        kfb[e] = s8_to_f(wb[e >> 2], e & 3);
+                    }
 #pragma unroll
-            for (int g = 0; g < GH; ++g) {
-                const float4* q4 = reinterpret_cast<const float4*>(s_q + g * kHd + c * 16);
-                const float4 qa = q4[0], qb = q4[1], qc = q4[2], qd = q4[3];
-                const float qv[16] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w,
-                                      qc.x, qc.y, qc.z, qc.w, qd.x, qd.y, qd.z, qd.w};
+                    for (int g = 0; g < GH; ++g) {
+                        const float4* q4 = reinterpret_cast<const float4*>(s_q + g * kHd + c * 16);
+                        const float4 qa = q4[0], qb = q4[1], qc = q4[2], qd = q4[3];
+                        const float qv[16] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w,
+                                              qc.x, qc.y, qc.z, qc.w, qd.x, qd.y, qd.z, qd.w};
 #pragma unroll
-                for (int e = 0; e < 16; ++e) acc[g][e & 7] = __fmaf_rn(qv[e], kf[e], acc[g][e & 7]);
+                        for (int e = 0; e < 16; ++e) {
+                            acc[0][g][e & 7] = __fmaf_rn(qv[e], kfa[e], acc[0][g][e & 7]);
+                            acc[1][g][e & 7] = __fmaf_rn(qv[e], kfb[e], acc[1][g][e & 7]);
+                        }
+                    }
+                }
+                __syncwarp();                                 // every lane has read the tile: the stage can be refilled
+                if (lane == 0 && k + 2 < my_tiles) issue_tile(k + 2);
+#pragma unroll
+                for (int s2 = 0; s2 < 2; ++s2) {
+                    const int t = s2 ? tB : tA;
+                    if (t < T) {
+                        const float ksc = (a.append && t == pos) ? s_stat[2 * GH] : __ldcg(sk + t);
+                        const float ks = ksc * sm_scale;
+#pragma unroll
+                        for (int g = 0; g < GH; ++g) {
+                            const float* ac = acc[s2][g];
+                            const float dot = (ac[0] + ac[1] + ac[2] + ac[3] + ac[4] + ac[5] + ac[6] + ac[7]) * ks;   // :691
+                            s_sc[(size_t)t * GH + g] = dot;
+                            tmax[g] = fmaxf(tmax[g], dot);
+                        }
+                    }
+                }
             }
         }
-        const float ksc = (a.append && t == pos) ? s_stat[2 * GH] : __ldcg(sk + t);
-        const float ks = ksc * sm_scale;
-#pragma unroll
-        for (int g = 0; g < GH; ++g) {
-            const float dot = (acc[g][0] + acc[g][1] + acc[g][2] + acc[g][3] + acc[g][4] + acc[g][5] + acc[g][6] + acc[g][7]) * ks;   // :691
-            s_sc[(size_t)t * GH + g] = dot;
-            tmax[g] = fmaxf(tmax[g], dot);
-        }
-        if (more) {
-#pragma unroll
-            for (int c = 0; c < 8; ++c) cur[c] = nxt[c];
+    } else {
+        auto load_row = [&](int t, uint4 (&r)[8]) {
+            const bool is_new = a.append && t == pos;
+            const uint4* src = is_new ? reinterpret_cast<const uint4*>(s_new8) : reinterpret_cast<const uint4*>(ck + (size_t)t * kHd);
+    #pragma unroll
+            for (int c = 0; c < 8; ++c) r[c] = is_new ? src[c] : ld_cg_u4(src + c);
+        };
+        uint4 cur[8], nxt[8];
+        if (tid < T) load_row(tid, cur);
+        for (int t = tid; t < T; t += NT) {
+            const bool more = t + NT < T;
+            if (more) load_row(t + NT, nxt);
+            float acc[GH][8];
+    #pragma unroll
+            for (int g = 0; g < GH; ++g)
+    #pragma unroll
+                for (int j = 0; j < 8; ++j) acc[g][j] = 0.0f;
+    #pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const uint32_t w[4] = {cur[c].x ^ 0x80808080u, cur[c].y ^ 0x80808080u, cur[c].z ^ 0x80808080u, cur[c].w ^ 0x80808080u};
+                float kf[16];
+    #pragma unroll
+                for (int e = 0; e < 16; ++e) kf[e] = s8_to_f(w[e >> 2], e & 3);
+    #pragma unroll
+                for (int g = 0; g < GH; ++g) {
+                    const float4* q4 = reinterpret_cast<const float4*>(s_q + g * kHd + c * 16);
+                    const float4 qa = q4[0], qb = q4[1], qc = q4[2], qd = q4[3];
+                    const float qv[16] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w,
+                                          qc.x, qc.y, qc.z, qc.w, qd.x, qd.y, qd.z, qd.w};
+    #pragma unroll
+                    for (int e = 0; e < 16; ++e) acc[g][e & 7] = __fmaf_rn(qv[e], kf[e], acc[g][e & 7]);
+                }
+            }
+            const float ksc = (a.append && t == pos) ? s_stat[2 * GH] : __ldcg(sk + t);
+            const float ks = ksc * sm_scale;
+    #pragma unroll
+            for (int g = 0; g < GH; ++g) {
+                const float dot = (acc[g][0] + acc[g][1] + acc[g][2] + acc[g][3] + acc[g][4] + acc[g][5] + acc[g][6] + acc[g][7]) * ks;   // :691
+                s_sc[(size_t)t * GH + g] = dot;
+                tmax[g] = fmaxf(tmax[g], dot);
+            }
+            if (more) {
+    #pragma unroll
+                for (int c = 0; c < 8; ++c) cur[c] = nxt[c];
+            }
         }
     }
 #pragma unroll
@@ -344,14 +461,18 @@ __global__ void __launch_bounds__(kAttnThreads) attn_kernel(const AttnLaunch L) 
     __syncthreads();
     if (tid < GH) {
         float m = s_red[tid];
-        for (int w = 1; w < kAttnThreads / 32; ++w) m = fmaxf(m, s_red[w * GH + tid]);
+        for (int w = 1; w < NT / 32; ++w) m = fmaxf(m, s_red[w * GH + tid]);
         s_stat[tid] = m;
     }
     __syncthreads();
     TZ_PH(1);
 
     // ---- e_t = expf(score - max), in parallel (:826) -----------------------------------------------
-    exp_in_place<GH>(s_sc, T * GH, s_stat, tid, kAttnThreads);
+    if (TILED && tid == 0) {                   // scoring is over: the ring region now takes the V chunks
+        issue_v(0);
+        if (n_chunks > 1) issue_v(1);
+    }
+    exp_in_place<GH>(s_sc, T * GH, s_stat, tid, NT);
     __syncthreads();
     TZ_PH(2);
     // ---- sum_t e_t, left to right, one thread per head (:824-829) ----------------------------------
@@ -359,7 +480,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_kernel(const AttnLaunch L) 
     __syncthreads();
     TZ_PH(3);
     // ---- weights p_t * s_v[t] (:830, :844) ------------------------------------------------------------
-    for (int idx = tid; idx < T * GH; idx += kAttnThreads) {
+    for (int idx = tid; idx < T * GH; idx += NT) {
         const int t = idx / GH;
         const float p = s_sc[idx] * s_stat[GH + idx % GH];
         const float vs = (a.append && t == pos) ? s_stat[2 * GH + 1] : __ldcg(sv + t);
@@ -372,7 +493,6 @@ __global__ void __launch_bounds__(kAttnThreads) attn_kernel(const AttnLaunch L) 
     float o[GH];
 #pragma unroll
     for (int g = 0; g < GH; ++g) o[g] = 0.0f;
-    bool timed_out = false;
     for (int c = 0; c < n_chunks; ++c) {
         const int t0 = c * kChunk, nkeys = min(kChunk, T - t0);
         unsigned char* vb = s_v + (size_t)(c & 1) * kChunk * kHd;
@@ -395,14 +515,42 @@ __global__ void __launch_bounds__(kAttnThreads) attn_kernel(const AttnLaunch L) 
     TZ_PH(5);
 }
 
-template <int GH>
-static cudaError_t launch_attn(const AttnLaunch& L, cudaStream_t st) {
-    const size_t smem = AttnSmem<GH>::bytes(L.a.max_len);
-    cudaError_t e = cudaFuncSetAttribute(attn_kernel<GH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
+// The K cache as a 3-D byte tensor {128, rows per sequence, sequences} for the scoring warps' tile loads.
+static int make_k_tensor_map(const tenzo_attention_args& a, CUtensorMap* out) {
+    typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = nullptr;
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn)
+            return -4;
+        encode = reinterpret_cast<EncodeFn>(fn);
+    }
+    // rows reachable from the layers up to this one; tiles that run past them are zero-filled and their keys are never used
+    const cuuint64_t rows = (cuuint64_t)(a.layer + 1) * a.n_kv * a.max_seq;
+    const cuuint64_t dims[3] = {(cuuint64_t)kHd, rows, (cuuint64_t)a.batch};
+    const cuuint64_t strides[2] = {(cuuint64_t)kHd, (cuuint64_t)a.seq_stride_kv};
+    const cuuint32_t box[3] = {(cuuint32_t)kHd, (cuuint32_t)kTileKeys, 1u};
+    const cuuint32_t estr[3] = {1u, 1u, 1u};
+    const CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, a.cache_k, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : -4;
+}
+
+template <int GH, bool TILED>
+static int launch_attn(const AttnLaunch& L, cudaStream_t st) {
+    CUtensorMap kmap;
+    std::memset(&kmap, 0, sizeof kmap);
+    if (TILED)
+        if (int rc = make_k_tensor_map(L.a, &kmap)) return rc;
+    const size_t smem = TILED ? AttnSmem<GH>::bytes_tiled(L.a.max_len, L.n_tile_warps) : AttnSmem<GH>::bytes(L.a.max_len);
+    cudaError_t e = cudaFuncSetAttribute(attn_kernel<GH, TILED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(L.a.n_q / GH), (unsigned)L.a.batch, 1);
-    cfg.blockDim = dim3(kAttnThreads, 1, 1);
+    cfg.blockDim = dim3(TILED ? kTileThreads : kAttnThreads, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -410,8 +558,12 @@ static cudaError_t launch_attn(const AttnLaunch& L, cudaStream_t st) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = L.a.use_pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, attn_kernel<GH>, L);
+    e = cudaLaunchKernelEx(&cfg, attn_kernel<GH, TILED>, L, kmap);
+    return e == cudaSuccess ? 0 : (int)e;
 }
+
+template <int GH>
+static int tile_warps_for(int max_len) { return AttnSmem<GH>::tile_warps_that_fit(max_len); }
 
 // Query heads per CTA: as many as share a kv head, halved while that leaves SMs idle or the score
 // vectors [max_len][GH] would not fit in shared memory.
@@ -466,12 +618,29 @@ extern "C" int tenzo_cuda_attention_int8(const tenzo_attention_args* args, void*
     L.gh = pick_heads_per_cta(a.batch, a.n_q, group, a.max_len);
     if (a.heads_per_cta == 1 || a.heads_per_cta == 2 || a.heads_per_cta == 4 || a.heads_per_cta == 8)
         if (a.heads_per_cta <= group && (size_t)a.heads_per_cta * a.max_len * sizeof(float) <= (size_t)kScoreSmemBytes) L.gh = a.heads_per_cta;
-    cudaError_t e;
+    // Many (sequence, kv head) items: K through TMA tiles, two keys per lane. Few items (single-sequence decode): direct loads.
+    int tw = 0;
     switch (L.gh) {
-        case 1: e = launch_attn<1>(L, st); break;
-        case 2: e = launch_attn<2>(L, st); break;
-        case 4: e = launch_attn<4>(L, st); break;
-        default: e = launch_attn<8>(L, st); break;
+        case 1: tw = tile_warps_for<1>(a.max_len); break;
+        case 2: tw = tile_warps_for<2>(a.max_len); break;
+        case 4: tw = tile_warps_for<4>(a.max_len); break;
+        default: tw = 0; break;          // eight heads per CTA need more registers than the tiled variant has
     }
-    return e == cudaSuccess ? 0 : (int)e;
+    const bool tiled = a.tiles != 2 && tw >= 4 && (a.tiles == 1 || a.batch * a.n_kv >= 64) && a.seq_stride_kv % 16 == 0 &&
+                       (reinterpret_cast<uintptr_t>(a.cache_k) & 15) == 0;
+    if (a.tiles == 1 && !tiled) return -5;
+    L.n_tile_warps = tiled ? tw : 0;
+    if (tiled) {
+        switch (L.gh) {
+            case 1: return launch_attn<1, true>(L, st);
+            case 2: return launch_attn<2, true>(L, st);
+            default: return launch_attn<4, true>(L, st);
+        }
+    }
+    switch (L.gh) {
+        case 1: return launch_attn<1, false>(L, st);
+        case 2: return launch_attn<2, false>(L, st);
+        case 4: return launch_attn<4, false>(L, st);
+        default: return launch_attn<8, false>(L, st);
+    }
 }

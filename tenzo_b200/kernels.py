@@ -84,7 +84,7 @@ def rmsnorm_quant(x: torch.Tensor, norm_w=None, *, do_norm=True, eps=1e-5, qmax=
 
 
 def attention_int8(q, k, v, cache_k, cache_v, scale_k, scale_v, pos, *, layer, n_q, n_kv, max_seq, rope_cos=None,
-                   rope_sin=None, append=True, max_len=None, use_pdl=False, heads_per_cta=0, out=None):
+                   rope_sin=None, append=True, max_len=None, use_pdl=False, heads_per_cta=0, out=None, tiles=0):
     """q [batch, n_q*128], k/v [batch, n_kv*128]; caches [batch, layers, n_kv, max_seq, 128] int8 and
     [batch, layers, n_kv, max_seq] fp32; pos int32 [batch]. Returns out [batch, n_q*128]."""
     lib = load_library()
@@ -101,6 +101,7 @@ def attention_int8(q, k, v, cache_k, cache_v, scale_k, scale_v, pos, *, layer, n
     a.pos, a.rope_cos, a.rope_sin = _ptr(pos), _ptr(rope_cos), _ptr(rope_sin)
     a.layer, a.n_q, a.n_kv, a.head_dim, a.max_seq = layer, n_q, n_kv, 128, max_seq
     a.batch, a.max_len, a.append, a.use_pdl, a.heads_per_cta = batch, max_len, int(append), int(use_pdl), heads_per_cta
+    a.tiles = tiles
     _ok(lib.tenzo_cuda_attention_int8(C.byref(a), _stream()), "tenzo_cuda_attention_int8")
     return out
 

@@ -137,11 +137,13 @@ def test_attention_batched_ragged_lengths(cuda_lib):
         assert np.array_equal(host(dck)[b].reshape(-1), ock) and np.array_equal(host(dsv)[b].reshape(-1), osv)
 
 
-@pytest.mark.parametrize("B,lens_cycle,ms", [(3, [1, 256, 700], 768), (130, [1, 2, 127, 128, 129, 255, 257, 300, 384, 385, 511, 512], 512),
+@pytest.mark.parametrize("B,lens_cycle,ms", [(3, [1, 256, 700], 768), (130, [1, 2, 63, 64, 65, 127, 128, 129, 255, 257, 300, 384, 385, 511, 512], 512),
                                              (4, [8192, 4097, 8000, 1], 8192)])
-def test_attention_many_sequences_and_long_context(cuda_lib, B, lens_cycle, ms):
+@pytest.mark.parametrize("tiles", [1, 2])
+def test_attention_many_sequences_and_long_context(cuda_lib, B, lens_cycle, ms, tiles):
     """Bit for bit against the oracle: a few sequences, 130 sequences (more CTAs than SMs) with ragged lengths
-    around the 128-key chunk and 512-key pass boundaries, and an 8192-token context."""
+    around the 64-key tile, 128-key chunk and 512-key pass boundaries, and an 8192-token context; with the keys read
+    through TMA tiles (tiles=1) and by per-lane loads (tiles=2)."""
     from tenzo_b200 import kernels
     O = ora.load_oracle()
     nq, nkv, hd = 20, 5, 128
@@ -159,7 +161,7 @@ def test_attention_many_sequences_and_long_context(cuda_lib, B, lens_cycle, ms):
     cs, sn = rope_tables(ms, 10000.0)
     pos = np.array([n - 1 for n in lens], np.int32)
     out = kernels.attention_int8(dev(q), dev(k), dev(v), dck, dcv, dsk, dsv, dev(pos), layer=0, n_q=nq, n_kv=nkv, max_seq=ms,
-                                 rope_cos=dev(cs), rope_sin=dev(sn))
+                                 rope_cos=dev(cs), rope_sin=dev(sn), tiles=tiles)
     torch.cuda.synchronize()
     assert cuda_lib.tenzo_cuda_attention_take_timeouts() == 0
     got, gck, gsv = host(out), host(dck), host(dsv)
