@@ -41,7 +41,7 @@ sys.path.insert(0, str(ROOT))
 
 PROMPT_LEN = 64
 SEED = 0
-NCU_DRAM_RATIO = 8.906 / 4.462     # measured DRAM bytes per algorithmic byte of the TL1 kernel (profiles/tl1_mma_kernel_gemv_6912x2560.md)
+NCU_DRAM_RATIO = 4482816 / 4461568  # measured DRAM bytes per algorithmic byte of the TL1 kernel (profiles/tl1_mma_kernel_gemv_6912x2560.md)
 
 
 def measured_peaks():
@@ -197,8 +197,9 @@ def gemv_stack_roofline(engine, model, iters, peak):
     achieved = bytes_per_launch / sec_per_launch / 1e9
     return {"bound": "hbm", "kernel": "tl1_mma_kernel", "achieved": achieved, "peak": peak[0], "peak_source": peak[1],
             "unit": "GB/s", "frac": achieved / peak[0], "traffic": NCU_DRAM_RATIO * bytes_per_launch,
-            "traffic_source": "ncu dram__bytes_read+write of the 6912x2560 launch (8.906 MB for 4.462 MB algorithmic: each launch also "
-                              "prefetches the next matrix into L2 and ncu flushes caches between replays), scaled to this launch mix",
+            "traffic_source": "ncu dram__bytes_read+write of the 6912x2560 launch with the next-matrix L2 prefetch off (4 482 816 B for "
+                              "4 461 568 B algorithmic), scaled to this launch mix; with the prefetch on, ncu's cache flush between replays "
+                              "counts the next matrix a second time (8.9 MB)",
             "bytes_per_launch": bytes_per_launch,
             "us_per_launch": sec_per_launch * 1e6, "launches_timed": launches}
 
@@ -293,6 +294,7 @@ def main():
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--pdl", type=int, default=1)
     ap.add_argument("--heads-per-cta", type=int, default=0)
+    ap.add_argument("--no-prefetch", action="store_true", help="gemv/gemm workloads: do not ask L2 for the next matrix (for DRAM-traffic captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)

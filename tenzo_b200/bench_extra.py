@@ -52,7 +52,7 @@ def run_gemv(args):
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
             for i, w in enumerate(ws):      # each launch asks L2 for the next matrix, as the decode engine does
-                kernels.tl1_gemv(x, w, N // 64, K, [0.016], out=out, use_pdl=bool(args.pdl), prefetch=ws[(i + 1) % n_mat])
+                kernels.tl1_gemv(x, w, N // 64, K, [0.016], out=out, use_pdl=bool(args.pdl), prefetch=None if args.no_prefetch else ws[(i + 1) % n_mat])
         for _ in range(max(3, args.warmup)):
             graph.replay()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -74,8 +74,8 @@ def run_gemv(args):
                                                     f"({n_mat * N * K // 4 / 1e6:.0f} MB > L2), one graph per step", "pdl": int(args.pdl)},
         "gpu_launches": launches,
         "roofline": {"bound": "hbm", "kernel": "tl1_mma_kernel", "achieved": gbs, "peak": peak[0], "peak_source": peak[1], "unit": "GB/s",
-                     "frac": gbs / peak[0], "traffic": 8.906e6, "traffic_source": "ncu dram__bytes_read+write per launch of this workload; "
-                     "twice the algorithmic bytes because every launch also prefetches the next matrix into L2 and ncu flushes caches between replays",
+                     "frac": gbs / peak[0], "traffic": 4482816.0, "traffic_source": "ncu dram__bytes_read+write per launch of this workload run with "
+                     "--no-prefetch; with the next-matrix L2 prefetch on, ncu's cache flush between replays counts that matrix twice (8.9 MB)",
                      "bytes_per_launch": bytes_per, "us_per_launch": ms * 1e3 / launches},
     }), flush=True)
 
@@ -104,7 +104,7 @@ def run_gemm(args):
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
             for i, w in enumerate(ws):
-                kernels.tl1_gemv(x, w, N // 64, K, [0.016], out=out, use_pdl=bool(args.pdl), prefetch=ws[(i + 1) % n_mat])
+                kernels.tl1_gemv(x, w, N // 64, K, [0.016], out=out, use_pdl=bool(args.pdl), prefetch=None if args.no_prefetch else ws[(i + 1) % n_mat])
         for _ in range(max(3, args.warmup)):
             graph.replay()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
