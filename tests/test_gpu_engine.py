@@ -130,6 +130,37 @@ def test_batched_engine_equals_independent_sequences(cuda_lib):
     cpu.close()
 
 
+def test_batched_engine_on_the_tensor_core_paths_matches_the_cpu_engine(cuda_lib):
+    """32 sequences: the TL1 layers run as tcgen05 GEMMs, the LM head as a tcgen05 GEMM, attention reads K through
+    TMA tiles (32 x 2 kv heads = 64 items). Every sequence's greedy stream and the last step's logits must equal the
+    CPU engine's for that sequence alone; both the stepwise call and the device-resident greedy loop are checked."""
+    cfg = dict(synth.TINY, hidden_size=512, num_q_heads=4, num_kv_heads=2, ffn_dim=768, num_layers=2, vocab_size=2048, max_seq_len=96)
+    m = synth.SyntheticModel(cfg, seed=29)
+    B, npre, ngen = 32, 70, 10                       # context crosses the 64-key tile boundary
+    prompts = np.stack([synth.prompt_tokens(300 + b, npre, cfg["vocab_size"]) for b in range(B)])
+    want, want_logits = [], []
+    for b in (0, 7, 31):
+        cpu = best_cpu_engine(m, max_seq_len=96)
+        want.append(greedy_stream(cpu, prompts[b], ngen))
+        want_logits.append(cpu.buffer("logits", cfg["vocab_size"]))
+        cpu.close()
+    with gpu_engine(m, batch=B, max_seq_len=96) as e:
+        for t in range(npre - 1):
+            e.prefill_tokens(prompts[:, t])
+        cur, outs = prompts[:, -1].copy(), []
+        for _ in range(ngen):
+            cur = e.generate_steps(cur)
+            outs.append(cur.copy())
+        got = np.stack(outs, axis=1)
+        for i, b in enumerate((0, 7, 31)):
+            assert np.array_equal(got[b], want[i]), f"sequence {b}"
+            assert np.array_equal(e.read_buffer(15, seq=b, count=cfg["vocab_size"]), want_logits[i]), f"logits of sequence {b}"
+    with gpu_engine(m, batch=B, max_seq_len=96) as e:
+        for t in range(npre - 1):
+            e.prefill_tokens(prompts[:, t])
+        assert np.array_equal(e.decode_greedy(prompts[:, -1], ngen).T, got)
+
+
 def test_rope_theta_extension_against_oracle(cuda_lib):
     m = synth.SyntheticModel(synth.TINY, seed=24)
     o = OracleEngine(m, rope_theta=500000.0)
