@@ -161,6 +161,25 @@ def test_batched_engine_on_the_tensor_core_paths_matches_the_cpu_engine(cuda_lib
         assert np.array_equal(e.decode_greedy(prompts[:, -1], ngen).T, got)
 
 
+def test_long_decode_crosses_every_attention_bucket(cuda_lib):
+    """1100 greedy tokens of a tiny model: the step graph is re-captured for the 512-, 1024- and 2048-key attention
+    buckets and the device-resident loop hands over between them; the stream must equal the CPU engine's throughout,
+    and no kernel may have given up a bounded wait."""
+    cfg = dict(synth.TINY, max_seq_len=1200)
+    m = synth.SyntheticModel(cfg, seed=31)
+    prompt = synth.prompt_tokens(8, 6, cfg["vocab_size"])
+    cpu = best_cpu_engine(m, max_seq_len=1200)
+    want = greedy_stream(cpu, prompt, 1100)
+    cpu.close()
+    with gpu_engine(m, max_seq_len=1200) as e:
+        for t in prompt[:-1]:
+            e.prefill_token(int(t))
+        got = e.decode_greedy([int(prompt[-1])], 1100)[:, 0]
+        assert np.array_equal(got, want), f"first difference at step {int(np.argmax(got != want))}"
+        assert e.seq_len() == len(prompt) - 1 + 1100
+    assert cuda_lib.tenzo_cuda_tl1_gemv_take_timeouts() == 0 and cuda_lib.tenzo_cuda_attention_take_timeouts() == 0
+
+
 def test_rope_theta_extension_against_oracle(cuda_lib):
     m = synth.SyntheticModel(synth.TINY, seed=24)
     o = OracleEngine(m, rope_theta=500000.0)
