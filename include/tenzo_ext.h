@@ -85,6 +85,12 @@ TENZO_API tenzo_status_t tenzo_ext_rope_tables(int max_seq, int head_dim, float 
 TENZO_API int tenzo_ext_parse_manifest(const char* text, unsigned long long* views, int max_views, int* n_views,
                                        float* scales, int max_scales, int* n_scales);
 
+/* The host half of the sampler on its own (no GPU needed): the reference's streaming top-k, softmax, top-p and draw
+ * (TenzoEngine.cpp:1745-1806) over `n` (value, index) pairs given in ascending index order; indices NULL means 0..n-1
+ * (a whole logit vector). r in [0,1] replaces rand()/RAND_MAX, r < 0 draws from rand(). The engine feeds it only the
+ * logits at or above the k-th largest, selected on the device; the result equals a scan of the whole vector. */
+TENZO_API int tenzo_ext_sample_pairs(const float* values, const int* indices, int n, const tenzo_sampling_params_t* params, float r);
+
 TENZO_API const char* tenzo_ext_last_error(void);
 
 #ifdef __cplusplus

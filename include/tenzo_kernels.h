@@ -161,6 +161,17 @@ TENZO_API int tenzo_cuda_lm_head_i8_static(const float* x, const float* norm_w, 
                                            int* argmax_out, int use_pdl, void* stream);
 TENZO_API int tenzo_cuda_lm_head_static_max_batch(void);
 
+/* ---- Sampling support: repetition penalty and top-k candidate selection on the device ----------------
+ * Replaces the first half of sample_top_k_top_p (:1735-1768). tenzo_cuda_repetition_penalty applies
+ * l > 0 ? l / penalty : l * penalty to logits[tokens[i]], counts[i] times (tokens distinct).
+ * tenzo_cuda_topk_candidates finds the k-th largest logit v* (three-pass radix select, one CTA) and writes every
+ * (value, index) with value >= v* in ascending index order: *count gets their number; values/indices (each
+ * tenzo_cuda_topk_max_candidates() entries) are written only if it does not exceed that capacity. Running the
+ * reference's streaming top-k over these candidates gives the same heap as over the whole vector. */
+TENZO_API int tenzo_cuda_repetition_penalty(float* logits, int vocab, const int* tokens, const int* counts, int n, float penalty, void* stream);
+TENZO_API int tenzo_cuda_topk_candidates(const float* logits, int vocab, int k, int* count, float* values, int* indices, void* stream);
+TENZO_API int tenzo_cuda_topk_max_candidates(void);
+
 /* ---- INT8 embedding row dequantisation ---------------------------------------------------------
  * Replaces embedding_lookup's int8 branch (:1299-1315): x = (float)W8[tok] * scale[tok]. */
 TENZO_API int tenzo_cuda_embedding_i8(const int8_t* w, const float* row_scales, int hidden,

@@ -77,13 +77,14 @@ EXT_SYMBOLS = [
     "tenzo_ext_generate_step", "tenzo_ext_decode_greedy", "tenzo_ext_kv_import", "tenzo_ext_kv_export",
     "tenzo_ext_kv_fill_random", "tenzo_ext_set_seq_len", "tenzo_ext_get_seq_len", "tenzo_ext_read_buffer",
     "tenzo_ext_write_x", "tenzo_ext_run_layer", "tenzo_ext_synchronize", "tenzo_ext_last_device_ms",
-    "tenzo_ext_kernel_launches", "tenzo_ext_last_error", "tenzo_ext_bench_gemv_stack", "tenzo_ext_rope_tables", "tenzo_ext_parse_manifest",
+    "tenzo_ext_kernel_launches", "tenzo_ext_last_error", "tenzo_ext_bench_gemv_stack", "tenzo_ext_rope_tables", "tenzo_ext_parse_manifest", "tenzo_ext_sample_pairs",
 ]
 KERNEL_SYMBOLS = [
     "tenzo_cuda_tl1_gemv", "tenzo_cuda_tl1_gemv_ksplit", "tenzo_cuda_tl1_gemv_workspace_bytes", "tenzo_cuda_tl1_gemv_take_timeouts", "tenzo_cuda_rmsnorm_quant", "tenzo_cuda_attention_int8",
     "tenzo_cuda_attention_heads_per_cta", "tenzo_cuda_attention_take_timeouts", "tenzo_cuda_lm_head_i8", "tenzo_cuda_lm_head_scratch_bytes",
     "tenzo_cuda_embedding_i8", "tenzo_cuda_tl1_pack_rows2bit", "tenzo_cuda_lm_head_i8_static",
-    "tenzo_cuda_lm_head_static_max_batch", "tenzo_cuda_lm_head_take_timeouts",
+    "tenzo_cuda_lm_head_static_max_batch", "tenzo_cuda_lm_head_take_timeouts", "tenzo_cuda_repetition_penalty",
+    "tenzo_cuda_topk_candidates", "tenzo_cuda_topk_max_candidates",
 ]
 HAL_SYMBOLS = ["tenzo_hal_initialize", "tenzo_hal_bitlinear_tl1_host", "tenzo_hal_rmsnorm_host", "tenzo_hal_gemm_f32_host"]
 
@@ -137,6 +138,7 @@ def declare_ext_abi(L):
     L.tenzo_ext_bench_gemv_stack.restype = f32
     L.tenzo_ext_bench_gemv_stack.argtypes = [vp, i32, C.POINTER(C.c_ulonglong)]
     L.tenzo_ext_rope_tables.restype, L.tenzo_ext_rope_tables.argtypes = i32, [i32, i32, f32, c_f32p, c_f32p]
+    L.tenzo_ext_sample_pairs.restype, L.tenzo_ext_sample_pairs.argtypes = i32, [c_f32p, c_i32p, i32, C.POINTER(TenzoSampling), f32]
     L.tenzo_ext_parse_manifest.restype = i32
     L.tenzo_ext_parse_manifest.argtypes = [C.c_char_p, C.POINTER(C.c_ulonglong), i32, C.POINTER(i32), c_f32p, i32, C.POINTER(i32)]
     return L
@@ -159,6 +161,9 @@ def declare_kernel_abi(L):
     L.tenzo_cuda_lm_head_i8_static.argtypes = [vp, vp, i32, f32, vp, vp, i32, i32, i32, i32, vp, vp, vp, i32, vp]
     L.tenzo_cuda_lm_head_static_max_batch.restype, L.tenzo_cuda_lm_head_static_max_batch.argtypes = i32, []
     L.tenzo_cuda_lm_head_take_timeouts.restype, L.tenzo_cuda_lm_head_take_timeouts.argtypes = i32, []
+    L.tenzo_cuda_repetition_penalty.restype, L.tenzo_cuda_repetition_penalty.argtypes = i32, [vp, i32, vp, vp, i32, f32, vp]
+    L.tenzo_cuda_topk_candidates.restype, L.tenzo_cuda_topk_candidates.argtypes = i32, [vp, i32, i32, vp, vp, vp, vp]
+    L.tenzo_cuda_topk_max_candidates.restype, L.tenzo_cuda_topk_max_candidates.argtypes = i32, []
     L.tenzo_cuda_lm_head_scratch_bytes.restype, L.tenzo_cuda_lm_head_scratch_bytes.argtypes = sz, [i32]
     L.tenzo_cuda_embedding_i8.restype, L.tenzo_cuda_embedding_i8.argtypes = i32, [vp, vp, i32, vp, i32, vp, i32, vp]
     L.tenzo_cuda_tl1_pack_rows2bit.restype, L.tenzo_cuda_tl1_pack_rows2bit.argtypes = i32, [vp, i32, i32, vp, vp]

@@ -18,7 +18,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "lib" / "libtenzo_runtime.so"
-SOURCES = ["tl1_gemv.cu", "tl1_umma.cu", "norm_quant.cu", "attention.cu", "lm_head.cu", "lm_head_umma.cu", "engine.cu", "capi.cu",
+SOURCES = ["tl1_gemv.cu", "tl1_umma.cu", "norm_quant.cu", "attention.cu", "lm_head.cu", "lm_head_umma.cu", "sampler.cu", "engine.cu", "capi.cu",
            "cuda_runtime_hal.cu", "model_loader.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -12,6 +12,7 @@
 #include "../../include/tenzo_ext.h"
 #include "../../include/tenzo_kernels.h"
 #include "engine.h"
+#include "sampler.h"
 
 namespace tz {
 tenzo_status_t load_model_files(Engine& e, const char* weights_path, const char* mlir_path);
@@ -180,12 +181,7 @@ int tenzo_generate_step(tenzo_engine_t engine, int cur_token, const tenzo_sampli
         const tenzo_sampling_params_t p = params ? *params : tenzo_default_sampling_params();   // :1729-1732
         e.generate(&cur_token, &out);
         const bool penalised = p.repetition_penalty != 1.0f && past_tokens && past_tokens_len > 0;
-        if (p.temperature > 0.0f || penalised) {
-            std::vector<float> lg((size_t)e.V);
-            if (cudaMemcpy(lg.data(), e.b_logits, lg.size() * 4, cudaMemcpyDeviceToHost) != cudaSuccess)
-                throw std::runtime_error("logit read-back failed");
-            out = e.sample_host(lg, p, past_tokens, past_tokens_len);
-        }
+        if (p.temperature > 0.0f || penalised) out = e.sample(p, past_tokens, past_tokens_len);
         return TENZO_SUCCESS;
     });
     return st == TENZO_SUCCESS ? out : -1;
@@ -366,6 +362,12 @@ tenzo_status_t tenzo_ext_rope_tables(int max_seq, int head_dim, float rope_theta
     if (max_seq <= 0 || head_dim <= 0 || (head_dim & 1) || !cos_host || !sin_host) return TENZO_ERROR_INVALID_ARGUMENT;
     tz::rope_tables_host(max_seq, head_dim, rope_theta > 0.0f ? rope_theta : 10000.0f, cos_host, sin_host);
     return TENZO_SUCCESS;
+}
+
+int tenzo_ext_sample_pairs(const float* values, const int* indices, int n, const tenzo_sampling_params_t* params, float r) {
+    if (!values || n <= 0) return -1;
+    const tenzo_sampling_params_t p = params ? *params : tenzo_default_sampling_params();
+    return tz::sample_pairs(values, indices, n, p, r);
 }
 
 const char* tenzo_ext_last_error(void) { return tz::g_last_error.c_str(); }

@@ -29,6 +29,7 @@
 #include "../../include/tenzo_ext.h"
 #include "../../include/tenzo_kernels.h"
 #include "engine.h"
+#include "sampler.h"
 
 namespace tz {
 
@@ -178,6 +179,8 @@ Engine::~Engine() {
     for (auto& kv : graphs) cudaGraphExecDestroy(kv.second);
     for (void* p : owned) cudaFree(p);
     if (h_pin) cudaFreeHost(h_pin);
+    if (h_cand) cudaFreeHost(h_cand);
+    if (d_sample_past) cudaFree(d_sample_past);
     if (d_history) cudaFree(d_history);
     cudaEventDestroy(ev0);
     cudaEventDestroy(ev1);
@@ -493,23 +496,21 @@ float Engine::last_ms() {
 
 // The reference sampler (TenzoEngine.cpp:1722-1807) on host logits, for the stochastic path and
 // for greedy decoding with a repetition penalty. Candidate order follows std::pair<float,int>.
-int Engine::sample_host(std::vector<float>& lg, const tenzo_sampling_params_t& p, const int* past, int n_past) {
-    int top_k = p.top_k < 1 ? 1 : (p.top_k > 64 ? 64 : p.top_k);
-    if (p.repetition_penalty != 1.0f && past && n_past > 0)
-        for (int i = 0; i < n_past; ++i) {
-            const int t = past[i];
-            if (t >= 0 && t < V) lg[t] = lg[t] > 0.0f ? lg[t] / p.repetition_penalty : lg[t] * p.repetition_penalty;
-        }
-    if (p.temperature <= 0.0f) {
+// The reference's streaming top-k, softmax, top-p and draw (TenzoEngine.cpp:1745-1806) over pairs in ascending index order.
+int sample_pairs(const float* vals, const int* idxs, int n_in, const tenzo_sampling_params_t& p, float r_in) {
+    if (n_in <= 0) return 0;
+    if (p.temperature <= 0.0f) {                          // first maximum (:1746-1755)
         int best = 0;
-        for (int i = 1; i < V; ++i)
-            if (lg[i] > lg[best]) best = i;
-        return best;
+        for (int i = 1; i < n_in; ++i)
+            if (vals[i] > vals[best]) best = i;
+        return idxs ? idxs[best] : best;
     }
+    const int top_k = p.top_k < 1 ? 1 : (p.top_k > 64 ? 64 : p.top_k);
     float cl[64];
     int ci[64], n = 0;
-    for (int i = 0; i < V; ++i) {
-        const float l = lg[i];
+    for (int j = 0; j < n_in; ++j) {                      // sorted insert = the min-heap of (value, index) pairs, :1760-1768
+        const float l = vals[j];
+        const int i = idxs ? idxs[j] : j;
         if (n == top_k) {
             if (!(l > cl[n - 1])) continue;
             --n;
@@ -527,10 +528,53 @@ int Engine::sample_host(std::vector<float>& lg, const tenzo_sampling_params_t& p
     float sub = 0.0f;
     for (int i = 0; i < cut; ++i) sub += probs[i];
     for (int i = 0; i < cut; ++i) probs[i] /= sub;
-    const float r = static_cast<float>(std::rand()) / static_cast<float>(RAND_MAX);   // :1800, process-global rand()
+    const float r = r_in >= 0.0f ? r_in : static_cast<float>(std::rand()) / static_cast<float>(RAND_MAX);   // :1800, process-global rand()
     float acc = 0.0f;
     for (int i = 0; i < cut; ++i) { acc += probs[i]; if (r <= acc) return ci[i]; }
     return ci[0];
+}
+
+// Penalty, k-th-largest selection and candidate compaction on the device (sampler.cu), the rest on the host.
+int Engine::sample(const tenzo_sampling_params_t& p, const int* past, int n_past) {
+    if (batch != 1) throw std::invalid_argument("sampling with parameters is per sequence");
+    if (p.repetition_penalty != 1.0f && past && n_past > 0) {
+        std::map<int, int> mult;                          // once per occurrence (:1736-1742)
+        for (int i = 0; i < n_past; ++i) ++mult[past[i]];
+        std::vector<int> toks, cnts;
+        for (auto& kv : mult) { toks.push_back(kv.first); cnts.push_back(kv.second); }
+        const size_t n = toks.size();
+        if (n > sample_past_cap) {
+            if (d_sample_past) cudaFree(d_sample_past);
+            sample_past_cap = n * 2;
+            TZ_CUDA(cudaMalloc((void**)&d_sample_past, sample_past_cap * 2 * sizeof(int)));
+        }
+        TZ_CUDA(cudaMemcpyAsync(d_sample_past, toks.data(), n * 4, cudaMemcpyHostToDevice, stream));
+        TZ_CUDA(cudaMemcpyAsync(d_sample_past + sample_past_cap, cnts.data(), n * 4, cudaMemcpyHostToDevice, stream));
+        TZ_CUDA(launch_penalty(b_logits, V, d_sample_past, d_sample_past + sample_past_cap, (int)n, p.repetition_penalty, stream));
+        launches += 1;
+    }
+    const int k = p.temperature <= 0.0f ? 1 : (p.top_k < 1 ? 1 : (p.top_k > 64 ? 64 : p.top_k));
+    if (!d_cand) {
+        TZ_CUDA(cudaMalloc((void**)&d_cand, 16 + (size_t)kMaxCandidates * 8));
+        owned.push_back(d_cand);
+        TZ_CUDA(cudaMallocHost((void**)&h_cand, 16 + (size_t)kMaxCandidates * 8));
+    }
+    int* d_count = reinterpret_cast<int*>(d_cand);
+    float* d_val = reinterpret_cast<float*>(static_cast<unsigned char*>(d_cand) + 16);
+    int* d_idx = reinterpret_cast<int*>(d_val + kMaxCandidates);
+    TZ_CUDA(launch_select_candidates(b_logits, V, k, d_count, d_val, d_idx, stream));
+    launches += 1;
+    TZ_CUDA(cudaMemcpyAsync(h_cand, d_cand, 16 + (size_t)kMaxCandidates * 8, cudaMemcpyDeviceToHost, stream));
+    TZ_CUDA(cudaStreamSynchronize(stream));
+    const int count = *reinterpret_cast<const int*>(h_cand);
+    const float* hv = reinterpret_cast<const float*>(static_cast<unsigned char*>(h_cand) + 16);
+    const int* hi = reinterpret_cast<const int*>(hv + kMaxCandidates);
+    if (count > kMaxCandidates) {                         // a huge tie at the threshold: take the whole vector
+        std::vector<float> lg((size_t)V);
+        TZ_CUDA(cudaMemcpy(lg.data(), b_logits, lg.size() * 4, cudaMemcpyDeviceToHost));
+        return sample_pairs(lg.data(), nullptr, V, p, -1.0f);
+    }
+    return sample_pairs(hv, hi, count, p, -1.0f);
 }
 
 }  // namespace tz

@@ -53,7 +53,7 @@ public:
     void prefill(const int* tokens);                       // one token per sequence, no logits
     void generate(const int* cur, int* out);               // device argmax
     void decode_greedy(const int* first, int n_steps, int* out);
-    int sample_host(std::vector<float>& logits, const tenzo_sampling_params_t& p, const int* past, int n_past);
+    int sample(const tenzo_sampling_params_t& p, const int* past, int n_past);   // on the logits of the last step
 
     void push_state(const int* tokens);
     void run_step(bool with_logits, bool feed_back);
@@ -86,6 +86,9 @@ public:
     size_t kv_rows_per_seq = 0;
     float *rope_cos = nullptr, *rope_sin = nullptr;
     void *lm_scratch = nullptr, *gemv_ws = nullptr;
+    void *d_cand = nullptr, *h_cand = nullptr;           // sampler: candidate count + (value, index) pairs
+    int* d_sample_past = nullptr;
+    size_t sample_past_cap = 0;
     int *h_pin = nullptr, *h_tokens = nullptr, *h_pos = nullptr, *h_next = nullptr;
     std::vector<int> seq_len;
     std::vector<void*> owned;

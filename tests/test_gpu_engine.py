@@ -200,13 +200,12 @@ def test_sampling_paths(cuda_lib, golden):
         toks = greedy_stream(GpuAsCpuApi(e), g["prompt"], 32)
         nxt = e.generate_step(int(toks[-1]), abi.TenzoSampling(0.0, 0.9, 40, 1.3), s["past"])
         assert nxt == int(s["next_penalised"])
-        lg = e.read_buffer(15)
-        top5 = set(np.argsort(lg)[-5:].tolist())
-        e.set_seq_len(0, e.get_seq_len() - 1)
+        e.set_seq_len(0, e.get_seq_len() - 1)               # the penalty was applied to the logits in place (as in the reference)
         draws = set()
         for _ in range(20):
             draws.add(e.generate_step(int(toks[-1]), abi.TenzoSampling(0.8, 0.95, 5, 1.0)))
             e.set_seq_len(0, e.get_seq_len() - 1)
+        top5 = set(np.argsort(e.read_buffer(15))[-5:].tolist())      # logits of the last (unpenalised) step
         assert draws <= top5
 
 

@@ -277,3 +277,34 @@ def test_embedding_and_repack(cuda_lib):
     for i, tok in enumerate(toks):
         assert np.array_equal(host(x)[i], w[tok].astype(np.float32) * s[tok])
     assert np.array_equal(host(packed), synth.pack_tl1(t))
+
+
+def test_sampler_kernels_penalty_and_topk_candidates(cuda_lib):
+    """Repetition penalty (once per occurrence) and the candidate selection: count, order and contents against numpy, with
+    heavy ties, k from 1 to 64, the full vocabulary size, and the over-capacity case."""
+    L = cuda_lib
+    rng = np.random.default_rng(61)
+    for V, levels in ((1000, 5), (128256, 4000), (128256, 1 << 30), (5000, 2)):
+        logits = (rng.integers(-levels, levels, V).astype(np.float64) * (8.0 / levels)).astype(np.float32)
+        toks = np.unique(rng.integers(0, V, 50)).astype(np.int32)
+        cnts = rng.integers(1, 4, toks.size).astype(np.int32)
+        d = dev(logits)
+        assert L.tenzo_cuda_repetition_penalty(d.data_ptr(), V, dev(toks).data_ptr(), dev(cnts).data_ptr(), toks.size, 1.3, None) == 0
+        want = logits.copy()
+        for t, c in zip(toks, cnts):
+            for _ in range(c):
+                want[t] = want[t] / np.float32(1.3) if want[t] > 0 else want[t] * np.float32(1.3)
+        torch.cuda.synchronize()
+        assert np.array_equal(host(d), want)
+        cap = L.tenzo_cuda_topk_max_candidates()
+        for k in (1, 2, 40, 64):
+            cnt = torch.zeros(1, dtype=torch.int32, device="cuda")
+            vals = torch.zeros(cap, dtype=torch.float32, device="cuda")
+            idxs = torch.zeros(cap, dtype=torch.int32, device="cuda")
+            assert L.tenzo_cuda_topk_candidates(d.data_ptr(), V, k, cnt.data_ptr(), vals.data_ptr(), idxs.data_ptr(), None) == 0
+            torch.cuda.synchronize()
+            thr = np.sort(want)[::-1][k - 1]
+            sel = np.nonzero(want >= thr)[0]
+            assert int(cnt.item()) == sel.size, (V, levels, k)
+            if sel.size <= cap:
+                assert np.array_equal(host(idxs)[: sel.size], sel) and np.array_equal(host(vals)[: sel.size], want[sel])
