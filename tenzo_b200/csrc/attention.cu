@@ -250,6 +250,25 @@ __global__ void __launch_bounds__(TILED ? kTileThreads : kAttnThreads) attn_kern
     const float* cs = a.rope_cos ? a.rope_cos + (size_t)pos * (kHd / 2) : nullptr;
     const float* sn = a.rope_sin ? a.rope_sin + (size_t)pos * (kHd / 2) : nullptr;
 
+    // ---- few items (latency matters): this thread's first key row, its scale and its first value scale are requested
+    //      now, so the loads fly while the queries are rotated and the new row is quantised -------------------------
+    uint4 pre_row[8];
+    float pre_ks = 0.0f, pre_vs = 0.0f;
+    bool pre_ok = false, pre_vs_ok = false;
+    if constexpr (!TILED) {
+        if (tid < T && !(a.append && tid == pos)) {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) pre_row[c] = ld_cg_u4(reinterpret_cast<const uint4*>(ck + (size_t)tid * kHd) + c);
+            pre_ks = __ldcg(sk + tid);
+            pre_ok = true;
+        }
+        const int tw = tid / GH;
+        if (tw < T && !(a.append && tw == pos)) {
+            pre_vs = __ldcg(sv + tw);
+            pre_vs_ok = true;
+        }
+    }
+
     // ---- V chunks travel by bulk copy into a double buffer; the first two leave now and overlap the
     //      whole scoring phase. (Rows are contiguous in the cache, so a chunk is one copy.) -------------
     auto issue_v = [&](int c) {
@@ -414,7 +433,14 @@ __global__ void __launch_bounds__(TILED ? kTileThreads : kAttnThreads) attn_kern
             for (int c = 0; c < 8; ++c) r[c] = is_new ? src[c] : ld_cg_u4(src + c);
         };
         uint4 cur[8], nxt[8];
-        if (tid < T) load_row(tid, cur);
+        if (tid < T) {
+            if (pre_ok) {
+    #pragma unroll
+                for (int c = 0; c < 8; ++c) cur[c] = pre_row[c];
+            } else {
+                load_row(tid, cur);
+            }
+        }
         for (int t = tid; t < T; t += NT) {
             const bool more = t + NT < T;
             if (more) load_row(t + NT, nxt);
@@ -439,7 +465,7 @@ __global__ void __launch_bounds__(TILED ? kTileThreads : kAttnThreads) attn_kern
                     for (int e = 0; e < 16; ++e) acc[g][e & 7] = __fmaf_rn(qv[e], kf[e], acc[g][e & 7]);
                 }
             }
-            const float ksc = (a.append && t == pos) ? s_stat[2 * GH] : __ldcg(sk + t);
+            const float ksc = (a.append && t == pos) ? s_stat[2 * GH] : ((pre_ok && t == tid) ? pre_ks : __ldcg(sk + t));
             const float ks = ksc * sm_scale;
     #pragma unroll
             for (int g = 0; g < GH; ++g) {
@@ -483,7 +509,7 @@ __global__ void __launch_bounds__(TILED ? kTileThreads : kAttnThreads) attn_kern
     for (int idx = tid; idx < T * GH; idx += NT) {
         const int t = idx / GH;
         const float p = s_sc[idx] * s_stat[GH + idx % GH];
-        const float vs = (a.append && t == pos) ? s_stat[2 * GH + 1] : __ldcg(sv + t);
+        const float vs = (a.append && t == pos) ? s_stat[2 * GH + 1] : ((pre_vs_ok && idx == tid) ? pre_vs : __ldcg(sv + t));
         s_sc[idx] = p * vs;
     }
     __syncthreads();
