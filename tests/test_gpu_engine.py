@@ -161,6 +161,23 @@ def test_batched_engine_on_the_tensor_core_paths_matches_the_cpu_engine(cuda_lib
         assert np.array_equal(e.decode_greedy(prompts[:, -1], ngen).T, got)
 
 
+def test_batch_256_engine_matches_the_cpu_engine(cuda_lib):
+    """256 sequences at once (the largest tcgen05 tile: 256 accumulator columns) for a few steps; three of the
+    sequences are replayed alone on the CPU engine."""
+    cfg = dict(synth.TINY, hidden_size=256, num_q_heads=2, num_kv_heads=1, ffn_dim=384, num_layers=2, vocab_size=2048, max_seq_len=32)
+    m = synth.SyntheticModel(cfg, seed=37)
+    B, npre, ngen = 256, 5, 6
+    prompts = np.stack([synth.prompt_tokens(700 + b, npre, cfg["vocab_size"]) for b in range(B)])
+    with gpu_engine(m, batch=B, max_seq_len=32) as e:
+        for t in range(npre - 1):
+            e.prefill_tokens(prompts[:, t])
+        got = e.decode_greedy(prompts[:, -1], ngen).T
+    for b in (0, 129, 255):
+        cpu = best_cpu_engine(m, max_seq_len=32)
+        assert np.array_equal(got[b], greedy_stream(cpu, prompts[b], ngen)), f"sequence {b}"
+        cpu.close()
+
+
 def test_long_decode_crosses_every_attention_bucket(cuda_lib):
     """1100 greedy tokens of a tiny model: the step graph is re-captured for the 512-, 1024- and 2048-key attention
     buckets and the device-resident loop hands over between them; the stream must equal the CPU engine's throughout,

@@ -308,3 +308,38 @@ def test_sampler_kernels_penalty_and_topk_candidates(cuda_lib):
             assert int(cnt.item()) == sel.size, (V, levels, k)
             if sel.size <= cap:
                 assert np.array_equal(host(idxs)[: sel.size], sel) and np.array_equal(host(vals)[: sel.size], want[sel])
+
+
+def test_attention_full_benchmark_shape_variants_agree_and_match_oracle(cuda_lib):
+    """Batch 64, 20/5 heads, context 8192 (the attention benchmark's shape, 693 MB of KV): the TMA-tile variant and the
+    per-lane-load variant produce identical outputs for every sequence, and two sequences are checked against the oracle."""
+    from tenzo_b200 import kernels
+    O = ora.load_oracle()
+    B, nq, nkv, hd, T = 64, 20, 5, 128, 8192
+    g = torch.Generator(device="cuda").manual_seed(91)
+    dck = torch.randint(-127, 128, (B, 1, nkv, T, hd), generator=g, device="cuda", dtype=torch.int8)
+    dcv = torch.randint(-127, 128, (B, 1, nkv, T, hd), generator=g, device="cuda", dtype=torch.int8)
+    dsk = 0.01 + 0.02 * torch.rand(B, 1, nkv, T, generator=g, device="cuda")
+    dsv = 0.01 + 0.02 * torch.rand(B, 1, nkv, T, generator=g, device="cuda")
+    q = torch.randn(B, nq * hd, generator=g, device="cuda")
+    k = torch.randn(B, nkv * hd, generator=g, device="cuda")
+    v = torch.randn(B, nkv * hd, generator=g, device="cuda")
+    pos = torch.full((B,), T - 1, dtype=torch.int32, device="cuda")
+    pos[3] = 5000                                    # one shorter sequence
+    cs, sn = rope_tables(T, 10000.0)
+    dcs, dsn = dev(cs), dev(sn)
+    snap = {b: (host(dck[b]).reshape(-1).copy(), host(dcv[b]).reshape(-1).copy(), host(dsk[b]).reshape(-1).copy(), host(dsv[b]).reshape(-1).copy())
+            for b in (3, 63)}
+    outs = []
+    for tiles in (1, 2):
+        outs.append(host(kernels.attention_int8(q, k, v, dck, dcv, dsk, dsv, pos, layer=0, n_q=nq, n_kv=nkv, max_seq=T, max_len=T,
+                                                rope_cos=dcs, rope_sin=dsn, tiles=tiles)))
+    torch.cuda.synchronize()
+    assert cuda_lib.tenzo_cuda_attention_take_timeouts() == 0
+    assert np.array_equal(outs[0], outs[1])
+    for b in (3, 63):
+        ock, ocv, osk, osv = snap[b]
+        qq, kk, vv, o = host(q)[b].copy(), host(k)[b].copy(), host(v)[b].copy(), np.zeros(nq * hd, np.float32)
+        O.ora_attention_int8(0, int(pos[b]), nq, nkv, hd, T, 10000.0, P(qq, ora.c_f32p), P(kk, ora.c_f32p), P(vv, ora.c_f32p),
+                             P(o, ora.c_f32p), P(ock, ora.c_i8p), P(ocv, ora.c_i8p), P(osk, ora.c_f32p), P(osv, ora.c_f32p))
+        assert np.array_equal(outs[0][b], o), f"sequence {b}"
