@@ -61,7 +61,7 @@ __device__ __forceinline__ void rope_pair(float x0, float x1, const float* cs, c
 template <int GH>
 struct AttnSmem {
     // floats: s_q[GH*128] | s_new[256] | s_red[16*GH] | s_stat[2*GH+2]; then 16-byte aligned: s_new8[256 B] |
-    // mbarriers[2 for V + 2 per tile warp] | V double buffer [2][kChunk*128 B] | scores [T][GH] floats.
+    // mbarriers[2 for V + 2 per tile warp] | V double buffer [2][kChunk*128 B] | scores [GH][padded T] floats.
     // TMA-tile variant: the V double buffer is the start of a 1024-byte-aligned region that first holds the scoring
     // warps' K-tile rings (n_tile_warps x 2 x 8 KB) and is handed to the V chunks once scoring is over.
     static constexpr int n_float = GH * kHd + 2 * kHd + 16 * GH + 2 * GH + 2;
@@ -69,11 +69,12 @@ struct AttnSmem {
     static constexpr int bar_off = new8_off + 2 * kHd;
     static constexpr int v_off = bar_off + 16 + 16 * kMaxTileWarps;
     static constexpr int sc_off = v_off + 2 * kChunk * kHd;
-    static size_t bytes(int max_len) { return (size_t)sc_off + (size_t)max_len * GH * sizeof(float); }
+    static __host__ __device__ int padded(int max_len) { return (max_len + 3) & ~3; }
+    static size_t bytes(int max_len) { return (size_t)sc_off + (size_t)padded(max_len) * GH * sizeof(float); }
     static __host__ __device__ int ring_bytes(int n_warps) { const int r = n_warps * 2 * kTileBytes; return r > 2 * kChunk * kHd ? r : 2 * kChunk * kHd; }
-    static size_t bytes_tiled(int max_len, int n_warps) { return (size_t)v_off + 1024 + ring_bytes(n_warps) + (size_t)max_len * GH * sizeof(float); }
+    static size_t bytes_tiled(int max_len, int n_warps) { return (size_t)v_off + 1024 + ring_bytes(n_warps) + (size_t)padded(max_len) * GH * sizeof(float); }
     static int tile_warps_that_fit(int max_len) {
-        const long long room = 227LL * 1024 - ((long long)v_off + 1024 + (long long)max_len * GH * 4);
+        const long long room = 227LL * 1024 - ((long long)v_off + 1024 + (long long)padded(max_len) * GH * 4);
         const long long n = room / (2 * kTileBytes);
         return (int)(n > kMaxTileWarps ? kMaxTileWarps : n);
     }
@@ -97,43 +98,37 @@ __device__ unsigned long long g_attn_phase[8];
 #define TZ_PH_DECL do {} while (0)
 #endif
 
-template <int GH>
-__device__ __forceinline__ void load_weights(const float* p, float (&w)[GH]) {      // p is GH*4-byte aligned
-    if constexpr (GH == 1) {
-        w[0] = p[0];
-    } else if constexpr (GH == 2) {
-        const float2 v = *reinterpret_cast<const float2*>(p);
-        w[0] = v.x; w[1] = v.y;
-    } else {
-#pragma unroll
-        for (int h = 0; h < GH; h += 4) {
-            const float4 v = *reinterpret_cast<const float4*>(p + h);
-            w[h] = v.x; w[h + 1] = v.y; w[h + 2] = v.z; w[h + 3] = v.w;
-        }
-    }
-}
+// The scores / e_t / weights of one (sequence, kv-head group) live in shared memory head-major: w[g][t] at
+// base + g * tp + t, tp = max_len rounded up to 4. A head's values for consecutive keys are then contiguous: the
+// scoring lanes store without bank conflicts, the sequential softmax sum reads four keys per load, and the value sum
+// fetches four keys of one head per LDS.128.
 
-// Value sum over one staged chunk for output dim `vcol - chunk base`: o[g] = fma(V[t][d], w[t][g], o[g])
+// Value sum over one staged chunk for output dim `vcol - chunk base`: o[g] = fma(V[t][d], w[g][t], o[g])
 // for t in order (:842-851). Keys are taken eight at a time with the next eight already requested
 // from shared memory (two register sets, alternating), so the loads stay off the dependent chain.
+// wg = weights of head 0 at the chunk's first key (16-byte aligned: chunks start at multiples of 128 keys).
 template <int GH>
-__device__ __forceinline__ void value_sum_chunk(const unsigned char* vcol, const float* wg, int nkeys, float (&o)[GH]) {
+__device__ __forceinline__ void value_sum_chunk(const unsigned char* vcol, const float* wg, int tp, int nkeys, float (&o)[GH]) {
     constexpr int U = 8;
     uint32_t va[U], vb[U];
-    float wa[U][GH], wb[U][GH];
-    auto loadg = [&](int gi, uint32_t (&v)[U], float (&w)[U][GH]) {
+    float wa[GH][U], wb[GH][U];
+    auto loadg = [&](int gi, uint32_t (&v)[U], float (&w)[GH][U]) {
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            v[u] = vcol[(gi * U + u) * kHd];
-            load_weights<GH>(wg + (size_t)(gi * U + u) * GH, w[u]);
+        for (int u = 0; u < U; ++u) v[u] = vcol[(gi * U + u) * kHd];
+#pragma unroll
+        for (int g = 0; g < GH; ++g) {
+            const float4* p = reinterpret_cast<const float4*>(wg + (size_t)g * tp + gi * U);
+            const float4 lo = p[0], hi = p[1];
+            w[g][0] = lo.x; w[g][1] = lo.y; w[g][2] = lo.z; w[g][3] = lo.w;
+            w[g][4] = hi.x; w[g][5] = hi.y; w[g][6] = hi.z; w[g][7] = hi.w;
         }
     };
-    auto compg = [&](const uint32_t (&v)[U], const float (&w)[U][GH]) {
+    auto compg = [&](const uint32_t (&v)[U], const float (&w)[GH][U]) {
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const float vf = __uint_as_float((v[u] ^ 0x80u) | 0x4B000000u) - 8388736.0f;
 #pragma unroll
-            for (int g = 0; g < GH; ++g) o[g] = __fmaf_rn(vf, w[u][g], o[g]);
+            for (int g = 0; g < GH; ++g) o[g] = __fmaf_rn(vf, w[g][u], o[g]);
         }
     };
     const int full = nkeys / U;
@@ -150,27 +145,31 @@ __device__ __forceinline__ void value_sum_chunk(const unsigned char* vcol, const
     for (int kl = full * U; kl < nkeys; ++kl) {
         const uint32_t b = vcol[kl * kHd];
         const float vf = __uint_as_float((b ^ 0x80u) | 0x4B000000u) - 8388736.0f;
-        float w[GH];
-        load_weights<GH>(wg + (size_t)kl * GH, w);
 #pragma unroll
-        for (int g = 0; g < GH; ++g) o[g] = __fmaf_rn(vf, w[g], o[g]);
+        for (int g = 0; g < GH; ++g) o[g] = __fmaf_rn(vf, wg[(size_t)g * tp + kl], o[g]);
     }
 }
 
-// sum_t e[t*stride], left to right (:824-829): sixteen loads in flight while the previous sixteen are added.
-__device__ __forceinline__ float sequential_sum(const float* e, int T, int stride) {
-    constexpr int U = 16;
-    float a[U], b[U];
+// sum_t e[t], left to right (:824-829), e 16-byte aligned and contiguous: four keys per load, sixteen keys in flight
+// while the previous sixteen are added (a dependent fp32 add takes 4.5 cycles; one load per add would double that).
+__device__ __forceinline__ float sequential_sum(const float* e, int T) {
+    const float4* p = reinterpret_cast<const float4*>(e);
+    float4 a[4], b[4];
     float sum = 0.0f;
-    auto loadg = [&](int gi, float (&v)[U]) {
+    auto loadg = [&](int gi, float4 (&v)[4]) {
 #pragma unroll
-        for (int u = 0; u < U; ++u) v[u] = e[(size_t)(gi * U + u) * stride];
+        for (int u = 0; u < 4; ++u) v[u] = p[gi * 4 + u];
     };
-    auto addg = [&](const float (&v)[U]) {
+    auto addg = [&](const float4 (&v)[4]) {
 #pragma unroll
-        for (int u = 0; u < U; ++u) sum = __fadd_rn(sum, v[u]);
+        for (int u = 0; u < 4; ++u) {
+            sum = __fadd_rn(sum, v[u].x);
+            sum = __fadd_rn(sum, v[u].y);
+            sum = __fadd_rn(sum, v[u].z);
+            sum = __fadd_rn(sum, v[u].w);
+        }
     };
-    const int full = T / U;
+    const int full = T / 16;
     int gi = 0;
     if (full > 0) loadg(0, a);
     while (gi + 1 < full) {
@@ -181,30 +180,36 @@ __device__ __forceinline__ float sequential_sum(const float* e, int T, int strid
         gi += 2;
     }
     if (gi < full) addg(a);
-    for (int t = full * U; t < T; ++t) sum = __fadd_rn(sum, e[(size_t)t * stride]);
+    for (int t = full * 16; t < T; ++t) sum = __fadd_rn(sum, e[t]);
     return sum;
 }
 
-// e[i] = expf(e[i] - max[i % GH]) for i < n, by all `n_threads` threads of the CTA (whole warps).
+// e[g][t] = expf(e[g][t] - max[g]) for t < T, by all `n_threads` threads of the CTA (whole warps: the table
+// lookup is a shuffle, so every lane makes every call).
 template <int GH>
-__device__ __forceinline__ void exp_in_place(float* e, int n, const float* mx, int tid, int n_threads) {
+__device__ __forceinline__ void exp_in_place(float* e, int T, int tp, const float* mx, int tid, int n_threads) {
     const int lane = tid & 31;
     const unsigned long long tab = kExp2fTab[lane];
     const uint32_t tab_lo = (uint32_t)tab, tab_hi = (uint32_t)(tab >> 32);
     constexpr int U = 4;
-    for (int base = 0; base < n; base += U * n_threads) {
-        float x[U];
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int idx = base + u * n_threads + tid;
-            x[u] = idx < n ? e[idx] - mx[idx % GH] : 0.0f;
-        }
+    for (int g = 0; g < GH; ++g) {
+        float* row = e + (size_t)g * tp;
+        const float m = mx[g];
+        for (int base = 0; base < T; base += U * n_threads) {
+            float x[U];
 #pragma unroll
-        for (int u = 0; u < U; ++u) x[u] = expf_reference_bits_lanes(x[u], tab_lo, tab_hi);
+            for (int u = 0; u < U; ++u) {
+                const int t = base + u * n_threads + tid;
+                x[u] = t < T ? row[t] - m : 0.0f;
+            }
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int idx = base + u * n_threads + tid;
-            if (idx < n) e[idx] = x[u];
+            for (int u = 0; u < U; ++u) x[u] = expf_reference_bits_lanes(x[u], tab_lo, tab_hi);
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int t = base + u * n_threads + tid;
+                if (t < T) row[t] = x[u];
+            }
         }
     }
 }
@@ -229,9 +234,10 @@ __global__ void __launch_bounds__(TILED ? kTileThreads : kAttnThreads) attn_kern
     uint64_t* s_kbar = s_bar + 2;                                        // [n_tile_warps][2] one per K-tile stage
     const uint32_t ring_off = TILED ? ((smem_addr(smem_raw) + (uint32_t)Lay::v_off + 1023u) & ~1023u) - smem_addr(smem_raw) : (uint32_t)Lay::v_off;
     unsigned char* s_v = smem_raw + ring_off;                            // [2][kChunk][128] V rows as in memory (TILED: K rings first)
-    float* s_sc = reinterpret_cast<float*>(smem_raw + (TILED ? ring_off + (uint32_t)Lay::ring_bytes(L.n_tile_warps) : (uint32_t)Lay::sc_off));   // [T][GH]
+    float* s_sc = reinterpret_cast<float*>(smem_raw + (TILED ? ring_off + (uint32_t)Lay::ring_bytes(L.n_tile_warps) : (uint32_t)Lay::sc_off));   // [GH][tp]
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tp = Lay::padded(a.max_len);
     const int G = a.n_q / a.n_kv;
     const int head0 = blockIdx.x * GH, kvh = head0 / G, seq = blockIdx.y;
     const bool stores_new_row = (head0 % G) == 0;
@@ -262,9 +268,8 @@ __global__ void __launch_bounds__(TILED ? kTileThreads : kAttnThreads) attn_kern
             pre_ks = __ldcg(sk + tid);
             pre_ok = true;
         }
-        const int tw = tid / GH;
-        if (tw < T && !(a.append && tw == pos)) {
-            pre_vs = __ldcg(sv + tw);
+        if (tid < T && !(a.append && tid == pos)) {      // first element of the weights pass: head 0, key tid
+            pre_vs = __ldcg(sv + tid);
             pre_vs_ok = true;
         }
     }
@@ -418,7 +423,7 @@ __global__ void __launch_bounds__(TILED ? kTileThreads : kAttnThreads) attn_kern
                         for (int g = 0; g < GH; ++g) {
                             const float* ac = acc[s2][g];
                             const float dot = (ac[0] + ac[1] + ac[2] + ac[3] + ac[4] + ac[5] + ac[6] + ac[7]) * ks;   // :691
-                            s_sc[(size_t)t * GH + g] = dot;
+                            s_sc[(size_t)g * tp + t] = dot;
                             tmax[g] = fmaxf(tmax[g], dot);
                         }
                     }
@@ -470,7 +475,7 @@ __global__ void __launch_bounds__(TILED ? kTileThreads : kAttnThreads) attn_kern
     #pragma unroll
             for (int g = 0; g < GH; ++g) {
                 const float dot = (acc[g][0] + acc[g][1] + acc[g][2] + acc[g][3] + acc[g][4] + acc[g][5] + acc[g][6] + acc[g][7]) * ks;   // :691
-                s_sc[(size_t)t * GH + g] = dot;
+                s_sc[(size_t)g * tp + t] = dot;
                 tmax[g] = fmaxf(tmax[g], dot);
             }
             if (more) {
@@ -498,19 +503,22 @@ __global__ void __launch_bounds__(TILED ? kTileThreads : kAttnThreads) attn_kern
         issue_v(0);
         if (n_chunks > 1) issue_v(1);
     }
-    exp_in_place<GH>(s_sc, T * GH, s_stat, tid, NT);
+    exp_in_place<GH>(s_sc, T, tp, s_stat, tid, NT);
     __syncthreads();
     TZ_PH(2);
     // ---- sum_t e_t, left to right, one thread per head (:824-829) ----------------------------------
-    if (tid < GH) s_stat[GH + tid] = 1.0f / sequential_sum(s_sc + tid, T, GH);
+    if (tid < GH) s_stat[GH + tid] = 1.0f / sequential_sum(s_sc + (size_t)tid * tp, T);
     __syncthreads();
     TZ_PH(3);
     // ---- weights p_t * s_v[t] (:830, :844) ------------------------------------------------------------
-    for (int idx = tid; idx < T * GH; idx += NT) {
-        const int t = idx / GH;
-        const float p = s_sc[idx] * s_stat[GH + idx % GH];
-        const float vs = (a.append && t == pos) ? s_stat[2 * GH + 1] : ((pre_vs_ok && idx == tid) ? pre_vs : __ldcg(sv + t));
-        s_sc[idx] = p * vs;
+#pragma unroll
+    for (int g = 0; g < GH; ++g) {
+        float* row = s_sc + (size_t)g * tp;
+        const float inv_sum = s_stat[GH + g];
+        for (int t = tid; t < T; t += NT) {
+            const float vs = (a.append && t == pos) ? s_stat[2 * GH + 1] : ((pre_vs_ok && t == tid) ? pre_vs : __ldcg(sv + t));
+            row[t] = (row[t] * inv_sum) * vs;
+        }
     }
     __syncthreads();
     TZ_PH(4);
@@ -529,7 +537,7 @@ __global__ void __launch_bounds__(TILED ? kTileThreads : kAttnThreads) attn_kern
             if (tid < 8) reinterpret_cast<uint4*>(vb + (size_t)(pos - t0) * kHd)[tid] = reinterpret_cast<const uint4*>(s_new8 + kHd)[tid];
             __syncthreads();
         }
-        if (tid < kHd) value_sum_chunk<GH>(vb + tid, s_sc + (size_t)t0 * GH, nkeys, o);
+        if (tid < kHd) value_sum_chunk<GH>(vb + tid, s_sc + t0, tp, nkeys, o);
         __syncthreads();                                         // buffer free again
         if (tid == 0 && c + 2 < n_chunks) issue_v(c + 2);
     }
