@@ -74,6 +74,12 @@ TENZO_API float tenzo_ext_bench_gemv_stack(tenzo_engine_t engine, int iters, uns
 /* Number of kernels launched (or replayed through a graph) since the engine was created. */
 TENZO_API unsigned long long tenzo_ext_kernel_launches(tenzo_engine_t engine);
 /* Message for the most recent failure on this thread ("" if none). */
+/* Chunked prefill (single-sequence engines): feeds n consecutive prompt tokens through every layer together - the
+ * TL1 layers as GEMMs over the n rows, causal attention as n queries over the one cache - instead of n calls of
+ * tenzo_prefill_token (TenzoEngine.cpp:1809-1819, main_inference.cpp:469-474 of the reference). Cache contents, state
+ * and every later token are bit-identical to the token-by-token path. */
+TENZO_API tenzo_status_t tenzo_ext_prefill_chunk(tenzo_engine_t engine, const int* tokens, int n);
+
 /* RoPE tables cos/sin [max_seq][head_dim/2] as the engine builds them (the reference's float expressions,
  * TenzoEngine.cpp:466-469), written to host memory: for callers that drive the per-kernel entry points
  * themselves (tensor-parallel decode) and need the same bits. */

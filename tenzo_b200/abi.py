@@ -77,7 +77,7 @@ EXT_SYMBOLS = [
     "tenzo_ext_generate_step", "tenzo_ext_decode_greedy", "tenzo_ext_kv_import", "tenzo_ext_kv_export",
     "tenzo_ext_kv_fill_random", "tenzo_ext_set_seq_len", "tenzo_ext_get_seq_len", "tenzo_ext_read_buffer",
     "tenzo_ext_write_x", "tenzo_ext_run_layer", "tenzo_ext_synchronize", "tenzo_ext_last_device_ms",
-    "tenzo_ext_kernel_launches", "tenzo_ext_last_error", "tenzo_ext_bench_gemv_stack", "tenzo_ext_rope_tables", "tenzo_ext_parse_manifest", "tenzo_ext_sample_pairs",
+    "tenzo_ext_kernel_launches", "tenzo_ext_last_error", "tenzo_ext_bench_gemv_stack", "tenzo_ext_rope_tables", "tenzo_ext_parse_manifest", "tenzo_ext_sample_pairs", "tenzo_ext_prefill_chunk",
 ]
 KERNEL_SYMBOLS = [
     "tenzo_cuda_tl1_gemv", "tenzo_cuda_tl1_gemv_ksplit", "tenzo_cuda_tl1_gemv_workspace_bytes", "tenzo_cuda_tl1_gemv_take_timeouts", "tenzo_cuda_rmsnorm_quant", "tenzo_cuda_attention_int8",
@@ -139,6 +139,7 @@ def declare_ext_abi(L):
     L.tenzo_ext_bench_gemv_stack.argtypes = [vp, i32, C.POINTER(C.c_ulonglong)]
     L.tenzo_ext_rope_tables.restype, L.tenzo_ext_rope_tables.argtypes = i32, [i32, i32, f32, c_f32p, c_f32p]
     L.tenzo_ext_sample_pairs.restype, L.tenzo_ext_sample_pairs.argtypes = i32, [c_f32p, c_i32p, i32, C.POINTER(TenzoSampling), f32]
+    L.tenzo_ext_prefill_chunk.restype, L.tenzo_ext_prefill_chunk.argtypes = i32, [vp, c_i32p, i32]
     L.tenzo_ext_parse_manifest.restype = i32
     L.tenzo_ext_parse_manifest.argtypes = [C.c_char_p, C.POINTER(C.c_ulonglong), i32, C.POINTER(i32), c_f32p, i32, C.POINTER(i32)]
     return L

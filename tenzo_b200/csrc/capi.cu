@@ -358,6 +358,14 @@ float tenzo_ext_bench_gemv_stack(tenzo_engine_t engine, int iters, unsigned long
 
 unsigned long long tenzo_ext_kernel_launches(tenzo_engine_t engine) { return live(engine) ? engine->impl->launches : 0ull; }
 
+tenzo_status_t tenzo_ext_prefill_chunk(tenzo_engine_t engine, const int* tokens, int n) {
+    if (!live(engine) || !tokens || n < 0) return TENZO_ERROR_INVALID_ARGUMENT;
+    return guarded([&]() -> tenzo_status_t {
+        engine->impl->prefill_chunk(tokens, n);
+        return TENZO_SUCCESS;
+    });
+}
+
 tenzo_status_t tenzo_ext_rope_tables(int max_seq, int head_dim, float rope_theta, float* cos_host, float* sin_host) {
     if (max_seq <= 0 || head_dim <= 0 || (head_dim & 1) || !cos_host || !sin_host) return TENZO_ERROR_INVALID_ARGUMENT;
     tz::rope_tables_host(max_seq, head_dim, rope_theta > 0.0f ? rope_theta : 10000.0f, cos_host, sin_host);

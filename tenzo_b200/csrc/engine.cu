@@ -27,6 +27,7 @@
 
 #include "../../include/tenzo.h"
 #include "../../include/tenzo_ext.h"
+#include "common.cuh"
 #include "../../include/tenzo_kernels.h"
 #include "engine.h"
 #include "sampler.h"
@@ -68,6 +69,46 @@ __global__ void advance_kernel(int* pos, int* tokens, const int* next, int batch
 __global__ void record_tokens_kernel(const int* next, int* history, int step, int batch) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < batch) history[(size_t)step * batch + i] = next[i];
+}
+
+// Chunked prefill: rotate and quantise the K rows, quantise the V rows of M consecutive tokens of one sequence and
+// append them at positions pos0.. (the same arithmetic as the attention kernel's own append, TenzoEngine.cpp:459-533).
+// One warp per (token, kv head, K|V); lane l holds elements 4l..4l+3.
+__global__ void __launch_bounds__(64) kv_append_rows_kernel(const float* qkv, int row_stride, int q_dim, int kv_dim, int n_kv, int pos0,
+                                                            const float* rope_cos, const float* rope_sin, int8_t* cache_k, int8_t* cache_v,
+                                                            float* scale_k, float* scale_v, size_t layer_row_base, int max_seq) {
+    const int token = blockIdx.x, kvh = blockIdx.y, is_v = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int pos = pos0 + token;
+    const float* src = qkv + (size_t)token * row_stride + q_dim + (is_v ? kv_dim : 0) + kvh * 128;
+    float x[4];
+    if (is_v) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) x[j] = __ldcg(src + lane * 4 + j);
+    } else {
+        const float* cs = rope_cos + (size_t)pos * 64;
+        const float* sn = rope_sin + (size_t)pos * 64;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int e = lane * 4 + j, i = e & 63;
+            const float x0 = __ldcg(src + i), x1 = __ldcg(src + i + 64), c = cs[i], sgn = sn[i];
+            x[j] = e < 64 ? __fmaf_rn(x0, c, -(x1 * sgn)) : __fmaf_rn(x0, sgn, x1 * c);      // :475-476
+        }
+    }
+    float amax = 1e-8f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) amax = fmaxf(amax, fabsf(x[j]));
+    amax = tz::warp_max(amax);
+    const float sc = amax / 127.0f;           // :522
+    const float inv = 1.0f / sc;              // :527
+    uint32_t packed = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float qf = fminf(fmaxf(roundf(x[j] * inv), -128.0f), 127.0f);   // :530
+        packed |= ((uint32_t)(uint8_t)(int8_t)(int)qf) << (8 * j);
+    }
+    const size_t row = layer_row_base + (size_t)kvh * max_seq + pos;
+    reinterpret_cast<uint32_t*>((is_v ? cache_v : cache_k) + row * 128)[lane] = packed;
+    if (lane == 0) (is_v ? scale_v : scale_k)[row] = sc;
 }
 
 // Deterministic stand-in KV: int8 rows and positive scales from a counter hash.
@@ -180,6 +221,8 @@ Engine::~Engine() {
     for (void* p : owned) cudaFree(p);
     if (h_pin) cudaFreeHost(h_pin);
     if (h_cand) cudaFreeHost(h_cand);
+    for (void* p : {(void*)pf_x, (void*)pf_qkv, (void*)pf_attn, (void*)pf_h1, (void*)pf_act, (void*)pf_tokens, (void*)pf_pos, pf_ws})
+        if (p) cudaFree(p);
     if (d_sample_past) cudaFree(d_sample_past);
     if (d_history) cudaFree(d_history);
     cudaEventDestroy(ev0);
@@ -337,6 +380,97 @@ void Engine::enqueue_step(bool with_logits, bool feed_back, int max_len) {
     advance_kernel<<<(batch + 127) / 128, 128, 0, stream>>>(d_pos, d_tokens, d_next, batch, feed_back ? 1 : 0);
     TZ_CUDA(cudaGetLastError());
     launches += 1;
+}
+
+static int bucket_for(int len, int max_seq);
+
+// Chunked prefill of one sequence: M prompt tokens go through every layer together - the TL1 layers as GEMMs over the
+// M rows, the K/V rows appended first, then causal attention as M independent queries over the same cache (token i sees
+// keys 0..pos0+i). Row i of every product is the same arithmetic as feeding token i alone, so the cache and the state
+// after the chunk are bit-identical to M calls of prefill().
+void Engine::prefill_chunk(const int* tokens, int M) {
+    if (batch != 1) throw std::invalid_argument("chunked prefill is for single-sequence engines");
+    if (M <= 0) return;
+    if (!lm_w) throw std::runtime_error("LM head / embedding was never set");
+    if (seq_len[0] + M > cfg.max_seq_len) throw std::out_of_range("KV cache is full (max_seq_len reached)");
+    for (int i = 0; i < M; ++i)
+        if (tokens[i] < 0 || tokens[i] >= V) throw std::out_of_range("token id outside [0, vocab_size)");
+    if (M > pf_cap) {
+        for (void* p : {(void*)pf_x, (void*)pf_qkv, (void*)pf_attn, (void*)pf_h1, (void*)pf_act, (void*)pf_tokens, (void*)pf_pos, pf_ws})
+            if (p) cudaFree(p);
+        pf_cap = M;
+        const size_t m = (size_t)M;
+        TZ_CUDA(cudaMalloc((void**)&pf_x, m * h * 4));
+        TZ_CUDA(cudaMalloc((void**)&pf_qkv, m * (qd + 2 * kvd) * 4));
+        TZ_CUDA(cudaMalloc((void**)&pf_attn, m * qd * 4));
+        TZ_CUDA(cudaMalloc((void**)&pf_h1, m * h * 4));
+        TZ_CUDA(cudaMalloc((void**)&pf_act, m * ffn * 4));
+        TZ_CUDA(cudaMalloc((void**)&pf_tokens, m * 4));
+        TZ_CUDA(cudaMalloc((void**)&pf_pos, m * 4));
+        TZ_CUDA(cudaMalloc(&pf_ws, tenzo_cuda_tl1_gemv_workspace_bytes(M > 1 ? M : 2, h > ffn ? h : ffn)));
+    }
+    const int pos0 = seq_len[0];
+    std::vector<int> hp(M);
+    for (int i = 0; i < M; ++i) hp[i] = pos0 + i;
+    TZ_CUDA(cudaMemcpyAsync(pf_tokens, tokens, (size_t)M * 4, cudaMemcpyHostToDevice, stream));
+    TZ_CUDA(cudaMemcpyAsync(pf_pos, hp.data(), (size_t)M * 4, cudaMemcpyHostToDevice, stream));
+    TZ_CUDA(cudaEventRecord(ev0, stream));
+    TZ_KERNEL(tenzo_cuda_embedding_i8(lm_w, lm_scales, h, pf_tokens, M, pf_x, h, stream));
+    launches += 1;
+    const int gemv_kernels = M > 1 ? 2 : 1;
+    const int max_len = bucket_for(pos0 + M, cfg.max_seq_len);
+    for (int l = 0; l < L; ++l) {
+        const LayerDev& d = layers[l];
+        if (!d.set) throw std::runtime_error("layer weights were never set");
+        tenzo_tl1_gemv_args g;
+        std::memset(&g, 0, sizeof g);
+        g.do_norm = 1; g.eps = 1e-5f; g.batch = M; g.workspace = pf_ws; g.use_pdl = 0;
+        g.x = pf_x; g.x_stride = h; g.norm_w = d.in_norm; g.w = d.qkv; g.K = h;
+        g.n_blocks = (qd + 2 * kvd) / 64;
+        g.seg_end[0] = qd / 64; g.seg_end[1] = (qd + kvd) / 64; g.seg_end[2] = g.n_blocks;
+        g.seg_scale[0] = d.s_q; g.seg_scale[1] = d.s_k; g.seg_scale[2] = d.s_v;
+        g.epilogue = TENZO_EPI_STORE; g.out = pf_qkv; g.out_stride = qd + 2 * kvd;
+        TZ_KERNEL(tenzo_cuda_tl1_gemv(&g, stream));
+        const size_t layer_row_base = (size_t)l * cfg.num_kv_heads * cfg.max_seq_len;
+        kv_append_rows_kernel<<<dim3((unsigned)M, (unsigned)cfg.num_kv_heads), 64, 0, stream>>>(
+            pf_qkv, qd + 2 * kvd, qd, kvd, cfg.num_kv_heads, pos0, rope_cos, rope_sin, cache_k, cache_v, scale_k, scale_v, layer_row_base,
+            cfg.max_seq_len);
+        TZ_CUDA(cudaGetLastError());
+        tenzo_attention_args a;
+        std::memset(&a, 0, sizeof a);
+        a.q = pf_qkv; a.out = pf_attn; a.q_stride = a.kv_stride = qd + 2 * kvd;
+        a.cache_k = cache_k; a.cache_v = cache_v; a.scale_k = scale_k; a.scale_v = scale_v;
+        a.seq_stride_kv = 0; a.seq_stride_sc = 0;          // every query row reads the one sequence's cache
+        a.pos = pf_pos; a.rope_cos = rope_cos; a.rope_sin = rope_sin;
+        a.layer = l; a.n_q = cfg.num_q_heads; a.n_kv = cfg.num_kv_heads; a.head_dim = 128;
+        a.max_seq = cfg.max_seq_len; a.batch = M; a.max_len = max_len; a.append = 0; a.tiles = 2;
+        TZ_KERNEL(tenzo_cuda_attention_int8(&a, stream));
+        g.x = pf_attn; g.x_stride = qd; g.norm_w = d.attn_sub_norm; g.w = d.o; g.K = h;
+        g.n_blocks = h / 64; g.seg_end[0] = g.seg_end[1] = g.seg_end[2] = g.n_blocks; g.seg_scale[0] = d.s_o;
+        g.epilogue = TENZO_EPI_RESIDUAL; g.resid = pf_x; g.out = pf_h1; g.out_stride = h;
+        TZ_KERNEL(tenzo_cuda_tl1_gemv(&g, stream));
+        launches += 2 * gemv_kernels + 2;
+        if (d.has_mlp) {
+            g.x = pf_h1; g.x_stride = h; g.norm_w = d.post_norm; g.w = d.gateup; g.K = h;
+            g.n_blocks = 2 * ffn / 64; g.seg_end[0] = ffn / 64; g.seg_end[1] = g.seg_end[2] = g.n_blocks;
+            g.seg_scale[0] = d.s_gate; g.seg_scale[1] = d.s_up;
+            g.epilogue = TENZO_EPI_RELU2_GLU; g.resid = nullptr; g.out = pf_act; g.out_stride = ffn;
+            TZ_KERNEL(tenzo_cuda_tl1_gemv(&g, stream));
+            g.x = pf_act; g.x_stride = ffn; g.norm_w = d.ffn_sub_norm; g.w = d.down; g.K = ffn;
+            g.n_blocks = h / 64; g.seg_end[0] = g.seg_end[1] = g.seg_end[2] = g.n_blocks; g.seg_scale[0] = d.s_down;
+            g.epilogue = TENZO_EPI_RESIDUAL; g.resid = pf_h1; g.out = pf_x; g.out_stride = h;
+            TZ_KERNEL(tenzo_cuda_tl1_gemv(&g, stream));
+            launches += 2 * gemv_kernels;
+        } else {
+            TZ_CUDA(cudaMemcpyAsync(pf_x, pf_h1, (size_t)M * h * 4, cudaMemcpyDeviceToDevice, stream));   // :1630
+        }
+    }
+    // the engine's single-token state after the chunk: residual stream of the last token, position
+    TZ_CUDA(cudaMemcpyAsync(b_x, pf_x + (size_t)(M - 1) * h, (size_t)h * 4, cudaMemcpyDeviceToDevice, stream));
+    TZ_CUDA(cudaEventRecord(ev1, stream));
+    TZ_CUDA(cudaStreamSynchronize(stream));
+    seq_len[0] += M;
+    check_device_status(false);
 }
 
 static int bucket_for(int len, int max_seq) {

@@ -51,6 +51,7 @@ public:
     void set_lm_head(const int8_t* w, const float* scales);
 
     void prefill(const int* tokens);                       // one token per sequence, no logits
+    void prefill_chunk(const int* tokens, int n);          // n consecutive tokens of the one sequence, together
     void generate(const int* cur, int* out);               // device argmax
     void decode_greedy(const int* first, int n_steps, int* out);
     int sample(const tenzo_sampling_params_t& p, const int* past, int n_past);   // on the logits of the last step
@@ -86,6 +87,9 @@ public:
     size_t kv_rows_per_seq = 0;
     float *rope_cos = nullptr, *rope_sin = nullptr;
     void *lm_scratch = nullptr, *gemv_ws = nullptr;
+    float *pf_x = nullptr, *pf_qkv = nullptr, *pf_attn = nullptr, *pf_h1 = nullptr, *pf_act = nullptr;   // chunked prefill rows
+    int *pf_tokens = nullptr, *pf_pos = nullptr, pf_cap = 0;
+    void* pf_ws = nullptr;
     void *d_cand = nullptr, *h_cand = nullptr;           // sampler: candidate count + (value, index) pairs
     int* d_sample_past = nullptr;
     size_t sample_past_cap = 0;

@@ -112,6 +112,11 @@ class Engine:
         assert t.size == self.batch
         self._check(self.lib.tenzo_ext_prefill_tokens(self._h, _p(t, abi.c_i32p)), "tenzo_ext_prefill_tokens")
 
+    def prefill_chunk(self, tokens: Sequence[int]):
+        """All of `tokens` (consecutive tokens of the one sequence) through the layers together."""
+        t = np.ascontiguousarray(tokens, dtype=np.int32)
+        self._check(self.lib.tenzo_ext_prefill_chunk(self._h, _p(t, abi.c_i32p), int(t.size)), "tenzo_ext_prefill_chunk")
+
     def generate_steps(self, cur_tokens: Sequence[int]) -> np.ndarray:
         t = np.ascontiguousarray(cur_tokens, dtype=np.int32)
         out = np.zeros(self.batch, np.int32)

@@ -313,3 +313,31 @@ def test_load_model_from_files_matches_the_cpu_engine(tmp_path, with_manifest):
         short.write_bytes(w.read_bytes()[: cfg["vocab_size"] * cfg["hidden_size"] * 4 + 1000])
         e.load_model(str(short), str(m))                   # tensors past the end become ones / zero weights, as in the reference
         assert e.lib.tenzo_load_model(e.get_raw_handle(), str(tmp_path / "missing.bin").encode(), str(m).encode()) == abi.ERR_IO
+
+
+def test_chunked_prefill_equals_token_by_token(cuda_lib):
+    """tenzo_ext_prefill_chunk (prompt rows through the GEMM path, K/V appended, causal attention as independent queries)
+    leaves the same KV cache bytes and scales as token-by-token prefill and the same greedy continuation, which is also
+    the CPU engine's. Chunks of 1, 15 (per-sequence kernels), 16+ (tensor cores) and a chunk that starts mid-sequence."""
+    cfg = dict(synth.TINY, hidden_size=512, num_q_heads=4, num_kv_heads=2, ffn_dim=768, num_layers=2, vocab_size=2048, max_seq_len=400)
+    m = synth.SyntheticModel(cfg, seed=41)
+    prompt = synth.prompt_tokens(12, 301, cfg["vocab_size"])
+    cpu = best_cpu_engine(m, max_seq_len=400)
+    want = greedy_stream(cpu, prompt, 12)
+    cpu.close()
+    with gpu_engine(m, max_seq_len=400) as ref:
+        for t in prompt[:-1]:
+            ref.prefill_token(int(t))
+        kv_ref = [ref.kv_export(0, l, 300) for l in range(cfg["num_layers"])]
+        assert np.array_equal(ref.decode_greedy([int(prompt[-1])], 12)[:, 0], want)
+    for chunks in ([300], [1, 15, 16, 100, 168], [37, 263]):
+        with gpu_engine(m, max_seq_len=400) as e:
+            at = 0
+            for c in chunks:
+                e.prefill_chunk(prompt[at:at + c])
+                at += c
+            assert at == 300 and e.seq_len() == 300
+            for l in range(cfg["num_layers"]):
+                for got, ref_part in zip(e.kv_export(0, l, 300), kv_ref[l]):
+                    assert np.array_equal(got, ref_part), f"layer {l}, chunks {chunks}"
+            assert np.array_equal(e.decode_greedy([int(prompt[-1])], 12)[:, 0], want), f"chunks {chunks}"
