@@ -252,6 +252,23 @@ def run_decode_b1(args):
     e2e_s = max_over_ranks(e2e_s, world)
     same_stream = bool(np.array_equal(np.asarray(toks_e2e), toks_dev[:, 0]))
 
+    # ---- prompt processing: token by token (the reference's loop) against one chunk through the batched path -----
+    eng.reset()
+    t0 = time.perf_counter()
+    for t in prompt[:-1]:
+        eng.prefill_token(int(t))
+    eng.synchronize()
+    pf_tokens_s = time.perf_counter() - t0
+    first_after_tokens = int(eng.decode_greedy([int(prompt[-1])], 1)[0, 0])
+    eng.reset()
+    eng.prefill_chunk(prompt[:-1])                  # warm-up (buffers, function attributes)
+    eng.reset()
+    t0 = time.perf_counter()
+    eng.prefill_chunk(prompt[:-1])
+    eng.synchronize()
+    pf_chunk_s = time.perf_counter() - t0
+    first_after_chunk = int(eng.decode_greedy([int(prompt[-1])], 1)[0, 0])
+
     roof = cpu = None
     if rank == 0:
         roof = gemv_stack_roofline(eng, model, 20, measured_peaks())
@@ -274,6 +291,8 @@ def run_decode_b1(args):
             "e2e": {"value": total / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 4,
                     "same_tokens_as_device_loop": same_stream},
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roof, "cpu_baseline": cpu,
+            "prefill": {"prompt_tokens": PROMPT_LEN - 1, "token_by_token_ms": 1e3 * pf_tokens_s, "chunked_ms": 1e3 * pf_chunk_s,
+                        "same_next_token": first_after_chunk == first_after_tokens},
             "hbm_frac_whole_token": model.weight_bytes_per_token() / (dev_ms * 1e-3 / args.steps) / 1e9 / measured_peaks()[0],
         }
         print(json.dumps(line), flush=True)
