@@ -18,6 +18,12 @@
 // all of them. With few sequences GH drops (down to 1) to put more CTAs on the machine; every CTA
 // then re-derives the new token's quantised K/V row itself (same arithmetic, same bits) and only
 // the CTA holding the group's first head stores it to the cache.
+//
+// Two instantiations: per-lane global loads of the key rows (few items, lowest latency: single-sequence
+// decode) and K tiles brought in by TMA with the 128-byte swizzle, two keys per lane (64 or more
+// (sequence, kv head) items). What bounds both long phases is the shared-memory return path, not HBM
+// or arithmetic: the query vector is re-read (broadcast LDS.128) for every key or key pair while
+// scoring, and every value warp re-reads the weights of its keys.
 #include <cuda.h>
 
 #include <cstring>
