@@ -80,6 +80,11 @@ def load_oracle():
         "ora_kv_quant_row": (f32, [c_f32p, i32, c_i8p]),
         "ora_attention_int8": (None, [i32, i32, i32, i32, i32, i32, f32, c_f32p, c_f32p, c_f32p, c_f32p,
                                       c_i8p, c_i8p, c_f32p, c_f32p]),
+        "ora_attention_paged_int8": (None, [i32, i32, i32, i32, i32, i32, f32, c_f32p, c_f32p, c_f32p, c_f32p,
+                                            c_i8p, c_i8p, c_f32p, c_f32p, c_i32p]),
+        "ora_engine_use_paged_kv": (None, [vp]),
+        "ora_engine_paged_kv": (None, [vp, C.POINTER(c_i8p), C.POINTER(c_i8p), C.POINTER(c_f32p), C.POINTER(c_f32p),
+                                       C.POINTER(c_i32p), C.POINTER(i32)]),
         "ora_embedding_i8": (None, [c_i8p, c_f32p, i32, i32, c_f32p]),
         "ora_act_quant127": (f32, [c_f32p, i32, c_i8p]),
         "ora_lm_head_i8": (None, [c_i8p, f32, c_i8p, c_f32p, i32, i32, c_f32p, c_i32p]),
@@ -138,6 +143,15 @@ def load_ref(kind: str = "kernels"):
             "refk_kv_k": (c_i8p, [vp]), "refk_kv_v": (c_i8p, [vp]),
             "refk_kv_k_scales": (c_f32p, [vp]), "refk_kv_v_scales": (c_f32p, [vp]),
             "refk_kv_attention": (None, [vp, i32, c_f32p, c_f32p, c_f32p, c_f32p]),
+            "refk_paged_create": (vp, [i32, i32, i32, i32, i32]),
+            "refk_paged_destroy": (None, [vp]),
+            "refk_paged_set_len": (None, [vp, i32]),
+            "refk_paged_k": (c_i8p, [vp]), "refk_paged_v": (c_i8p, [vp]),
+            "refk_paged_k_scales": (c_f32p, [vp]), "refk_paged_v_scales": (c_f32p, [vp]),
+            "refk_paged_table": (i32, [vp, c_i32p, i32]),
+            "refk_paged_push_block": (None, [vp, i32]),
+            "refk_paged_attention": (None, [vp, i32, c_f32p, c_f32p, c_f32p, c_f32p]),
+            "refk_engine_paged_kv": (vp, [vp]),
             "refk_engine_buffer": (c_f32p, [vp, i32]),
             "refk_engine_x_i8": (c_i8p, [vp]),
             "refk_engine_kv": (vp, [vp]),

@@ -73,6 +73,42 @@ void refk_kv_attention(void* kv, int layer, float* q, float* k, float* v, float*
     static_cast<tenzo::FusedKVCache*>(kv)->forward_attention_raw(layer, q, k, v, out);
 }
 
+// PagedKVCache (kv_mode "paged_int8", TenzoEngine.h:154-193); pools and block table are public members.
+__attribute__((visibility("default")))
+void* refk_paged_create(int layers, int q_heads, int kv_heads, int head_dim, int total_blocks) {
+    return new tenzo::PagedKVCache(layers, q_heads, kv_heads, head_dim, total_blocks);
+}
+__attribute__((visibility("default")))
+void refk_paged_destroy(void* kv) { delete static_cast<tenzo::PagedKVCache*>(kv); }
+__attribute__((visibility("default")))
+void refk_paged_set_len(void* kv, int len) { static_cast<tenzo::PagedKVCache*>(kv)->cur_seq_len = len; }
+__attribute__((visibility("default")))
+int8_t* refk_paged_k(void* kv) { return static_cast<tenzo::PagedKVCache*>(kv)->paged_k_pool.data(); }
+__attribute__((visibility("default")))
+int8_t* refk_paged_v(void* kv) { return static_cast<tenzo::PagedKVCache*>(kv)->paged_v_pool.data(); }
+__attribute__((visibility("default")))
+float* refk_paged_k_scales(void* kv) { return static_cast<tenzo::PagedKVCache*>(kv)->paged_k_scales.data(); }
+__attribute__((visibility("default")))
+float* refk_paged_v_scales(void* kv) { return static_cast<tenzo::PagedKVCache*>(kv)->paged_v_scales.data(); }
+// Block table as the cache holds it after the calls so far; returns its length.
+__attribute__((visibility("default")))
+int refk_paged_table(void* kv, int32_t* out, int max_n) {
+    auto& t = static_cast<tenzo::PagedKVCache*>(kv)->block_table;
+    for (int i = 0; i < static_cast<int>(t.size()) && i < max_n; ++i) out[i] = t[i];
+    return static_cast<int>(t.size());
+}
+// Hands the next logical block a physical block chosen by the caller (the reference's own allocator only ever
+// yields 0, 1, 2, ...): lets a test exercise the table translation with a scattered placement.
+__attribute__((visibility("default")))
+void refk_paged_push_block(void* kv, int32_t blk) { static_cast<tenzo::PagedKVCache*>(kv)->block_table.push_back(blk); }
+// forward_attention_raw (TenzoEngine.cpp:242-445); does not advance cur_seq_len.
+__attribute__((visibility("default")))
+void refk_paged_attention(void* kv, int layer, float* q, float* k, float* v, float* out) {
+    static_cast<tenzo::PagedKVCache*>(kv)->forward_attention_raw(layer, q, k, v, out);
+}
+__attribute__((visibility("default")))
+void* refk_engine_paged_kv(tenzo_engine_t e) { return &e->impl->paged_kv_cache; }
+
 // Engine internals for teacher forcing (TenzoEngine.h:195-262, all public).
 // which: 0 x, 1 norm_x, 2 q, 3 k, 4 v, 5 attn_out, 6 attn_sub, 7 out, 8 h1, 9 post_norm,
 //        10 gate, 11 up, 12 act, 13 ffn_norm, 14 down, 15 logits

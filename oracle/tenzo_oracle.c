@@ -255,6 +255,76 @@ void ora_attention_int8(int layer, int pos, int n_q, int n_kv, int head_dim, int
     }
 }
 
+/* PagedKVCache::forward_attention_raw (:242-445). Not the int8_fused arithmetic with another address
+ * map: the dot product runs in two sets of eight FMA lanes (elements d..d+7 and d+8..d+15 of every
+ * 16, :371-381) added lane by lane (:382) and then left to right starting from 0.0f (:385-386), the
+ * score is (dot * s_k) * (1/sqrt(hd)) (:388), the weights are e_t * (1/(sum + 1e-8f)) (:400-403)
+ * and keys whose weight is below 1e-7f are skipped (:416). Pools are
+ * [block][n_layers][kv_head][16][head_dim] (scales [..][16]); block_table[b] is the physical block
+ * of tokens 16b..16b+15 and must already hold an entry for pos/16 (the reference takes one from its
+ * free list at :294-300 when layer 0 reaches a new block). */
+void ora_attention_paged_int8(int layer, int pos, int n_q, int n_kv, int head_dim, int n_layers, float theta,
+                              float* q, float* k, float* v, float* out,
+                              int8_t* pool_k, int8_t* pool_v, float* pool_sk, float* pool_sv,
+                              const int32_t* block_table) {
+    enum { BS = 16 };
+    float cs[256], sn[256];
+    ora_rope_table(pos, head_dim, theta, cs, sn);                      /* :250-289 */
+    ora_rope_apply(q, n_q, head_dim, cs, sn);
+    ora_rope_apply(k, n_kv, head_dim, cs, sn);
+
+    const int slot = pos % BS;
+    const int32_t new_blk = block_table[pos / BS];
+    for (int h = 0; h < n_kv; ++h) {                                   /* :318-347 */
+        size_t row = (((size_t)new_blk * n_layers + layer) * n_kv + h) * BS + slot;
+        pool_sk[row] = ora_kv_quant_row(k + (size_t)h * head_dim, head_dim, pool_k + row * head_dim);
+        pool_sv[row] = ora_kv_quant_row(v + (size_t)h * head_dim, head_dim, pool_v + row * head_dim);
+    }
+
+    const int T = pos + 1, group = n_q / n_kv;
+    const float qk_scale = 1.0f / sqrtf((float)head_dim);             /* :352 */
+#pragma omp parallel for schedule(dynamic, 2)
+    for (int qh = 0; qh < n_q; ++qh) {
+        const int kvh = qh / group;
+        const float* qv = q + (size_t)qh * head_dim;
+        float* p = (float*)malloc((size_t)T * sizeof(float));
+        float mx = -1e30f;                                             /* :360 */
+        for (int t = 0; t < T; ++t) {
+            const size_t row = (((size_t)block_table[t / BS] * n_layers + layer) * n_kv + kvh) * BS + t % BS;
+            const int8_t* kr = pool_k + row * head_dim;
+            float a0[8] = {0, 0, 0, 0, 0, 0, 0, 0}, a1[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            for (int d = 0; d < head_dim; d += 16)                     /* :371-381 */
+                for (int j = 0; j < 8; ++j) {
+                    a0[j] = fmaf(qv[d + j], (float)kr[d + j], a0[j]);
+                    a1[j] = fmaf(qv[d + 8 + j], (float)kr[d + 8 + j], a1[j]);
+                }
+            float dot = 0.0f;
+            for (int j = 0; j < 8; ++j) dot += a0[j] + a1[j];          /* :382-386 */
+            const float score = dot * pool_sk[row] * qk_scale;         /* :388 */
+            p[t] = score;
+            mx = mx > score ? mx : score;
+        }
+        float sum = 0.0f;                                              /* :395-403 */
+        for (int t = 0; t < T; ++t) {
+            p[t] = expf(p[t] - mx);
+            sum += p[t];
+        }
+        const float inv = 1.0f / (sum + 1e-8f);
+        for (int t = 0; t < T; ++t) p[t] *= inv;
+
+        float* o = out + (size_t)qh * head_dim;
+        for (int d = 0; d < head_dim; ++d) o[d] = 0.0f;
+        for (int t = 0; t < T; ++t) {                                  /* :409-441 */
+            if (p[t] < 1e-7f) continue;
+            const size_t row = (((size_t)block_table[t / BS] * n_layers + layer) * n_kv + kvh) * BS + t % BS;
+            const int8_t* vr = pool_v + row * head_dim;
+            const float wgt = p[t] * pool_sv[row];
+            for (int d = 0; d < head_dim; ++d) o[d] = fmaf(wgt, (float)vr[d], o[d]);
+        }
+        free(p);
+    }
+}
+
 /* ------------------------------------------------------------------------------------------- */
 /* embedding, LM head, sampler                                                                 */
 /* ------------------------------------------------------------------------------------------- */
@@ -360,6 +430,11 @@ struct ora_engine {
     int seq_len;
     float* buf[16];
     int8_t* x8;
+    /* kv_mode "paged_int8" (:1218-1220): pools, block table, blocks handed out so far */
+    int paged, total_blocks, n_table;
+    int8_t *pk, *pv;
+    float *psk, *psv;
+    int32_t* table;
 };
 
 ora_engine* ora_engine_create(const ora_config* cfg) {
@@ -383,7 +458,34 @@ ora_engine* ora_engine_create(const ora_config* cfg) {
 void ora_engine_destroy(ora_engine* e) {
     if (!e) return;
     for (int i = 0; i < 16; ++i) free(e->buf[i]);
-    free(e->x8); free(e->ck); free(e->cv); free(e->sk); free(e->sv); free(e->L); free(e);
+    free(e->x8); free(e->ck); free(e->cv); free(e->sk); free(e->sv); free(e->L);
+    free(e->pk); free(e->pv); free(e->psk); free(e->psv); free(e->table); free(e);
+}
+
+/* kv_mode = "paged_int8": (max_seq+15)/16 blocks of 16 tokens (:1218), scales preset to 1 (:238-239).
+ * The reference's free list hands out block 0, 1, 2, ... after every reset (TenzoEngine.h:128-141: filled
+ * from total-1 down to 0 and popped from the back), so a counter restates it. */
+void ora_engine_use_paged_kv(ora_engine* e) {
+    const ora_config* c = &e->c;
+    if (e->paged) return;
+    e->paged = 1;
+    e->total_blocks = (c->max_seq + 15) / 16;
+    size_t rows = (size_t)e->total_blocks * c->layers * c->n_kv * 16;
+    e->pk = (int8_t*)calloc(rows * c->head_dim, 1);
+    e->pv = (int8_t*)calloc(rows * c->head_dim, 1);
+    e->psk = (float*)malloc(rows * sizeof(float));
+    e->psv = (float*)malloc(rows * sizeof(float));
+    for (size_t i = 0; i < rows; ++i) e->psk[i] = e->psv[i] = 1.0f;
+    e->table = (int32_t*)calloc((size_t)e->total_blocks + 1, sizeof(int32_t));
+    e->n_table = 0;
+}
+void ora_engine_paged_kv(ora_engine* e, int8_t** k, int8_t** v, float** sk, float** sv, int32_t** table, int* n_table) {
+    if (k) *k = e->pk;
+    if (v) *v = e->pv;
+    if (sk) *sk = e->psk;
+    if (sv) *sv = e->psv;
+    if (table) *table = e->table;
+    if (n_table) *n_table = e->n_table;
 }
 
 void ora_engine_set_layer(ora_engine* e, int layer, const ora_layer* w) {
@@ -392,7 +494,7 @@ void ora_engine_set_layer(ora_engine* e, int layer, const ora_layer* w) {
 }
 void ora_engine_set_final_norm(ora_engine* e, const float* w) { e->final_norm = w; }
 void ora_engine_set_lm_head_i8(ora_engine* e, const int8_t* w, const float* s) { e->lm_w = w; e->lm_s = s; }
-void ora_engine_reset(ora_engine* e) { e->seq_len = 0; }
+void ora_engine_reset(ora_engine* e) { e->seq_len = 0; e->n_table = 0; }
 int ora_engine_seq_len(const ora_engine* e) { return e->seq_len; }
 float* ora_engine_buffer(ora_engine* e, int which) { return (which >= 0 && which < 16) ? e->buf[which] : NULL; }
 void ora_engine_kv(ora_engine* e, int8_t** k, int8_t** v, float** sk, float** sv) {
@@ -419,8 +521,17 @@ void ora_engine_forward_layer(ora_engine* e, int l) {                  /* :1538-
     ora_bitlinear_tl1(b[B_NORM], w->k_w, kvd, h, w->k_s, b[B_K], NULL);
     ora_bitlinear_tl1(b[B_NORM], w->v_w, kvd, h, w->v_s, b[B_V], NULL);
 
-    ora_attention_int8(l, e->seq_len, c->n_q, c->n_kv, c->head_dim, c->max_seq, c->rope_theta,
-                       b[B_Q], b[B_K], b[B_V], b[B_ATT], e->ck, e->cv, e->sk, e->sv);
+    if (e->paged) {
+        if (e->seq_len / 16 >= e->n_table && e->n_table < e->total_blocks) {   /* :294-300 */
+            e->table[e->n_table] = e->n_table;
+            e->n_table += 1;
+        }
+        ora_attention_paged_int8(l, e->seq_len, c->n_q, c->n_kv, c->head_dim, c->layers, c->rope_theta,
+                                 b[B_Q], b[B_K], b[B_V], b[B_ATT], e->pk, e->pv, e->psk, e->psv, e->table);
+    } else {
+        ora_attention_int8(l, e->seq_len, c->n_q, c->n_kv, c->head_dim, c->max_seq, c->rope_theta,
+                           b[B_Q], b[B_K], b[B_V], b[B_ATT], e->ck, e->cv, e->sk, e->sv);
+    }
 
     ora_rms_norm(b[B_ATT], w->attn_sub_norm, b[B_ATTSUB], h, 1e-5f);  /* :1582 uses hidden, not q_dim */
     ora_bitlinear_tl1(b[B_ATTSUB], w->o_w, h, h, w->o_s, b[B_OUT], NULL);

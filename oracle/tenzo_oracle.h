@@ -1,7 +1,7 @@
 /* CPU oracle for the quantized decode path — TEST INFRASTRUCTURE, NOT PRODUCT CODE.
  *
  * A plain-C restatement of what the reference engine (src/runtime/TenzoEngine.cpp of
- * catdlia/tenzo) computes for one decoded token in its "cpu" device, int8_fused KV mode, with
+ * catdlia/tenzo) computes for one decoded token in its "cpu" device, int8_fused (or paged_int8) KV mode, with
  * TL1-packed ternary layers and an INT8 LM head. Every function names the reference lines it
  * follows. Only tests, the smoke check and the CPU-baseline leg of the benchmark may load this
  * library; the CUDA product never does.
@@ -64,6 +64,15 @@ void ora_attention_int8(int layer, int pos, int n_q, int n_kv, int head_dim, int
                         float* q, float* k, float* v, float* out,
                         int8_t* cache_k, int8_t* cache_v, float* scale_k, float* scale_v);
 
+/* PagedKVCache::forward_attention_raw (kv_mode "paged_int8", :242-445): same RoPE and append, but the
+ * pools are [block][n_layers][kv_head][16][head_dim] behind block_table, and the arithmetic differs
+ * from int8_fused (two sets of eight FMA lanes, (dot*s_k)*scale, 1/(sum+1e-8), weights < 1e-7
+ * skipped). block_table must already map logical block pos/16. */
+void ora_attention_paged_int8(int layer, int pos, int n_q, int n_kv, int head_dim, int n_layers, float theta,
+                              float* q, float* k, float* v, float* out,
+                              int8_t* pool_k, int8_t* pool_v, float* pool_sk, float* pool_sv,
+                              const int32_t* block_table);
+
 /* ---- embedding, LM head, sampler ------------------------------------------------------------ */
 /* x = (float)W8[tok] * scale[tok]. TenzoEngine.cpp:1299-1315. */
 void ora_embedding_i8(const int8_t* w, const float* scales, int hidden, int tok, float* x);
@@ -97,6 +106,9 @@ void ora_engine_destroy(ora_engine* e);
 void ora_engine_set_layer(ora_engine* e, int layer, const ora_layer* w);
 void ora_engine_set_final_norm(ora_engine* e, const float* w);
 void ora_engine_set_lm_head_i8(ora_engine* e, const int8_t* w, const float* scales);
+/* Switch a fresh engine to kv_mode "paged_int8" (:1218-1220, :1575-1576). */
+void ora_engine_use_paged_kv(ora_engine* e);
+void ora_engine_paged_kv(ora_engine* e, int8_t** k, int8_t** v, float** sk, float** sv, int32_t** table, int* n_table);
 void ora_engine_reset(ora_engine* e);
 int ora_engine_seq_len(const ora_engine* e);
 void ora_engine_prefill(ora_engine* e, int tok);                       /* :1809-1819 */

@@ -108,9 +108,10 @@ class SyntheticModel:
 
     def config_struct(self, lib=None, **overrides) -> abi.TenzoConfig:
         c = abi.TenzoConfig()
+        kv_mode = overrides.pop("kv_mode", "int8_fused")
         for k, v in {**self.cfg, **overrides}.items():
             setattr(c, k, v)
-        c.kv_mode = b"int8_fused"
+        c.kv_mode = kv_mode.encode() if isinstance(kv_mode, str) else kv_mode
         c.device = b"cpu"
         return c
 

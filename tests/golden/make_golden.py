@@ -118,6 +118,53 @@ def engine_cases():
     r.close()
 
 
+def paged_cases():
+    """kv_mode "paged_int8": PagedKVCache::forward_attention_raw with the blocks placed out of order, and whole-engine streams."""
+    L, nq, nkv, hd, blocks, layer, steps = 2, 8, 2, 128, 20, 1, 300
+    rng = np.random.default_rng(15)
+    order = rng.permutation(blocks).astype(np.int32)
+    kv = R.refk_paged_create(L, nq, nkv, hd, blocks)
+    q = rng.standard_normal((steps, nq * hd)).astype(np.float32)
+    q[::7] *= 4.0                                   # peaked softmax rows: some weights fall under the 1e-7 cut
+    k = rng.standard_normal((steps, nkv * hd)).astype(np.float32)
+    v = rng.standard_normal((steps, nkv * hd)).astype(np.float32)
+    outs = np.zeros((steps, nq * hd), np.float32)
+    for t in range(steps):
+        if t % 16 == 0:
+            R.refk_paged_push_block(kv, int(order[t // 16]))
+        qq, kk, vv = q[t].copy(), k[t].copy(), v[t].copy()
+        R.refk_paged_set_len(kv, t)
+        R.refk_paged_attention(kv, layer, P(qq, ora.c_f32p), P(kk, ora.c_f32p), P(vv, ora.c_f32p), P(outs[t], ora.c_f32p))
+    rows = blocks * L * nkv * 16
+    keep = [0, 1, 15, 16, 17, 127, 128, 255, 256, 299]
+    np.savez_compressed(HERE / "attention_paged.npz", qkv_sha=np.array(sha(np.concatenate([q, k, v], axis=1))), order=order,
+                        pool_k=ora.view(R.refk_paged_k(kv), rows * hd, np.int8).reshape(blocks, L, nkv, 16, hd).copy(),
+                        pool_v=ora.view(R.refk_paged_v(kv), rows * hd, np.int8).reshape(blocks, L, nkv, 16, hd).copy(),
+                        scale_k=ora.view(R.refk_paged_k_scales(kv), rows, np.float32).reshape(blocks, L, nkv, 16).copy(),
+                        scale_v=ora.view(R.refk_paged_v_scales(kv), rows, np.float32).reshape(blocks, L, nkv, 16).copy(),
+                        keep=np.array(keep), outs=outs[keep], dims=np.array([L, nq, nkv, hd, blocks, steps, layer]))
+    R.refk_paged_destroy(kv)
+    # whole engine, tiny shape and BitNet-2B shape (same models and prompts as engine_cases)
+    out = {}
+    m = synth.SyntheticModel(synth.TINY, seed=3)
+    r = RefEngine(m, kv_mode="paged_int8")
+    prompt = synth.prompt_tokens(3, 16, synth.TINY["vocab_size"])
+    out["tiny_prompt"], out["tiny_tokens"] = prompt, greedy_stream(r, prompt, 32)
+    out["tiny_logits"], out["tiny_attn_out"] = r.buffer("logits", 1024), r.buffer("attn_out", 256)
+    r.close()
+    cfg = dict(synth.BITNET_2B, max_seq_len=256)
+    m = synth.SyntheticModel(cfg, seed=0)
+    r = RefEngine(m, kv_mode="paged_int8")
+    prompt = synth.prompt_tokens(0, 64, cfg["vocab_size"])
+    out["b2_prompt"], out["b2_tokens"] = prompt, greedy_stream(r, prompt, 32)
+    lg = r.buffer("logits", cfg["vocab_size"])
+    top = np.argsort(lg)[-16:][::-1]
+    out["b2_top_idx"], out["b2_top_val"], out["b2_logits_sha"] = top.astype(np.int32), lg[top], np.array(sha(lg))
+    out["b2_attn_out_sha"] = np.array(sha(r.buffer("attn_out", cfg["hidden_size"])))
+    r.close()
+    np.savez_compressed(HERE / "engine_paged.npz", **out)
+
+
 def lm_head_case():
     rng = np.random.default_rng(14)
     V, H = 500, 256
@@ -137,10 +184,8 @@ def lm_head_case():
 
 
 if __name__ == "__main__":
-    gemv_cases()
-    norm_cases()
-    attention_case()
-    lm_head_case()
-    engine_cases()
+    groups = dict(gemv=gemv_cases, norm=norm_cases, attention=attention_case, lm_head=lm_head_case, engine=engine_cases, paged=paged_cases)
+    for name in (sys.argv[1:] or list(groups)):      # no arguments: everything; else only the named groups
+        groups[name]()
     for f in sorted(HERE.glob("*.npz")):
         print(f.name, f.stat().st_size)

@@ -19,10 +19,10 @@ from tenzo_b200 import abi, synth  # noqa: E402
 class RefEngine:
     """The unmodified reference engine (compiled by oracle/Makefile) loaded with a SyntheticModel."""
 
-    def __init__(self, model: synth.SyntheticModel, max_seq_len: int | None = None, kind: str = "kernels"):
+    def __init__(self, model: synth.SyntheticModel, max_seq_len: int | None = None, kind: str = "kernels", kv_mode: str = "int8_fused"):
         self.L = ora.load_ref(kind)
         self.model = model
-        self.cfg = model.config_struct(**({"max_seq_len": max_seq_len} if max_seq_len else {}))
+        self.cfg = model.config_struct(kv_mode=kv_mode, **({"max_seq_len": max_seq_len} if max_seq_len else {}))
         self.h = self.L.tenzo_create_engine(C.byref(self.cfg))
         assert self.h
         self._keep = []
@@ -62,12 +62,15 @@ class RefEngine:
 class OracleEngine:
     """The C restatement's engine loaded with a SyntheticModel."""
 
-    def __init__(self, model: synth.SyntheticModel, max_seq_len: int | None = None, rope_theta: float = 10000.0):
+    def __init__(self, model: synth.SyntheticModel, max_seq_len: int | None = None, rope_theta: float = 10000.0,
+                 kv_mode: str = "int8_fused"):
         self.O = ora.load_oracle()
         c = model.cfg
         self.cfg = ora.OraConfig(c["hidden_size"], c["num_q_heads"], c["num_kv_heads"], c["head_dim"], c["num_layers"],
                                  c["ffn_dim"], c["vocab_size"], max_seq_len or c["max_seq_len"], rope_theta)
         self.e = self.O.ora_engine_create(C.byref(self.cfg))
+        if kv_mode == "paged_int8":
+            self.O.ora_engine_use_paged_kv(self.e)
         self.model = model
         self._keep = []
         for l, lw in enumerate(model.layers):
@@ -105,11 +108,11 @@ class OracleEngine:
         return self.O.ora_engine_seq_len(self.e)
 
 
-def best_cpu_engine(model, max_seq_len=None):
+def best_cpu_engine(model, max_seq_len=None, kv_mode="int8_fused"):
     """The compiled reference when it is present (it is the authority), else the C oracle."""
     if ora.ref_available("kernels"):
-        return RefEngine(model, max_seq_len)
-    return OracleEngine(model, max_seq_len)
+        return RefEngine(model, max_seq_len, kv_mode=kv_mode)
+    return OracleEngine(model, max_seq_len, kv_mode=kv_mode)
 
 
 def greedy_stream(engine, prompt, n_gen):

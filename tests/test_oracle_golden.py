@@ -88,6 +88,45 @@ def test_attention_sequence(golden):
     assert not ck.reshape(L, nkv, ms, hd)[0].any(), "layer 0 of the cache must stay untouched"
 
 
+def paged_attention_inputs(g):
+    L, nq, nkv, hd, blocks, steps, layer = (int(v) for v in g["dims"])
+    rng = np.random.default_rng(15)
+    order = rng.permutation(blocks).astype(np.int32)
+    q = rng.standard_normal((steps, nq * hd)).astype(np.float32)
+    q[::7] *= 4.0
+    k = rng.standard_normal((steps, nkv * hd)).astype(np.float32)
+    v = rng.standard_normal((steps, nkv * hd)).astype(np.float32)
+    assert sha(np.concatenate([q, k, v], axis=1)) == str(g["qkv_sha"]) and np.array_equal(order, g["order"])
+    return (L, nq, nkv, hd, blocks, steps, layer), order, q, k, v
+
+
+def test_paged_attention_sequence(golden):
+    g = golden["attention_paged"]
+    (L, nq, nkv, hd, blocks, steps, layer), order, q, k, v = paged_attention_inputs(g)
+    rows = blocks * L * nkv * 16
+    pk, pv = np.zeros(rows * hd, np.int8), np.zeros(rows * hd, np.int8)
+    psk, psv = np.ones(rows, np.float32), np.ones(rows, np.float32)      # the reference presets scales to 1
+    keep = {int(t): i for i, t in enumerate(g["keep"])}
+    for t in range(steps):
+        qq, kk, vv, o = q[t].copy(), k[t].copy(), v[t].copy(), np.zeros(nq * hd, np.float32)
+        O.ora_attention_paged_int8(layer, t, nq, nkv, hd, L, 10000.0, P(qq, ora.c_f32p), P(kk, ora.c_f32p), P(vv, ora.c_f32p),
+                                   P(o, ora.c_f32p), P(pk, ora.c_i8p), P(pv, ora.c_i8p), P(psk, ora.c_f32p), P(psv, ora.c_f32p),
+                                   P(order, ora.c_i32p))
+        if t in keep:
+            assert np.array_equal(o, g["outs"][keep[t]]), f"paged attention output differs at position {t}"
+    assert np.array_equal(pk.reshape(g["pool_k"].shape), g["pool_k"]) and np.array_equal(pv.reshape(g["pool_v"].shape), g["pool_v"])
+    assert np.array_equal(psk.reshape(g["scale_k"].shape), g["scale_k"]) and np.array_equal(psv.reshape(g["scale_v"].shape), g["scale_v"])
+
+
+def test_paged_engine_tiny_stream(golden):
+    g = golden["engine_paged"]
+    e = OracleEngine(synth.SyntheticModel(synth.TINY, seed=3), kv_mode="paged_int8")
+    assert np.array_equal(greedy_stream(e, g["tiny_prompt"], 32), g["tiny_tokens"])
+    assert np.array_equal(e.buffer("logits", 1024), g["tiny_logits"])
+    assert np.array_equal(e.buffer("attn_out", 256), g["tiny_attn_out"])
+    e.close()
+
+
 def test_lm_head(golden):
     g = golden["lm_head"]
     w, s, x, fn = g["w"], g["s"], g["x"], g["final_norm"]

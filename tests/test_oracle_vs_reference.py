@@ -63,3 +63,56 @@ def test_penalised_greedy_matches():
         past.append(cur_r)
     r.close()
     o.close()
+
+
+def test_paged_attention_bit_exact_with_scattered_blocks():
+    """PagedKVCache::forward_attention_raw against the restatement, blocks placed out of order."""
+    O, R = ora.load_oracle(), ora.load_ref("kernels")
+    L, nq, nkv, hd, blocks, layer = 2, 8, 2, 128, 12, 1
+    rng = np.random.default_rng(41)
+    order = rng.permutation(blocks).astype(np.int32)
+    kv = R.refk_paged_create(L, nq, nkv, hd, blocks)
+    rows = blocks * L * nkv * 16
+    pk, pv = np.zeros(rows * hd, np.int8), np.zeros(rows * hd, np.int8)
+    psk, psv = np.ones(rows, np.float32), np.ones(rows, np.float32)
+    steps = 70
+    for t in range(steps):
+        if t % 16 == 0:
+            R.refk_paged_push_block(kv, int(order[t // 16]))
+        q = (rng.standard_normal(nq * hd) * (4.0 if t % 7 == 0 else 1.0)).astype(np.float32)   # peaked rows: weights under 1e-7
+        k = rng.standard_normal(nkv * hd).astype(np.float32)
+        v = rng.standard_normal(nkv * hd).astype(np.float32)
+        o1, o2 = np.zeros(nq * hd, np.float32), np.zeros(nq * hd, np.float32)
+        q1, k1, v1 = q.copy(), k.copy(), v.copy()
+        R.refk_paged_set_len(kv, t)
+        R.refk_paged_attention(kv, layer, P(q1, ora.c_f32p), P(k1, ora.c_f32p), P(v1, ora.c_f32p), P(o1, ora.c_f32p))
+        q2, k2, v2 = q.copy(), k.copy(), v.copy()
+        O.ora_attention_paged_int8(layer, t, nq, nkv, hd, L, 10000.0, P(q2, ora.c_f32p), P(k2, ora.c_f32p), P(v2, ora.c_f32p),
+                                   P(o2, ora.c_f32p), P(pk, ora.c_i8p), P(pv, ora.c_i8p), P(psk, ora.c_f32p), P(psv, ora.c_f32p),
+                                   P(order, ora.c_i32p))
+        assert np.array_equal(o1, o2), t
+        assert np.array_equal(q1, q2) and np.array_equal(k1, k2)
+    assert np.array_equal(ora.view(R.refk_paged_k(kv), rows * hd, np.int8), pk)
+    assert np.array_equal(ora.view(R.refk_paged_v(kv), rows * hd, np.int8), pv)
+    assert np.array_equal(ora.view(R.refk_paged_k_scales(kv), rows, np.float32), psk)
+    assert np.array_equal(ora.view(R.refk_paged_v_scales(kv), rows, np.float32), psv)
+    R.refk_paged_destroy(kv)
+
+
+def test_paged_engine_stream_matches_and_differs_from_fused():
+    cfg = dict(synth.TINY, max_seq_len=96)
+    m = synth.SyntheticModel(cfg, seed=9)
+    r, o = RefEngine(m, kv_mode="paged_int8"), OracleEngine(m, kv_mode="paged_int8")
+    prompt = synth.prompt_tokens(9, 20, cfg["vocab_size"])
+    assert np.array_equal(greedy_stream(r, prompt, 40), greedy_stream(o, prompt, 40))
+    for name, n in dict(x=cfg["hidden_size"], attn_out=cfg["hidden_size"], logits=cfg["vocab_size"]).items():
+        assert np.array_equal(r.buffer(name, n), o.buffer(name, n)), name
+    assert r.seq_len() == o.seq_len() == 19 + 40
+    tab = np.zeros(16, np.int32)
+    n = ora.load_ref("kernels").refk_paged_table(ora.load_ref("kernels").refk_engine_paged_kv(r.h), P(tab, ora.c_i32p), 16)
+    assert n == 4 and list(tab[:4]) == [0, 1, 2, 3]          # the reference's allocator hands out 0, 1, 2, ...
+    f = OracleEngine(m)                                       # the two KV modes are different arithmetic: ulps apart
+    greedy_stream(f, prompt, 40)
+    assert not np.array_equal(f.buffer("attn_out", cfg["hidden_size"]), o.buffer("attn_out", cfg["hidden_size"]))
+    for e in (r, o, f):
+        e.close()
