@@ -119,6 +119,16 @@ typedef struct {
                               (two keys per lane; for many (sequence, kv head) items; returns -5 if it does not fit:
                               needs four 16 KB tile rings beside the weights, n_q/n_kv <= 4 heads per CTA, cache_k and
                               seq_stride_kv 16-byte aligned); 2 = force per-lane global loads */
+    /* kv_mode "paged_int8" (PagedKVCache of the reference, TenzoEngine.cpp:220-445, TenzoEngine.h:154-193). A non-NULL
+     * block_table selects it: cache_k/cache_v are then the block pools int8 [block][n_layers][kv_head][16][128] and
+     * scale_k/scale_v fp32 [block][n_layers][kv_head][16]; token t of sequence s lives in block
+     * block_table[s*table_stride + t/16], slot t%16 (the entry for pos[s]/16 must exist before the call); seq_stride_*
+     * are ignored. The arithmetic is that of PagedKVCache::forward_attention_raw, which is not the contiguous cache's
+     * (two sets of eight FMA lanes, (dot*s_k)*scale, 1/(sum+1e-8), weights under 1e-7 dropped); outputs are
+     * bit-identical to it. */
+    const int* block_table; /* device */
+    int table_stride;       /* ints between the tables of consecutive sequences; 0 = all query rows share one table */
+    int n_layers;
 } tenzo_attention_args;
 
 TENZO_API int tenzo_cuda_attention_int8(const tenzo_attention_args* args, void* stream);

@@ -21,7 +21,10 @@
 //
 // Two instantiations: per-lane global loads of the key rows (few items, lowest latency: single-sequence
 // decode) and K tiles brought in by TMA with the 128-byte swizzle, two keys per lane (64 or more
-// (sequence, kv head) items). What bounds both long phases is the shared-memory return path, not HBM
+// (sequence, kv head) items). A third one follows the reference's other int8 cache, kv_mode "paged_int8"
+// (PagedKVCache::forward_attention_raw, :242-445): 16-token blocks behind a block table, and its own arithmetic
+// (two sets of eight FMA lanes, (dot * s_k) * scale, 1 / (sum + 1e-8), weights under 1e-7 dropped), again bit for bit.
+// What bounds both long phases is the shared-memory return path, not HBM
 // or arithmetic: the query vector is re-read (broadcast LDS.128) for every key or key pair while
 // scoring, and every value warp re-reads the weights of its keys.
 #include <cuda.h>
@@ -225,7 +228,10 @@ __device__ __forceinline__ void exp_in_place(float* e, int T, int tp, const floa
 //                per-warp rings with the 128-byte swizzle. Direct per-lane loads of 128-byte rows cost 32 data-pipe
 //                wavefronts per instruction, and the query vector is then re-read once per key; a tile costs four
 //                wavefronts per 16-byte column and each query load serves two keys. Same arithmetic, same bits.
-template <int GH, bool TILED>
+// PAGED (with TILED = false): the caches are the reference's block pools [block][n_layers][kv_head][16][128] (scales
+//                [..][16]) and key t of a sequence lives in block block_table[t / 16], slot t % 16; the arithmetic is that of
+//                PagedKVCache::forward_attention_raw, which differs from the contiguous cache's in four places (marked below).
+template <int GH, bool TILED, bool PAGED>
 __global__ void __launch_bounds__(TILED ? kTileThreads : kAttnThreads) attn_kernel(const AttnLaunch L, const __grid_constant__ CUtensorMap kmap) {
     constexpr int NT = TILED ? kTileThreads : kAttnThreads;
     const tenzo_attention_args& a = L.a;
@@ -254,11 +260,17 @@ __global__ void __launch_bounds__(TILED ? kTileThreads : kAttnThreads) attn_kern
     const int T = pos + 1;
     const int n_chunks = (T + kChunk - 1) / kChunk;
 
-    const size_t row_base = ((size_t)a.layer * a.n_kv + kvh) * a.max_seq;   // :509-510
-    int8_t* ck = a.cache_k + (size_t)seq * a.seq_stride_kv + row_base * kHd;
-    int8_t* cv = a.cache_v + (size_t)seq * a.seq_stride_kv + row_base * kHd;
-    float* sk = a.scale_k + (size_t)seq * a.seq_stride_sc + row_base;
-    float* sv = a.scale_v + (size_t)seq * a.seq_stride_sc + row_base;
+    const size_t row_base = PAGED ? 0 : ((size_t)a.layer * a.n_kv + kvh) * a.max_seq;   // :509-510
+    int8_t* ck = a.cache_k + (PAGED ? (size_t)0 : (size_t)seq * a.seq_stride_kv + row_base * kHd);
+    int8_t* cv = a.cache_v + (PAGED ? (size_t)0 : (size_t)seq * a.seq_stride_kv + row_base * kHd);
+    float* sk = a.scale_k + (PAGED ? (size_t)0 : (size_t)seq * a.seq_stride_sc + row_base);
+    float* sv = a.scale_v + (PAGED ? (size_t)0 : (size_t)seq * a.seq_stride_sc + row_base);
+    // row of key t relative to ck / cv / sk / sv: t itself in the contiguous cache, (block, layer, kv head, slot) in the pools (:322-323)
+    const int* tbl = PAGED ? a.block_table + (size_t)seq * a.table_stride : nullptr;
+    auto rowi = [&](int t) -> size_t {
+        if constexpr (PAGED) return (((size_t)__ldg(tbl + (t >> 4)) * a.n_layers + a.layer) * a.n_kv + kvh) * 16 + (size_t)(t & 15);
+        else return (size_t)t;
+    };
     const float* cs = a.rope_cos ? a.rope_cos + (size_t)pos * (kHd / 2) : nullptr;
     const float* sn = a.rope_sin ? a.rope_sin + (size_t)pos * (kHd / 2) : nullptr;
 
@@ -267,16 +279,14 @@ __global__ void __launch_bounds__(TILED ? kTileThreads : kAttnThreads) attn_kern
     uint4 pre_row[8];
     float pre_ks = 0.0f, pre_vs = 0.0f;
     bool pre_ok = false, pre_vs_ok = false;
-    if constexpr (!TILED) {
+    if constexpr (!TILED && !PAGED) {
         if (tid < T && !(a.append && tid == pos)) {
 #pragma unroll
-            for (int c = 0; c < 8; ++c) pre_row[c] = ld_cg_u4(reinterpret_cast<const uint4*>(ck + (size_t)tid * kHd) + c);
-            pre_ks = __ldcg(sk + tid);
-            pre_ok = true;
-        }
-        if (tid < T && !(a.append && tid == pos)) {      // first element of the weights pass: head 0, key tid
-            pre_vs = __ldcg(sv + tid);
-            pre_vs_ok = true;
+            const size_t r = rowi(tid);
+            for (int c = 0; c < 8; ++c) pre_row[c] = ld_cg_u4(reinterpret_cast<const uint4*>(ck + r * kHd) + c);
+            pre_ks = __ldcg(sk + r);
+            pre_vs = __ldcg(sv + r);                     // first element of the weights pass: head 0, key tid
+            pre_ok = pre_vs_ok = true;
         }
     }
 
@@ -285,7 +295,14 @@ __global__ void __launch_bounds__(TILED ? kTileThreads : kAttnThreads) attn_kern
     auto issue_v = [&](int c) {
         const int t0 = c * kChunk, nk = min(kChunk, T - t0);
         mbar_expect_tx(&s_bar[c & 1], (unsigned)nk * kHd);
-        bulk_g2s(s_v + (size_t)(c & 1) * kChunk * kHd, cv + (size_t)t0 * kHd, (unsigned)nk * kHd, &s_bar[c & 1]);
+        if constexpr (PAGED) {                 // a chunk is eight blocks of 16 rows, each contiguous in the pool
+            for (int t = t0; t < t0 + nk; t += 16) {
+                const int n = min(16, t0 + nk - t);
+                bulk_g2s(s_v + (size_t)(c & 1) * kChunk * kHd + (size_t)(t - t0) * kHd, cv + rowi(t) * kHd, (unsigned)n * kHd, &s_bar[c & 1]);
+            }
+        } else {
+            bulk_g2s(s_v + (size_t)(c & 1) * kChunk * kHd, cv + (size_t)t0 * kHd, (unsigned)nk * kHd, &s_bar[c & 1]);
+        }
     };
     if (tid == 0) {
         mbar_init(&s_bar[0], 1);
@@ -341,9 +358,10 @@ __global__ void __launch_bounds__(TILED ? kTileThreads : kAttnThreads) attn_kern
             reinterpret_cast<uint32_t*>(s_new8 + warp * kHd)[lane] = packed;
             if (lane == 0) s_stat[2 * GH + warp] = s;
             if (stores_new_row) {
-                int8_t* dst = (warp == 0 ? ck : cv) + (size_t)pos * kHd;
+                const size_t r = rowi(pos);
+                int8_t* dst = (warp == 0 ? ck : cv) + r * kHd;
                 reinterpret_cast<uint32_t*>(dst)[lane] = packed;
-                if (lane == 0) (warp == 0 ? sk : sv)[pos] = s;
+                if (lane == 0) (warp == 0 ? sk : sv)[r] = s;
             }
         }
     }
@@ -436,10 +454,47 @@ __global__ void __launch_bounds__(TILED ? kTileThreads : kAttnThreads) attn_kern
                 }
             }
         }
+    } else if constexpr (PAGED) {
+        // One key per thread through the block table. Where the arithmetic departs from the contiguous cache's:
+        // difference 1 (:371-386): sixteen accumulators - element e of every 16 has its own chain - then lane j =
+        //   acc[j] + acc[j + 8], and the eight lanes are added left to right starting from 0.0f;
+        // difference 2 (:388): score = (dot * s_k) * (1/sqrt(d)).
+        // One head at a time, so that sixteen accumulators are live, not 16 x GH.
+        for (int t = tid; t < T; t += NT) {
+            const bool is_new = a.append && t == pos;
+            const size_t r = is_new ? 0 : rowi(t);
+            const uint4* src = is_new ? reinterpret_cast<const uint4*>(s_new8) : reinterpret_cast<const uint4*>(ck + r * kHd);
+            uint4 cur[8];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) cur[c] = is_new ? src[c] : ld_cg_u4(src + c);
+            const float ksc = is_new ? s_stat[2 * GH] : __ldcg(sk + r);
+#pragma unroll 1
+            for (int g = 0; g < GH; ++g) {             // not unrolled: the byte-to-float conversions are redone per head instead of kept live
+                float acc[16];
+#pragma unroll
+                for (int e = 0; e < 16; ++e) acc[e] = 0.0f;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const uint32_t w[4] = {cur[c].x ^ 0x80808080u, cur[c].y ^ 0x80808080u, cur[c].z ^ 0x80808080u, cur[c].w ^ 0x80808080u};
+                    const float4* q4 = reinterpret_cast<const float4*>(s_q + g * kHd + c * 16);
+                    const float4 qa = q4[0], qb = q4[1], qc = q4[2], qd = q4[3];
+                    const float qv[16] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w,
+                                          qc.x, qc.y, qc.z, qc.w, qd.x, qd.y, qd.z, qd.w};
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) acc[e] = __fmaf_rn(qv[e], s8_to_f(w[e >> 2], e & 3), acc[e]);
+                }
+                float dot = 0.0f;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) dot = __fadd_rn(dot, __fadd_rn(acc[j], acc[j + 8]));
+                const float score = __fmul_rn(__fmul_rn(dot, ksc), sm_scale);
+                s_sc[(size_t)g * tp + t] = score;
+                tmax[g] = fmaxf(tmax[g], score);
+            }
+        }
     } else {
         auto load_row = [&](int t, uint4 (&r)[8]) {
             const bool is_new = a.append && t == pos;
-            const uint4* src = is_new ? reinterpret_cast<const uint4*>(s_new8) : reinterpret_cast<const uint4*>(ck + (size_t)t * kHd);
+            const uint4* src = is_new ? reinterpret_cast<const uint4*>(s_new8) : reinterpret_cast<const uint4*>(ck + rowi(t) * kHd);
     #pragma unroll
             for (int c = 0; c < 8; ++c) r[c] = is_new ? src[c] : ld_cg_u4(src + c);
         };
@@ -455,34 +510,36 @@ __global__ void __launch_bounds__(TILED ? kTileThreads : kAttnThreads) attn_kern
         for (int t = tid; t < T; t += NT) {
             const bool more = t + NT < T;
             if (more) load_row(t + NT, nxt);
-            float acc[GH][8];
+            const float ksc = (a.append && t == pos) ? s_stat[2 * GH] : ((pre_ok && t == tid) ? pre_ks : __ldcg(sk + rowi(t)));
+            {
+                float acc[GH][8];
     #pragma unroll
-            for (int g = 0; g < GH; ++g)
+                for (int g = 0; g < GH; ++g)
     #pragma unroll
-                for (int j = 0; j < 8; ++j) acc[g][j] = 0.0f;
+                    for (int j = 0; j < 8; ++j) acc[g][j] = 0.0f;
     #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                const uint32_t w[4] = {cur[c].x ^ 0x80808080u, cur[c].y ^ 0x80808080u, cur[c].z ^ 0x80808080u, cur[c].w ^ 0x80808080u};
-                float kf[16];
+                for (int c = 0; c < 8; ++c) {
+                    const uint32_t w[4] = {cur[c].x ^ 0x80808080u, cur[c].y ^ 0x80808080u, cur[c].z ^ 0x80808080u, cur[c].w ^ 0x80808080u};
+                    float kf[16];
     #pragma unroll
-                for (int e = 0; e < 16; ++e) kf[e] = s8_to_f(w[e >> 2], e & 3);
+                    for (int e = 0; e < 16; ++e) kf[e] = s8_to_f(w[e >> 2], e & 3);
+    #pragma unroll
+                    for (int g = 0; g < GH; ++g) {
+                        const float4* q4 = reinterpret_cast<const float4*>(s_q + g * kHd + c * 16);
+                        const float4 qa = q4[0], qb = q4[1], qc = q4[2], qd = q4[3];
+                        const float qv[16] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w,
+                                              qc.x, qc.y, qc.z, qc.w, qd.x, qd.y, qd.z, qd.w};
+    #pragma unroll
+                        for (int e = 0; e < 16; ++e) acc[g][e & 7] = __fmaf_rn(qv[e], kf[e], acc[g][e & 7]);
+                    }
+                }
+                const float ks = ksc * sm_scale;
     #pragma unroll
                 for (int g = 0; g < GH; ++g) {
-                    const float4* q4 = reinterpret_cast<const float4*>(s_q + g * kHd + c * 16);
-                    const float4 qa = q4[0], qb = q4[1], qc = q4[2], qd = q4[3];
-                    const float qv[16] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w,
-                                          qc.x, qc.y, qc.z, qc.w, qd.x, qd.y, qd.z, qd.w};
-    #pragma unroll
-                    for (int e = 0; e < 16; ++e) acc[g][e & 7] = __fmaf_rn(qv[e], kf[e], acc[g][e & 7]);
+                    const float dot = (acc[g][0] + acc[g][1] + acc[g][2] + acc[g][3] + acc[g][4] + acc[g][5] + acc[g][6] + acc[g][7]) * ks;   // :691
+                    s_sc[(size_t)g * tp + t] = dot;
+                    tmax[g] = fmaxf(tmax[g], dot);
                 }
-            }
-            const float ksc = (a.append && t == pos) ? s_stat[2 * GH] : ((pre_ok && t == tid) ? pre_ks : __ldcg(sk + t));
-            const float ks = ksc * sm_scale;
-    #pragma unroll
-            for (int g = 0; g < GH; ++g) {
-                const float dot = (acc[g][0] + acc[g][1] + acc[g][2] + acc[g][3] + acc[g][4] + acc[g][5] + acc[g][6] + acc[g][7]) * ks;   // :691
-                s_sc[(size_t)g * tp + t] = dot;
-                tmax[g] = fmaxf(tmax[g], dot);
             }
             if (more) {
     #pragma unroll
@@ -513,7 +570,10 @@ __global__ void __launch_bounds__(TILED ? kTileThreads : kAttnThreads) attn_kern
     __syncthreads();
     TZ_PH(2);
     // ---- sum_t e_t, left to right, one thread per head (:824-829) ----------------------------------
-    if (tid < GH) s_stat[GH + tid] = 1.0f / sequential_sum(s_sc + (size_t)tid * tp, T);
+    if (tid < GH) {
+        const float sum = sequential_sum(s_sc + (size_t)tid * tp, T);
+        s_stat[GH + tid] = PAGED ? 1.0f / __fadd_rn(sum, 1e-8f) : 1.0f / sum;       // difference 3 (:400)
+    }
     __syncthreads();
     TZ_PH(3);
     // ---- weights p_t * s_v[t] (:830, :844) ------------------------------------------------------------
@@ -522,8 +582,10 @@ __global__ void __launch_bounds__(TILED ? kTileThreads : kAttnThreads) attn_kern
         float* row = s_sc + (size_t)g * tp;
         const float inv_sum = s_stat[GH + g];
         for (int t = tid; t < T; t += NT) {
-            const float vs = (a.append && t == pos) ? s_stat[2 * GH + 1] : ((pre_vs_ok && t == tid) ? pre_vs : __ldcg(sv + t));
-            row[t] = (row[t] * inv_sum) * vs;
+            const float vs = (a.append && t == pos) ? s_stat[2 * GH + 1] : ((pre_vs_ok && t == tid) ? pre_vs : __ldcg(sv + rowi(t)));
+            const float p = row[t] * inv_sum;
+            // difference 4 (:416): keys whose weight is under 1e-7 are skipped; a zero weight leaves every sum as it was
+            row[t] = (PAGED && p < 1e-7f) ? 0.0f : p * vs;
         }
     }
     __syncthreads();
@@ -579,14 +641,14 @@ static int make_k_tensor_map(const tenzo_attention_args& a, CUtensorMap* out) {
     return r == CUDA_SUCCESS ? 0 : -4;
 }
 
-template <int GH, bool TILED>
+template <int GH, bool TILED, bool PAGED = false>
 static int launch_attn(const AttnLaunch& L, cudaStream_t st) {
     CUtensorMap kmap;
     std::memset(&kmap, 0, sizeof kmap);
     if (TILED)
         if (int rc = make_k_tensor_map(L.a, &kmap)) return rc;
     const size_t smem = TILED ? AttnSmem<GH>::bytes_tiled(L.a.max_len, L.n_tile_warps) : AttnSmem<GH>::bytes(L.a.max_len);
-    cudaError_t e = cudaFuncSetAttribute(attn_kernel<GH, TILED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attn_kernel<GH, TILED, PAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(L.a.n_q / GH), (unsigned)L.a.batch, 1);
@@ -598,7 +660,7 @@ static int launch_attn(const AttnLaunch& L, cudaStream_t st) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = L.a.use_pdl ? 1 : 0;
-    e = cudaLaunchKernelEx(&cfg, attn_kernel<GH, TILED>, L, kmap);
+    e = cudaLaunchKernelEx(&cfg, attn_kernel<GH, TILED, PAGED>, L, kmap);
     return e == cudaSuccess ? 0 : (int)e;
 }
 
@@ -645,6 +707,7 @@ extern "C" int tenzo_cuda_attention_int8(const tenzo_attention_args* args, void*
     if (!a.q || !a.out || !a.cache_k || !a.cache_v || !a.scale_k || !a.scale_v || !a.pos) return -1;
     if (a.append && (!a.k || !a.v)) return -1;
     if (a.head_dim != kHd) return -5;
+    if (a.block_table && (a.n_layers <= 0 || a.layer < 0 || a.layer >= a.n_layers || a.table_stride < 0 || a.tiles == 1)) return a.tiles == 1 ? -5 : -1;
     if (a.n_q <= 0 || a.n_kv <= 0 || a.n_q % a.n_kv || a.batch <= 0 || a.max_len <= 0 || a.max_len > a.max_seq) return -1;
     if ((a.rope_cos == nullptr) != (a.rope_sin == nullptr)) return -1;
     const int group = a.n_q / a.n_kv;
@@ -658,6 +721,15 @@ extern "C" int tenzo_cuda_attention_int8(const tenzo_attention_args* args, void*
     L.gh = pick_heads_per_cta(a.batch, a.n_q, group, a.max_len);
     if (a.heads_per_cta == 1 || a.heads_per_cta == 2 || a.heads_per_cta == 4 || a.heads_per_cta == 8)
         if (a.heads_per_cta <= group && (size_t)a.heads_per_cta * a.max_len * sizeof(float) <= (size_t)kScoreSmemBytes) L.gh = a.heads_per_cta;
+    if (a.block_table) {                     // block pools: per-lane loads through the block table
+        L.n_tile_warps = 0;
+        switch (L.gh) {
+            case 1: return launch_attn<1, false, true>(L, st);
+            case 2: return launch_attn<2, false, true>(L, st);
+            case 4: return launch_attn<4, false, true>(L, st);
+            default: return launch_attn<8, false, true>(L, st);
+        }
+    }
     // Many (sequence, kv head) items: K through TMA tiles, two keys per lane. Few items (single-sequence decode): direct loads.
     int tw = 0;
     switch (L.gh) {

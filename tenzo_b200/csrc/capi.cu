@@ -91,8 +91,8 @@ tenzo_engine_t tenzo_ext_create_engine(const tenzo_config_t* config, const tenzo
     guarded([&]() -> tenzo_status_t {
         tenzo_config_t c = config ? *config : tenzo_default_config();
         tenzo_ext_options_t o = opt ? *opt : tenzo_ext_default_options();
-        if (c.kv_mode && std::strcmp(c.kv_mode, "int8_fused") != 0)
-            throw std::invalid_argument(std::string("kv_mode '") + c.kv_mode + "' is not implemented; only int8_fused");
+        if (c.kv_mode && std::strcmp(c.kv_mode, "int8_fused") != 0 && std::strcmp(c.kv_mode, "paged_int8") != 0)
+            throw std::invalid_argument(std::string("kv_mode '") + c.kv_mode + "' is not implemented; only int8_fused and paged_int8");
         int n_dev = 0;
         if (cudaGetDeviceCount(&n_dev) != cudaSuccess || n_dev == 0)
             throw std::runtime_error("no CUDA device is visible; this library has no CPU path");
@@ -113,7 +113,11 @@ void tenzo_destroy_engine(tenzo_engine_t engine) {
 
 void tenzo_reset(tenzo_engine_t engine) {
     if (!live(engine)) return;
-    for (auto& n : engine->impl->seq_len) n = 0;   // TenzoEngine.cpp:213-215
+    try {
+        engine->impl->reset_kv();                  // TenzoEngine.cpp:213-215, :242-246
+    } catch (const std::exception& ex) {
+        tz::set_error(ex.what());
+    }
 }
 
 int tenzo_get_seq_len(tenzo_engine_t engine) { return live(engine) ? engine->impl->seq_len[0] : 0; }
@@ -231,24 +235,32 @@ static tenzo_status_t kv_copy(tenzo_engine_t engine, int seq, int layer, void* k
         if (seq < 0 || seq >= e.batch || layer < 0 || layer >= e.L || len < 0 || len > e.cfg.max_seq_len)
             throw std::out_of_range("sequence, layer or length out of range");
         cudaStreamSynchronize(e.stream);
-        const int nkv = e.cfg.num_kv_heads, ms = e.cfg.max_seq_len;
-        for (int hh = 0; hh < nkv && len > 0; ++hh) {
-            const size_t row = (size_t)seq * e.kv_rows_per_seq + ((size_t)layer * nkv + hh) * ms;
-            const size_t hb = (size_t)hh * len;
-            cudaError_t c0, c1, c2, c3;
-            if (to_device) {
-                c0 = cudaMemcpy(e.cache_k + row * 128, (const int8_t*)k + hb * 128, (size_t)len * 128, cudaMemcpyHostToDevice);
-                c1 = cudaMemcpy(e.cache_v + row * 128, (const int8_t*)v + hb * 128, (size_t)len * 128, cudaMemcpyHostToDevice);
-                c2 = cudaMemcpy(e.scale_k + row, (const float*)sk + hb, (size_t)len * 4, cudaMemcpyHostToDevice);
-                c3 = cudaMemcpy(e.scale_v + row, (const float*)sv + hb, (size_t)len * 4, cudaMemcpyHostToDevice);
-            } else {
-                c0 = cudaMemcpy((int8_t*)k + hb * 128, e.cache_k + row * 128, (size_t)len * 128, cudaMemcpyDeviceToHost);
-                c1 = cudaMemcpy((int8_t*)v + hb * 128, e.cache_v + row * 128, (size_t)len * 128, cudaMemcpyDeviceToHost);
-                c2 = cudaMemcpy((float*)sk + hb, e.scale_k + row, (size_t)len * 4, cudaMemcpyDeviceToHost);
-                c3 = cudaMemcpy((float*)sv + hb, e.scale_v + row, (size_t)len * 4, cudaMemcpyDeviceToHost);
+        const int nkv = e.cfg.num_kv_heads;
+        if (e.paged) {
+            if (to_device) e.reserve_blocks(seq, len);            // an import brings its own blocks
+            else if (e.n_blocks[seq] * tz::Engine::kBlock < len) throw std::out_of_range("the sequence holds fewer tokens than asked for");
+        }
+        const int run = e.paged ? tz::Engine::kBlock : (len > 0 ? len : 1);   // tokens that are contiguous in the cache
+        for (int hh = 0; hh < nkv; ++hh) {
+            for (int t0 = 0; t0 < len; t0 += run) {
+                const size_t n = (size_t)(len - t0 < run ? len - t0 : run);
+                const size_t row = e.kv_row(seq, layer, hh, t0);
+                const size_t hb = (size_t)hh * len + t0;
+                cudaError_t c0, c1, c2, c3;
+                if (to_device) {
+                    c0 = cudaMemcpy(e.cache_k + row * 128, (const int8_t*)k + hb * 128, n * 128, cudaMemcpyHostToDevice);
+                    c1 = cudaMemcpy(e.cache_v + row * 128, (const int8_t*)v + hb * 128, n * 128, cudaMemcpyHostToDevice);
+                    c2 = cudaMemcpy(e.scale_k + row, (const float*)sk + hb, n * 4, cudaMemcpyHostToDevice);
+                    c3 = cudaMemcpy(e.scale_v + row, (const float*)sv + hb, n * 4, cudaMemcpyHostToDevice);
+                } else {
+                    c0 = cudaMemcpy((int8_t*)k + hb * 128, e.cache_k + row * 128, n * 128, cudaMemcpyDeviceToHost);
+                    c1 = cudaMemcpy((int8_t*)v + hb * 128, e.cache_v + row * 128, n * 128, cudaMemcpyDeviceToHost);
+                    c2 = cudaMemcpy((float*)sk + hb, e.scale_k + row, n * 4, cudaMemcpyDeviceToHost);
+                    c3 = cudaMemcpy((float*)sv + hb, e.scale_v + row, n * 4, cudaMemcpyDeviceToHost);
+                }
+                if (c0 != cudaSuccess || c1 != cudaSuccess || c2 != cudaSuccess || c3 != cudaSuccess)
+                    throw std::runtime_error("KV copy failed");
             }
-            if (c0 != cudaSuccess || c1 != cudaSuccess || c2 != cudaSuccess || c3 != cudaSuccess)
-                throw std::runtime_error("KV copy failed");
         }
         return TENZO_SUCCESS;
     });
@@ -278,8 +290,12 @@ tenzo_status_t tenzo_ext_set_seq_len(tenzo_engine_t engine, int seq, int len) {
     if (!live(engine)) return TENZO_ERROR_INVALID_ARGUMENT;
     tz::Engine& e = *engine->impl;
     if (seq < 0 || seq >= e.batch || len < 0 || len > e.cfg.max_seq_len) return TENZO_ERROR_INVALID_ARGUMENT;
-    e.seq_len[seq] = len;
-    return TENZO_SUCCESS;
+    return guarded([&]() -> tenzo_status_t {
+        e.release_blocks(seq, len);                // block pools: the table follows the length
+        e.reserve_blocks(seq, len);
+        e.seq_len[seq] = len;
+        return TENZO_SUCCESS;
+    });
 }
 
 int tenzo_ext_get_seq_len(tenzo_engine_t engine, int seq) {
@@ -333,6 +349,7 @@ tenzo_status_t tenzo_ext_run_layer(tenzo_engine_t engine, int layer) {
             longest = e.seq_len[s] + 1 > longest ? e.seq_len[s] + 1 : longest;
         }
         e.push_state(nullptr);
+        e.prepare_kv(1);
         e.enqueue_layer(layer, longest);
         if (cudaStreamSynchronize(e.stream) != cudaSuccess) throw std::runtime_error("layer execution failed");
         return TENZO_SUCCESS;

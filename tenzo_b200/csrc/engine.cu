@@ -74,9 +74,12 @@ __global__ void record_tokens_kernel(const int* next, int* history, int step, in
 // Chunked prefill: rotate and quantise the K rows, quantise the V rows of M consecutive tokens of one sequence and
 // append them at positions pos0.. (the same arithmetic as the attention kernel's own append, TenzoEngine.cpp:459-533).
 // One warp per (token, kv head, K|V); lane l holds elements 4l..4l+3.
+// With a block table (kv_mode "paged_int8") the row goes to block table[pos / 16], slot pos % 16 of the pools
+// [block][n_layers][kv_head][16][128] (TenzoEngine.cpp:322-323).
 __global__ void __launch_bounds__(64) kv_append_rows_kernel(const float* qkv, int row_stride, int q_dim, int kv_dim, int n_kv, int pos0,
                                                             const float* rope_cos, const float* rope_sin, int8_t* cache_k, int8_t* cache_v,
-                                                            float* scale_k, float* scale_v, size_t layer_row_base, int max_seq) {
+                                                            float* scale_k, float* scale_v, size_t layer_row_base, int max_seq,
+                                                            const int* table, int n_layers, int layer) {
     const int token = blockIdx.x, kvh = blockIdx.y, is_v = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int pos = pos0 + token;
     const float* src = qkv + (size_t)token * row_stride + q_dim + (is_v ? kv_dim : 0) + kvh * 128;
@@ -106,7 +109,8 @@ __global__ void __launch_bounds__(64) kv_append_rows_kernel(const float* qkv, in
         const float qf = fminf(fmaxf(roundf(x[j] * inv), -128.0f), 127.0f);   // :530
         packed |= ((uint32_t)(uint8_t)(int8_t)(int)qf) << (8 * j);
     }
-    const size_t row = layer_row_base + (size_t)kvh * max_seq + pos;
+    const size_t row = table ? (((size_t)table[pos >> 4] * n_layers + layer) * n_kv + kvh) * 16 + (size_t)(pos & 15)
+                             : layer_row_base + (size_t)kvh * max_seq + pos;
     reinterpret_cast<uint32_t*>((is_v ? cache_v : cache_k) + row * 128)[lane] = packed;
     if (lane == 0) (is_v ? scale_v : scale_k)[row] = sc;
 }
@@ -144,7 +148,8 @@ Engine::Engine(const tenzo_config_t& c, const tenzo_ext_options_t& o) : cfg(c) {
     rope_theta = o.rope_theta > 0.0f ? o.rope_theta : 10000.0f;   // TenzoEngine.cpp:456
     use_graph = o.use_graph >= 0 ? o.use_graph : env_flag("TENZO_CUDA_GRAPH", 1);
     use_pdl = o.use_pdl >= 0 ? o.use_pdl : env_flag("TENZO_CUDA_PDL", 1);
-    cfg.kv_mode = "int8_fused";
+    paged = c.kv_mode && std::strcmp(c.kv_mode, "paged_int8") == 0;       // TenzoEngine.cpp:1220
+    cfg.kv_mode = paged ? "paged_int8" : "int8_fused";
     cfg.device = "cuda";
     h = cfg.hidden_size;
     qd = cfg.num_q_heads * cfg.head_dim;
@@ -186,6 +191,17 @@ Engine::Engine(const tenzo_config_t& c, const tenzo_ext_options_t& o) : cfg(c) {
     b_logits = (float*)dalloc(B * V * 4);
 
     kv_rows_per_seq = (size_t)L * cfg.num_kv_heads * cfg.max_seq_len;
+    if (paged) {
+        // (max_seq_len + 15) / 16 blocks per sequence as the reference sizes its pool (:1218), for every sequence
+        table_stride = (cfg.max_seq_len + kBlock - 1) / kBlock;
+        total_blocks = batch * table_stride;
+        kv_rows_per_seq = (size_t)table_stride * L * cfg.num_kv_heads * kBlock;
+        d_table = (int*)dalloc(B * table_stride * 4);
+        TZ_CUDA(cudaMallocHost(&h_table, B * table_stride * sizeof(int)));
+        std::memset(h_table, 0, B * table_stride * sizeof(int));
+        n_blocks.assign(batch, 0);
+        for (int i = total_blocks - 1; i >= 0; --i) free_blocks.push_back(i);     // TenzoEngine.h:128-134
+    }
     cache_k = (int8_t*)dalloc(B * kv_rows_per_seq * 128);
     cache_v = (int8_t*)dalloc(B * kv_rows_per_seq * 128);
     scale_k = (float*)dalloc(B * kv_rows_per_seq * 4);
@@ -220,6 +236,7 @@ Engine::~Engine() {
     for (auto& kv : graphs) cudaGraphExecDestroy(kv.second);
     for (void* p : owned) cudaFree(p);
     if (h_pin) cudaFreeHost(h_pin);
+    if (h_table) cudaFreeHost(h_table);
     if (h_cand) cudaFreeHost(h_cand);
     for (void* p : {(void*)pf_x, (void*)pf_qkv, (void*)pf_attn, (void*)pf_h1, (void*)pf_act, (void*)pf_tokens, (void*)pf_pos, pf_ws})
         if (p) cudaFree(p);
@@ -228,6 +245,56 @@ Engine::~Engine() {
     cudaEventDestroy(ev0);
     cudaEventDestroy(ev1);
     cudaStreamDestroy(stream);
+}
+
+void Engine::reserve_blocks(int s, int len) {
+    if (!paged) return;
+    while (n_blocks[s] * kBlock < len) {
+        if (free_blocks.empty()) throw std::out_of_range("the KV block pool is exhausted");   // the reference would reuse block 0 (:302)
+        h_table[(size_t)s * table_stride + n_blocks[s]] = free_blocks.back();   // TenzoEngine.h:136-141
+        free_blocks.pop_back();
+        n_blocks[s] += 1;
+        table_dirty = true;
+    }
+}
+
+void Engine::release_blocks(int s, int len) {
+    if (!paged) return;
+    const int keep = (len + kBlock - 1) / kBlock;
+    if (n_blocks[s] <= keep) return;
+    TZ_CUDA(cudaStreamSynchronize(stream));               // no step in flight may still read the entries given back
+    while (n_blocks[s] > keep) {
+        n_blocks[s] -= 1;
+        free_blocks.push_back(h_table[(size_t)s * table_stride + n_blocks[s]]);   // TenzoEngine.h:143-147
+    }
+}
+
+// Entries are only ever added between two synchronising calls (reset_kv, release_blocks), so a copy still queued
+// behind earlier steps may carry newer entries without harm: those steps do not read them.
+void Engine::prepare_kv(int extra) {
+    if (!paged) return;
+    for (int s = 0; s < batch; ++s) reserve_blocks(s, seq_len[s] + extra);
+    if (table_dirty) {
+        TZ_CUDA(cudaMemcpyAsync(d_table, h_table, (size_t)batch * table_stride * sizeof(int), cudaMemcpyHostToDevice, stream));
+        table_dirty = false;
+    }
+}
+
+void Engine::reset_kv() {                                  // TenzoEngine.cpp:242-246
+    for (auto& n : seq_len) n = 0;
+    if (!paged) return;
+    TZ_CUDA(cudaStreamSynchronize(stream));
+    free_blocks.clear();
+    for (int i = total_blocks - 1; i >= 0; --i) free_blocks.push_back(i);
+    n_blocks.assign(batch, 0);
+}
+
+size_t Engine::kv_row(int s, int layer, int kvh, int t) const {
+    if (paged) {
+        const size_t blk = (size_t)h_table[(size_t)s * table_stride + t / kBlock];
+        return ((blk * L + layer) * cfg.num_kv_heads + kvh) * kBlock + (size_t)(t % kBlock);
+    }
+    return (size_t)s * kv_rows_per_seq + ((size_t)layer * cfg.num_kv_heads + kvh) * cfg.max_seq_len + t;
 }
 
 void* Engine::upload(const void* host, size_t bytes) {
@@ -332,6 +399,7 @@ void Engine::enqueue_layer(int l, int max_len, bool gemv_only) {
     a.max_seq = cfg.max_seq_len; a.batch = batch; a.max_len = max_len; a.append = 1;
     a.use_pdl = use_pdl;
     a.q_stride = a.kv_stride = qd + 2 * kvd;
+    if (paged) { a.block_table = d_table; a.table_stride = table_stride; a.n_layers = L; }
     if (!gemv_only) {
         TZ_KERNEL(tenzo_cuda_attention_int8(&a, stream));
         launches += 1;
@@ -410,6 +478,7 @@ void Engine::prefill_chunk(const int* tokens, int M) {
         TZ_CUDA(cudaMalloc(&pf_ws, tenzo_cuda_tl1_gemv_workspace_bytes(M > 1 ? M : 2, h > ffn ? h : ffn)));
     }
     const int pos0 = seq_len[0];
+    prepare_kv(M);
     std::vector<int> hp(M);
     for (int i = 0; i < M; ++i) hp[i] = pos0 + i;
     TZ_CUDA(cudaMemcpyAsync(pf_tokens, tokens, (size_t)M * 4, cudaMemcpyHostToDevice, stream));
@@ -434,7 +503,7 @@ void Engine::prefill_chunk(const int* tokens, int M) {
         const size_t layer_row_base = (size_t)l * cfg.num_kv_heads * cfg.max_seq_len;
         kv_append_rows_kernel<<<dim3((unsigned)M, (unsigned)cfg.num_kv_heads), 64, 0, stream>>>(
             pf_qkv, qd + 2 * kvd, qd, kvd, cfg.num_kv_heads, pos0, rope_cos, rope_sin, cache_k, cache_v, scale_k, scale_v, layer_row_base,
-            cfg.max_seq_len);
+            cfg.max_seq_len, paged ? d_table : nullptr, L, l);
         TZ_CUDA(cudaGetLastError());
         tenzo_attention_args a;
         std::memset(&a, 0, sizeof a);
@@ -444,6 +513,7 @@ void Engine::prefill_chunk(const int* tokens, int M) {
         a.pos = pf_pos; a.rope_cos = rope_cos; a.rope_sin = rope_sin;
         a.layer = l; a.n_q = cfg.num_q_heads; a.n_kv = cfg.num_kv_heads; a.head_dim = 128;
         a.max_seq = cfg.max_seq_len; a.batch = M; a.max_len = max_len; a.append = 0; a.tiles = 2;
+        if (paged) { a.block_table = d_table; a.table_stride = 0; a.n_layers = L; }      // every query row reads sequence 0's table
         TZ_KERNEL(tenzo_cuda_attention_int8(&a, stream));
         g.x = pf_attn; g.x_stride = qd; g.norm_w = d.attn_sub_norm; g.w = d.o; g.K = h;
         g.n_blocks = h / 64; g.seg_end[0] = g.seg_end[1] = g.seg_end[2] = g.n_blocks; g.seg_scale[0] = d.s_o;
@@ -487,6 +557,7 @@ void Engine::run_step(bool with_logits, bool feed_back) {
         longest = seq_len[s] + 1 > longest ? seq_len[s] + 1 : longest;
     }
     const int max_len = bucket_for(longest, cfg.max_seq_len);
+    prepare_kv(1);
     if (!use_graph) {
         enqueue_step(with_logits, feed_back, max_len);
     } else {
@@ -582,10 +653,15 @@ void Engine::decode_greedy(const int* first, int n_steps, int* out) {
 
 void Engine::kv_fill(int len, unsigned long long seed) {
     const size_t rows = (size_t)batch * kv_rows_per_seq;
-    kv_fill_kernel<<<148 * 16, 256, 0, stream>>>(cache_k, cache_v, scale_k, scale_v, rows, cfg.max_seq_len, len, seed);
+    // block pools: every row of every block is filled, then each sequence is given the blocks that hold `len` tokens
+    kv_fill_kernel<<<148 * 16, 256, 0, stream>>>(cache_k, cache_v, scale_k, scale_v, rows, paged ? 1 : cfg.max_seq_len, paged ? 1 : len, seed);
     TZ_CUDA(cudaGetLastError());
     TZ_CUDA(cudaStreamSynchronize(stream));
-    for (auto& n : seq_len) n = len;
+    for (int s = 0; s < batch; ++s) {
+        release_blocks(s, len);
+        reserve_blocks(s, len);
+        seq_len[s] = len;
+    }
 }
 
 float Engine::bench_gemv_stack(int iters, unsigned long long* n_launches) {

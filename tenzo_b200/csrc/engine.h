@@ -68,6 +68,22 @@ public:
     unsigned status_poll = 0;
     void kv_fill(int len, unsigned long long seed);
 
+    // kv_mode "paged_int8" (PagedKVCache + PagedBlockManager of the reference, TenzoEngine.h:117-193): the caches are pools
+    // of 16-token blocks [block][layer][kv_head][16][128]; every sequence has a row of the block table. Blocks are taken
+    // from the free list on the host before the step that first writes into them (the reference does it inside layer 0,
+    // TenzoEngine.cpp:294-300) and the table row is copied to the device ahead of the launch.
+    static constexpr int kBlock = 16;
+    bool paged = false;
+    int total_blocks = 0, table_stride = 0;
+    int *d_table = nullptr, *h_table = nullptr;          // [batch][table_stride]; h_table is the pinned master copy
+    std::vector<int> free_blocks, n_blocks;              // free list (taken from the back: 0, 1, 2, ... as the reference's)
+    bool table_dirty = false;
+    void reserve_blocks(int seq, int len);               // the table of `seq` covers tokens [0, len)
+    void release_blocks(int seq, int len);               // blocks past token len go back to the free list
+    void prepare_kv(int extra);                          // before a step that appends `extra` tokens to every sequence
+    void reset_kv();
+    size_t kv_row(int seq, int layer, int kvh, int t) const;   // row of a cached token in cache_k/v (x128) and scale_k/v
+
     tenzo_config_t cfg;
     int batch = 1, device = 0, use_graph = 1, use_pdl = 1;
     float rope_theta = 10000.0f;

@@ -84,9 +84,12 @@ def rmsnorm_quant(x: torch.Tensor, norm_w=None, *, do_norm=True, eps=1e-5, qmax=
 
 
 def attention_int8(q, k, v, cache_k, cache_v, scale_k, scale_v, pos, *, layer, n_q, n_kv, max_seq, rope_cos=None,
-                   rope_sin=None, append=True, max_len=None, use_pdl=False, heads_per_cta=0, out=None, tiles=0):
+                   rope_sin=None, append=True, max_len=None, use_pdl=False, heads_per_cta=0, out=None, tiles=0,
+                   block_table=None, n_layers=0):
     """q [batch, n_q*128], k/v [batch, n_kv*128]; caches [batch, layers, n_kv, max_seq, 128] int8 and
-    [batch, layers, n_kv, max_seq] fp32; pos int32 [batch]. Returns out [batch, n_q*128]."""
+    [batch, layers, n_kv, max_seq] fp32; pos int32 [batch]. Returns out [batch, n_q*128].
+    With block_table (int32 [batch, blocks per sequence]) the caches are the paged_int8 pools
+    [blocks, n_layers, n_kv, 16, 128] / [blocks, n_layers, n_kv, 16] and the arithmetic is the paged cache's."""
     lib = load_library()
     batch = q.shape[0]
     if max_len is None:
@@ -102,6 +105,9 @@ def attention_int8(q, k, v, cache_k, cache_v, scale_k, scale_v, pos, *, layer, n
     a.layer, a.n_q, a.n_kv, a.head_dim, a.max_seq = layer, n_q, n_kv, 128, max_seq
     a.batch, a.max_len, a.append, a.use_pdl, a.heads_per_cta = batch, max_len, int(append), int(use_pdl), heads_per_cta
     a.tiles = tiles
+    if block_table is not None:
+        assert block_table.dtype == torch.int32 and block_table.is_contiguous()
+        a.block_table, a.table_stride, a.n_layers = _ptr(block_table), (block_table.stride(0) if block_table.dim() == 2 else 0), n_layers
     _ok(lib.tenzo_cuda_attention_int8(C.byref(a), _stream()), "tenzo_cuda_attention_int8")
     return out
 

@@ -14,8 +14,9 @@ FP_TOL = 1e-3
 
 def gpu_engine(model, **kw):
     from tenzo_b200.engine import Engine
-    return Engine(model.config_struct(**{k: v for k, v in kw.items() if k == "max_seq_len"}),
-                  **{k: v for k, v in kw.items() if k != "max_seq_len"}).load_synthetic(model)
+    cfg_keys = ("max_seq_len", "kv_mode")
+    return Engine(model.config_struct(**{k: v for k, v in kw.items() if k in cfg_keys}),
+                  **{k: v for k, v in kw.items() if k not in cfg_keys}).load_synthetic(model)
 
 
 class GpuAsCpuApi:
