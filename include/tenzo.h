@@ -6,9 +6,9 @@
  * (or its C++ wrapper include/tenzo.hpp) links against libtenzo_runtime.so from this repository
  * unchanged. tests/test_abi.py checks sizes and field offsets against the reference layout.
  *
- * Differences in behaviour, all on the strict side (see INTEGRATION.md):
+ * Differences in behaviour, all on the strict side:
  *   - the engine always runs on the CUDA device; `device` in the config is accepted and ignored;
- *   - only kv_mode "int8_fused" (or NULL) is implemented, other modes fail engine creation;
+ *   - kv_mode "int8_fused" (or NULL) and "paged_int8" are implemented, other modes fail engine creation;
  *   - setters copy to device memory at once, so callers may free their buffers afterwards;
  *   - out-of-range layer indices, token ids and a full KV cache are reported instead of ignored.
  */
@@ -56,7 +56,7 @@ typedef struct { /* reference tenzo.h:53-64; defaults are BitNet-b1.58-2B-4T */
     int ffn_dim;         /* 6912   */
     int vocab_size;      /* 128256 */
     int max_seq_len;     /* 8192   */
-    const char* kv_mode; /* "int8_fused" or NULL */
+    const char* kv_mode; /* "int8_fused" (or NULL) or "paged_int8" */
     const char* device;  /* ignored: always the current CUDA device */
 } tenzo_config_t;
 
