@@ -212,7 +212,7 @@ def run_decode_b1(args):
     cfg = dict(synth.BITNET_2B, max_seq_len=512)
     model = synth.SyntheticModel(cfg, seed=SEED)
     prompt = synth.prompt_tokens(SEED, PROMPT_LEN, cfg["vocab_size"])
-    eng = Engine(model.config_struct()).load_synthetic(model)
+    eng = Engine(model.config_struct(kv_mode=args.kv_mode)).load_synthetic(model)
     greedy = abi.TenzoSampling(0.0, 0.9, 40, 1.0)
 
     def prefill():
@@ -287,7 +287,8 @@ def run_decode_b1(args):
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
             "config": {"workload": "decode_b1: BitNet-2B-shaped greedy decode (30L, 2560/6912, 20q/5kv, INT8 LM head 128256x2560, INT8 KV), "
                                    "64-token prompt, one sequence per GPU", "l2": "inputs larger than L2 (852 MB of weights per step)",
-                       "parallelism": "replicas only" if world > 1 else "single GPU", "bytes_per_token": model.weight_bytes_per_token()},
+                       "parallelism": "replicas only" if world > 1 else "single GPU", "bytes_per_token": model.weight_bytes_per_token(),
+                       "kv_mode": args.kv_mode},
             "e2e": {"value": total / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 4,
                     "same_tokens_as_device_loop": same_stream},
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roof, "cpu_baseline": cpu,
@@ -313,6 +314,9 @@ def main():
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--pdl", type=int, default=1)
     ap.add_argument("--heads-per-cta", type=int, default=0)
+    ap.add_argument("--gemm-rows", type=int, default=13824, help="gemm workload: output rows of the TL1 matrix (multiple of 128)")
+    ap.add_argument("--gemm-k", type=int, default=2560, help="gemm workload: K of the TL1 matrix (multiple of 128)")
+    ap.add_argument("--kv-mode", default="int8_fused", choices=["int8_fused", "paged_int8"], help="decode workloads: KV cache mode")
     ap.add_argument("--no-prefetch", action="store_true", help="gemv/gemm workloads: do not ask L2 for the next matrix (for DRAM-traffic captures)")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -91,7 +91,8 @@ def _peak_tensor():
 def run_gemm(args):
     import torch
     from . import kernels
-    N, K, n_mat = 13824, 2560, 16
+    N, K = args.gemm_rows, args.gemm_k
+    n_mat = max(16, min(128, (160 << 20) // (N * K // 4) + 1))     # distinct matrices per step: more bytes than L2 holds
     B = args.batch
     ws = [_random_tl1_device(N * K // 4, 200 + i) for i in range(n_mat)]
     x = torch.randn(B, K, device="cuda", generator=torch.Generator(device="cuda").manual_seed(3))
@@ -181,7 +182,7 @@ def run_decode_batch(args):
     ctx = args.context
     cfg = dict(synth.BITNET_2B, max_seq_len=ctx + args.steps + max(3, args.warmup) + 8)
     model = synth.SyntheticModel(cfg, seed=0)
-    eng = Engine(model.config_struct(), batch=B).load_synthetic(model)
+    eng = Engine(model.config_struct(kv_mode=args.kv_mode), batch=B).load_synthetic(model)
     eng.kv_fill_random(ctx, seed=rank)
     first = synth.prompt_tokens(1000 + rank, B, cfg["vocab_size"])
     warm = eng.decode_greedy(first, max(3, args.warmup))
@@ -202,7 +203,7 @@ def run_decode_batch(args):
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
             "config": {"workload": f"decode_batch: BitNet-2B shape, global batch {args.batch}, context {ctx} (device-filled KV), "
-                                   f"{B} sequences per GPU", "parallelism": f"dp{world}"},
+                                   f"{B} sequences per GPU", "parallelism": f"dp{world}", "kv_mode": args.kv_mode},
             "gpu_launches": int(launches),
         }), flush=True)
     eng.close()

@@ -21,10 +21,22 @@
 //                       barrier, which is what lets the producer refill the stage.
 // After the last chunk a final commit signals the epilogue (warps 2-5: one TMEM lane = one weight
 // row per thread, tcgen05.ld 16 sequences at a time, scale / residual / ReLU^2*GLU, coalesced stores).
+// Few row tiles (the out, down and q|k|v projections have 20 to 30) would leave most SMs idle, so K is then split
+// across the 2, 4 or 8 CTAs of a thread-block cluster: each accumulates its share of the chunks in its own tensor
+// memory and parks its int32 partial tile in shared memory; after a hardware cluster barrier every CTA takes the
+// 16-sequence column blocks b = rank, rank + ksplit, ..., adds its peers' partials for them through distributed
+// shared memory (integer sums: order-free, exact), runs the epilogue on them and stores them (a reduce-scatter:
+// the epilogue work is spread over the cluster instead of queueing on one leader).
 // Every mbarrier wait is bounded; a wait that gives up sets g_umma_timeouts, the roles fall through
 // to the end and the TMEM allocation is released on every path.
+#include <cooperative_groups.h>
+
+#include <cstdlib>
+
 #include "umma.cuh"
 #include "../../include/tenzo_kernels.h"
+
+namespace cg = cooperative_groups;
 
 namespace tz {
 
@@ -46,6 +58,7 @@ struct UmmaLaunch {
     int n_box;               // sequences per CTA, padded to a multiple of 16 (<= 256)
     int tmem_cols;           // power of two >= max(32, n_box)
     int n_stages;            // A/B tile stages
+    int ksplit;              // CTAs of a cluster that share one tile's K range (1 = no cluster)
 };
 
 __device__ int g_umma_timeouts = 0;
@@ -66,7 +79,8 @@ struct UmmaSmem {
 };
 
 __global__ void __launch_bounds__(kUmmaThreads, 1) tl1_umma_kernel(const UmmaLaunch L, const __grid_constant__ CUtensorMap amap,
-                                                                   const __grid_constant__ CUtensorMap omap) {
+                                                                   const __grid_constant__ CUtensorMap omap,
+                                                                   const __grid_constant__ CUtensorMap omap16) {
     const tenzo_tl1_gemv_args& a = L.a;
     extern __shared__ unsigned char smem_raw[];
     const uint32_t base_off = ((smem_addr(smem_raw) + 1023u) & ~1023u) - smem_addr(smem_raw);
@@ -90,7 +104,11 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) tl1_umma_kernel(const UmmaLau
     const int tile = blockIdx.x, seq0 = blockIdx.y * kMaxN;
     const int blk0 = glu ? tile : 2 * tile;
     const int blk1 = glu ? tile + L.units : (2 * tile + 1 < a.n_blocks ? 2 * tile + 1 : -1);
-    const int n_chunks = a.K / kKc;
+    const int ksplit = L.ksplit;
+    const int split = ksplit > 1 ? (int)cg::this_cluster().block_rank() : 0;      // cluster = the CTAs with this tile's blockIdx.z = 0..ksplit-1
+    const int all_chunks = a.K / kKc;
+    const int c_begin = split * all_chunks / ksplit;                                // this CTA's chunks of K: never empty (all_chunks >= ksplit)
+    const int n_chunks = (split + 1) * all_chunks / ksplit - c_begin;
     const int N = L.n_box;
 
     if (tid == 0) {
@@ -119,7 +137,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) tl1_umma_kernel(const UmmaLau
         pdl_wait();
         pdl_launch_dependents();
     }
-    bool timed_out = false;
+    bool timed_out = false, epi_ok = false;
     for (int i = tid; i < N; i += kUmmaThreads) {              // per-sequence epilogue operands (read after the final barrier)
         const int seq = seq0 + i;
         s_inv[i] = seq < a.batch ? __ldcg(L.inv + seq) : 0.0f;
@@ -144,14 +162,15 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) tl1_umma_kernel(const UmmaLau
                     const unsigned bytes = (unsigned)chunks * (kPBytes / 2);
                     unsigned char* sP = pring + (size_t)slot * kPGroup * kPBytes;
                     mbar_expect_tx(&bar_p[slot], blk1 >= 0 ? 2 * bytes : bytes);
-                    bulk_g2s(sP, a.w + (size_t)blk0 * blk_bytes + (size_t)gp * kPGroup * (kPBytes / 2), bytes, &bar_p[slot]);
-                    if (blk1 >= 0) bulk_g2s(sP + kPGroup * (kPBytes / 2), a.w + (size_t)blk1 * blk_bytes + (size_t)gp * kPGroup * (kPBytes / 2), bytes, &bar_p[slot]);
+                    const size_t k_off = (size_t)(c_begin + gp * kPGroup) * (kPBytes / 2);
+                    bulk_g2s(sP, a.w + (size_t)blk0 * blk_bytes + k_off, bytes, &bar_p[slot]);
+                    if (blk1 >= 0) bulk_g2s(sP + kPGroup * (kPBytes / 2), a.w + (size_t)blk1 * blk_bytes + k_off, bytes, &bar_p[slot]);
                 }
                 if (timed_out) break;
                 const int s = j % S, use = j / S;
                 if (use > 0 && !mbar_spin_bounded(&bar_empty[s], (unsigned)(use - 1) & 1u)) { timed_out = true; break; }
                 mbar_expect_tx(&bar_raw[s], (unsigned)(N * kKc));
-                tma_load_2d(stages + (size_t)s * stage_bytes + kABytes, &amap, j * kKc, seq0, &bar_raw[s]);
+                tma_load_2d(stages + (size_t)s * stage_bytes + kABytes, &amap, (c_begin + j) * kKc, seq0, &bar_raw[s]);
             }
         }
     } else if (warp == 1) {
@@ -227,24 +246,57 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) tl1_umma_kernel(const UmmaLau
             if (lane == 0) mbar_arrive(&bar_ready[s]);
         }
         if (grp == 0) {
-
-        // ---- epilogue: TMEM lane = weight row -------------------------------------------------------
-        bool ok = true;
-        if (lane == 0) ok = !timed_out && mbar_spin_bounded(bar_accum, 0u);
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) timed_out = true;
-        tc_fence_after();
+            // ---- all of this CTA's MMAs have completed; a cluster peer parks its partial tile [N][128] int32 in the
+            //      stage memory the pipeline no longer needs ------------------------------------------------------------
+            bool ok = true;
+            if (lane == 0) ok = !timed_out && mbar_spin_bounded(bar_accum, 0u);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) timed_out = true;
+            tc_fence_after();
+            epi_ok = ok;
+            if (ksplit > 1) {
+                const int q = warp & 3, row = 32 * q + lane;
+                int* s_part = reinterpret_cast<int*>(stages);
+                for (int c0 = 0; c0 < N; c0 += 16) {
+                    if ((c0 >> 4) % ksplit == split) continue;       // this CTA's own column blocks stay in tensor memory
+                    uint32_t r[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) r[i] = 0u;
+                    if (ok) tmem_ld16(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)c0, r);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) s_part[(c0 + i) * 128 + row] = (int)r[i];
+                }
+            }
+        }
+    }
+    if (ksplit > 1) cg::this_cluster().sync();               // every CTA's partial tile is in place
+    if (warp >= 2 && warp < 6) {
+        // ---- epilogue: TMEM lane = weight row; column blocks split, split + ksplit, ... (all of them without a cluster) ----
+        const bool ok = epi_ok;
         const int q = warp & 3;                              // this warp may touch TMEM lanes 32q..32q+31
         const int row = 32 * q + lane, rblk = row >> 6, rr = row & 63;
         const int block = rblk ? blk1 : blk0;
         const float wscale = block >= 0 ? umma_seg_scale(a, block) : 0.0f;
-        // Output tile [N sequences][128 rows] (GLU: [N][64]) is assembled in the stage memory the
-        // pipeline no longer needs, one row per thread, and leaves through one TMA store: rows of
+        const int* peer[8];
+#pragma unroll
+        for (int p = 0; p < 8; ++p)
+            peer[p] = (ksplit > 1 && p < ksplit && p != split) ? cg::this_cluster().map_shared_rank(reinterpret_cast<int*>(stages), p) : nullptr;
+        // The output columns [sequences][128 rows] (GLU: [..][64]) are assembled in shared memory the pipeline no
+        // longer needs - the stage memory, or with a cluster the packed-weight ring, because the stage memory then
+        // holds the partial tile the peers are reading - one row per thread, and leave through TMA stores: rows of
         // 512 (256) contiguous bytes per sequence, clipped at the matrix edge by the tensor map.
-        float* s_out = reinterpret_cast<float*>(stages);
-        for (int c0 = 0; c0 < N; c0 += 16) {
+        float* s_out = reinterpret_cast<float*>(ksplit > 1 ? pring : stages);
+        int o0 = 0;                                          // column slot in s_out of the block being processed
+        for (int c0 = 16 * split; c0 < N; c0 += 16 * ksplit, o0 += 16) {
             uint32_t r[16];
             if (ok) tmem_ld16(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)c0, r);
+#pragma unroll
+            for (int p = 0; p < 8; ++p) {
+                if (peer[p]) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) r[i] += (uint32_t)peer[p][(c0 + i) * 128 + row];
+                }
+            }
             int sums[16];
             float invs[16], res[16];
 #pragma unroll
@@ -283,26 +335,36 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) tl1_umma_kernel(const UmmaLau
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
                         const float rl = fmaxf(0.0f, v[i]);
-                        s_out[(c0 + i) * 64 + rr] = (rl * rl) * s_glu[i * 64 + rr];   // :1618-1619
+                        s_out[(o0 + i) * 64 + rr] = (rl * rl) * s_glu[i * 64 + rr];   // :1618-1619
                     }
                 }
                 named_barrier_sync(1, 128);
             } else {
 #pragma unroll
                 for (int i = 0; i < 16; ++i)
-                    s_out[(c0 + i) * 128 + row] = a.epilogue == TENZO_EPI_RESIDUAL ? res[i] + v[i] : v[i];   // :1590
+                    s_out[(o0 + i) * 128 + row] = a.epilogue == TENZO_EPI_RESIDUAL ? res[i] + v[i] : v[i];   // :1590
             }
         }
         fence_proxy_async_smem();
         named_barrier_sync(1, 128);
         if (tid == 64 && ok) {
-            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
-                         ::"l"(&omap), "r"((glu ? tile : blk0) * 64), "r"(seq0), "r"(smem_addr(s_out)) : "memory");
+            if (ksplit == 1) {
+                asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                             ::"l"(&omap), "r"((glu ? tile : blk0) * 64), "r"(seq0), "r"(smem_addr(s_out)) : "memory");
+            } else {                                         // one 16-sequence box per column block of this CTA
+                const int row_floats = glu ? 64 : 128;
+                int slot = 0;
+                for (int c0 = 16 * split; c0 < N; c0 += 16 * ksplit, slot += 16) {
+                    if (seq0 + c0 >= a.batch) break;         // nothing but padding from here on
+                    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                                 ::"l"(&omap16), "r"((glu ? tile : blk0) * 64), "r"(seq0 + c0), "r"(smem_addr(s_out + slot * row_floats)) : "memory");
+                }
+            }
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");     // the tile has left shared memory
         }
-        }
     }
+    if (ksplit > 1) cg::this_cluster().sync();               // every peer has read this CTA's partial tile: it may exit
     if (timed_out) atomicExch(&g_umma_timeouts, 1);
     tc_fence_before();
     __syncthreads();
@@ -314,6 +376,23 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) tl1_umma_kernel(const UmmaLau
 
 bool tl1_umma_applicable(const tenzo_tl1_gemv_args& a) {
     return a.batch >= 16 && a.K % kKc == 0 && a.K >= kKc && a.out_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(a.out) & 15) == 0;
+}
+
+// CTAs of a cluster that split one tile's K range: doubled while the grid still fits the SMs (one CTA per SM) and
+// every CTA keeps at least four 128-byte chunks. TENZO_UMMA_KSPLIT = 1, 2, 4 or 8 overrides the choice (measurement aid).
+static int pick_umma_ksplit(int ctas, int n_chunks) {
+    static int n_sm = 0, forced = -1;
+    if (forced < 0) {
+        const char* e = std::getenv("TENZO_UMMA_KSPLIT");
+        const int v = e ? std::atoi(e) : 0;
+        forced = (v == 1 || v == 2 || v == 4 || v == 8) ? v : 0;
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
+    }
+    if (forced) return forced <= n_chunks ? forced : 1;
+    int k = 1;
+    while (k < 8 && ctas * k * 2 <= n_sm && n_chunks / (k * 2) >= 4) k *= 2;
+    return k;
 }
 
 // a8 [batch][K] int8 (16-byte aligned), inv [batch], sum_a [batch] already produced on `st`.
@@ -329,7 +408,9 @@ int launch_tl1_umma(const tenzo_tl1_gemv_args& a, const int8_t* a8, const float*
     L.tmem_cols = 32;
     while (L.tmem_cols < L.n_box) L.tmem_cols *= 2;
     L.n_stages = UmmaSmem::stages_for(L.n_box);
-    CUtensorMap amap, omap;
+    const int seq_tiles = (a.batch + kMaxN - 1) / kMaxN;
+    L.ksplit = pick_umma_ksplit(L.units * seq_tiles, a.K / kKc);
+    CUtensorMap amap, omap, omap16;
     // activations [batch][K] int8: B-operand tiles {128 bytes of K, n_box sequences}, 128-byte swizzle
     if (int rc = encode_2d(&amap, CU_TENSOR_MAP_DATA_TYPE_UINT8, a8, (uint64_t)a.K, (uint64_t)a.batch, (uint64_t)a.K, kKc, (uint32_t)L.n_box,
                            CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
@@ -337,20 +418,34 @@ int launch_tl1_umma(const tenzo_tl1_gemv_args& a, const int8_t* a8, const float*
     const uint64_t n_out = (uint64_t)(glu ? a.n_blocks / 2 : a.n_blocks) * 64;
     if (int rc = encode_2d(&omap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a.out, n_out, (uint64_t)a.batch, (uint64_t)a.out_stride * 4, glu ? 64u : 128u,
                            (uint32_t)L.n_box, CU_TENSOR_MAP_SWIZZLE_NONE)) return rc;
+    // the same matrix in boxes of 16 sequences, for the column blocks a cluster's CTAs store separately
+    if (int rc = encode_2d(&omap16, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a.out, n_out, (uint64_t)a.batch, (uint64_t)a.out_stride * 4, glu ? 64u : 128u,
+                           16u, CU_TENSOR_MAP_SWIZZLE_NONE)) return rc;
     const size_t smem = UmmaSmem::bytes(L.n_box);
     cudaError_t e = cudaFuncSetAttribute(tl1_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)L.units, (unsigned)((a.batch + kMaxN - 1) / kMaxN), 1);
+    cfg.gridDim = dim3((unsigned)L.units, (unsigned)seq_tiles, (unsigned)L.ksplit);
     cfg.blockDim = dim3(kUmmaThreads, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int n_attr = 0;
+    if (L.ksplit > 1) {
+        attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+        attr[n_attr].val.clusterDim.x = 1;
+        attr[n_attr].val.clusterDim.y = 1;
+        attr[n_attr].val.clusterDim.z = (unsigned)L.ksplit;
+        ++n_attr;
+    }
+    if (a.use_pdl) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        ++n_attr;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = a.use_pdl ? 1 : 0;
-    e = cudaLaunchKernelEx(&cfg, tl1_umma_kernel, L, amap, omap);
+    cfg.numAttrs = n_attr;
+    e = cudaLaunchKernelEx(&cfg, tl1_umma_kernel, L, amap, omap, omap16);
     return e == cudaSuccess ? 0 : (int)e;
 }
 

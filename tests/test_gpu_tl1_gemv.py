@@ -175,18 +175,20 @@ def test_tensor_core_path_bit_exact(cuda_lib, N, K, batch):
         assert np.array_equal(host(r["out"])[b], out), "fp32 outputs differ"
 
 
-def test_tensor_core_path_epilogues_match_single_sequence_path(cuda_lib):
+@pytest.mark.parametrize("h", [512, 2048])
+def test_tensor_core_path_epilogues_match_single_sequence_path(cuda_lib, h):
     """Segment scales + fused norm, residual and ReLU^2*GLU epilogues at 48 sequences against the same
-    launches made one sequence at a time (already pinned to the oracle above)."""
+    launches made one sequence at a time (already pinned to the oracle above). At h = 2048 every one of them
+    splits K across a cluster of four CTAs."""
     from tenzo_b200 import kernels
-    h, f, B = 512, 704, 48
+    f, B = 704, 48
     rng = np.random.default_rng(46)
     x = rng.standard_normal((B, h)).astype(np.float32)
     res = rng.standard_normal((B, h)).astype(np.float32)
     nw = (1 + 0.1 * rng.standard_normal(h)).astype(np.float32)
     wo = dev(synth.random_tl1_packed(rng, h, h))
     wgu = dev(np.concatenate([synth.random_tl1_packed(rng, f, h), synth.random_tl1_packed(rng, f, h)]))
-    wqkv = dev(np.concatenate([synth.random_tl1_packed(rng, n, h) for n in (512, 128, 128)]))
+    wqkv = dev(np.concatenate([synth.random_tl1_packed(rng, n, h) for n in (512, 128, 128)]))   # 12 row blocks
     dx, dres, dnw = dev(x), dev(res), dev(nw)
 
     def launches(xs, rs):
