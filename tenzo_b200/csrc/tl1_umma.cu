@@ -246,8 +246,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) tl1_umma_kernel(const UmmaLau
             if (lane == 0) mbar_arrive(&bar_ready[s]);
         }
         if (grp == 0) {
-            // ---- all of this CTA's MMAs have completed; a cluster peer parks its partial tile [N][128] int32 in the
-            //      stage memory the pipeline no longer needs ------------------------------------------------------------
+            // ---- all of this CTA's MMAs have completed; in a cluster it parks its partial tile [N][128] int32 (the
+            //      column blocks its peers will reduce) in the stage memory the pipeline no longer needs ------------------
             bool ok = true;
             if (lane == 0) ok = !timed_out && mbar_spin_bounded(bar_accum, 0u);
             ok = __shfl_sync(0xffffffffu, ok, 0);
