@@ -73,6 +73,10 @@ typedef struct {
 TENZO_API int tenzo_cuda_tl1_gemv(const tenzo_tl1_gemv_args* args, void* stream);
 /* Cluster size along K (1, 2, 4 or 8 CTAs share one row block) the launcher picks for this shape; informational. */
 TENZO_API int tenzo_cuda_tl1_gemv_ksplit(int n_blocks, int K, int epilogue);
+/* 16 or more sequences (tensor-core path): CTAs of a thread-block cluster that share one 128-row tile's K range
+ * (1, 2, 4 or 8; more than 1 when the row tiles alone would leave most SMs idle); 0 if that path does not take the
+ * shape. Informational. */
+TENZO_API int tenzo_cuda_tl1_gemm_ksplit(int n_blocks, int K, int batch, int epilogue);
 TENZO_API size_t tenzo_cuda_tl1_gemv_workspace_bytes(int batch, int K);
 /* The kernel's waits on asynchronous copies are bounded. Returns 1 (and clears the flag) if any launch
  * since the last call gave up waiting — its output is then invalid; 0 otherwise; -1 if the query failed.

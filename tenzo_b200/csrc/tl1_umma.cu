@@ -458,3 +458,9 @@ int tl1_umma_take_timeouts() {
 }
 
 }  // namespace tz
+
+extern "C" int tenzo_cuda_tl1_gemm_ksplit(int n_blocks, int K, int batch, int epilogue) {
+    if (n_blocks <= 0 || K < tz::kKc || K % tz::kKc || batch < 16) return 0;       // the tensor-core path does not apply
+    const int units = epilogue == TENZO_EPI_RELU2_GLU ? n_blocks / 2 : (n_blocks + 1) / 2;
+    return tz::pick_umma_ksplit(units * ((batch + tz::kMaxN - 1) / tz::kMaxN), K / tz::kKc);
+}

@@ -101,6 +101,9 @@ def test_kernel_entry_points_reject_bad_arguments_without_a_device(lib):
     assert lib.tenzo_cuda_attention_int8(None, None) == abi.ERR_INVALID
     assert lib.tenzo_cuda_lm_head_i8(None, None, 1, 1e-5, None, None, 0, 0, 0, 0, None, None, None, None, 0, None) == abi.ERR_INVALID
     assert lib.tenzo_cuda_tl1_gemv_ksplit(40, 2560, 0) >= 1
+    # tensor-core GEMM, BitNet-2B shapes at 64 sequences: out / down / q|k|v split K over a cluster of four, gate|up (108 tiles) does not
+    assert [lib.tenzo_cuda_tl1_gemm_ksplit(n, k, 64, e) for n, k, e in ((40, 2560, 1), (40, 6912, 1), (60, 2560, 0), (216, 2560, 2))] == [4, 4, 4, 1]
+    assert lib.tenzo_cuda_tl1_gemm_ksplit(2, 16384, 17, 0) == 8 and lib.tenzo_cuda_tl1_gemm_ksplit(40, 2560, 8, 0) == 0
     assert lib.tenzo_cuda_attention_heads_per_cta(1, 20, 5, 256) == 1 and lib.tenzo_cuda_attention_heads_per_cta(64, 20, 5, 8192) == 4
 
 
