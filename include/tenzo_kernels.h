@@ -133,6 +133,8 @@ typedef struct {
     const int* block_table; /* device */
     int table_stride;       /* ints between the tables of consecutive sequences; 0 = all query rows share one table */
     int n_layers;
+    int n_pool_blocks;      /* blocks in the pools; 0 = not given, which rules out the TMA-tile variant (tiles == 1 then
+                               returns -5): its tensor map needs the pool's extent */
 } tenzo_attention_args;
 
 TENZO_API int tenzo_cuda_attention_int8(const tenzo_attention_args* args, void* stream);

@@ -64,7 +64,7 @@ class AttentionArgs(C.Structure):
         ("layer", C.c_int), ("n_q", C.c_int), ("n_kv", C.c_int), ("head_dim", C.c_int), ("max_seq", C.c_int),
         ("batch", C.c_int), ("max_len", C.c_int), ("append", C.c_int),
         ("heads_per_cta", C.c_int), ("use_pdl", C.c_int), ("tiles", C.c_int),
-        ("block_table", C.c_void_p), ("table_stride", C.c_int), ("n_layers", C.c_int),
+        ("block_table", C.c_void_p), ("table_stride", C.c_int), ("n_layers", C.c_int), ("n_pool_blocks", C.c_int),
     ]
 
 

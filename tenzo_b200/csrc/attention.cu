@@ -82,8 +82,10 @@ struct AttnSmem {
     static size_t bytes(int max_len) { return (size_t)sc_off + (size_t)padded(max_len) * GH * sizeof(float); }
     static __host__ __device__ int ring_bytes(int n_warps) { const int r = n_warps * 2 * kTileBytes; return r > 2 * kChunk * kHd ? r : 2 * kChunk * kHd; }
     static size_t bytes_tiled(int max_len, int n_warps) { return (size_t)v_off + 1024 + ring_bytes(n_warps) + (size_t)padded(max_len) * GH * sizeof(float); }
-    static int tile_warps_that_fit(int max_len) {
-        const long long room = 227LL * 1024 - ((long long)v_off + 1024 + (long long)padded(max_len) * GH * 4);
+    // block pools: the sequence's block table is staged behind the scores
+    static __host__ __device__ int table_bytes(int max_len) { return (((max_len + 15) >> 4) * 4 + 15) & ~15; }
+    static int tile_warps_that_fit(int max_len, bool paged = false) {
+        const long long room = 227LL * 1024 - ((long long)v_off + 1024 + (long long)padded(max_len) * GH * 4) - (paged ? table_bytes(max_len) : 0);
         const long long n = room / (2 * kTileBytes);
         return (int)(n > kMaxTileWarps ? kMaxTileWarps : n);
     }
@@ -94,6 +96,13 @@ struct AttnSmem {
 __device__ __forceinline__ void tma_load_k_tile(void* dst, const CUtensorMap* map, int row0, int seq, uint64_t* bar) {
     asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
                  ::"r"(smem_addr(dst)), "l"(map), "r"(0), "r"(row0), "r"(seq), "r"(smem_addr(bar)) : "memory");
+}
+
+// Block pools: the 16 rows x 128 bytes of one (block, layer, kv head) slice, rows row0.. of the pool seen as one long
+// 2-D byte matrix; four of them make a 64-key tile with the same swizzled layout as above.
+__device__ __forceinline__ void tma_load_k_rows(void* dst, const CUtensorMap* map, int row0, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(smem_addr(dst)), "l"(map), "r"(0), "r"(row0), "r"(smem_addr(bar)) : "memory");
 }
 
 __device__ int g_attn_timeouts = 0;   // set when a bounded wait on a V-chunk copy gave up
@@ -266,9 +275,19 @@ __global__ void __launch_bounds__(TILED ? kTileThreads : kAttnThreads) attn_kern
     float* sk = a.scale_k + (PAGED ? (size_t)0 : (size_t)seq * a.seq_stride_sc + row_base);
     float* sv = a.scale_v + (PAGED ? (size_t)0 : (size_t)seq * a.seq_stride_sc + row_base);
     // row of key t relative to ck / cv / sk / sv: t itself in the contiguous cache, (block, layer, kv head, slot) in the pools (:322-323)
+    // The sequence's table entries are staged in shared memory (behind the scores): a lookup per key from global memory
+    // would put an L2 round trip in front of every address. rowi_g reads the table in global memory and serves only the
+    // value copies that leave before the staging is complete.
     const int* tbl = PAGED ? a.block_table + (size_t)seq * a.table_stride : nullptr;
-    auto rowi = [&](int t) -> size_t {
+    int* s_tbl = reinterpret_cast<int*>(s_sc + (size_t)GH * tp);
+    if constexpr (PAGED)
+        for (int i = tid; i <= (pos >> 4); i += NT) s_tbl[i] = __ldg(tbl + i);
+    auto rowi_g = [&](int t) -> size_t {
         if constexpr (PAGED) return (((size_t)__ldg(tbl + (t >> 4)) * a.n_layers + a.layer) * a.n_kv + kvh) * 16 + (size_t)(t & 15);
+        else return (size_t)t;
+    };
+    auto rowi = [&](int t) -> size_t {              // valid after the first block-wide barrier
+        if constexpr (PAGED) return (((size_t)s_tbl[t >> 4] * a.n_layers + a.layer) * a.n_kv + kvh) * 16 + (size_t)(t & 15);
         else return (size_t)t;
     };
     const float* cs = a.rope_cos ? a.rope_cos + (size_t)pos * (kHd / 2) : nullptr;
@@ -292,13 +311,14 @@ __global__ void __launch_bounds__(TILED ? kTileThreads : kAttnThreads) attn_kern
 
     // ---- V chunks travel by bulk copy into a double buffer; the first two leave now and overlap the
     //      whole scoring phase. (Rows are contiguous in the cache, so a chunk is one copy.) -------------
-    auto issue_v = [&](int c) {
+    auto issue_v = [&](int c, bool table_staged) {
         const int t0 = c * kChunk, nk = min(kChunk, T - t0);
         mbar_expect_tx(&s_bar[c & 1], (unsigned)nk * kHd);
         if constexpr (PAGED) {                 // a chunk is eight blocks of 16 rows, each contiguous in the pool
             for (int t = t0; t < t0 + nk; t += 16) {
                 const int n = min(16, t0 + nk - t);
-                bulk_g2s(s_v + (size_t)(c & 1) * kChunk * kHd + (size_t)(t - t0) * kHd, cv + rowi(t) * kHd, (unsigned)n * kHd, &s_bar[c & 1]);
+                const size_t r = table_staged ? rowi(t) : rowi_g(t);
+                bulk_g2s(s_v + (size_t)(c & 1) * kChunk * kHd + (size_t)(t - t0) * kHd, cv + r * kHd, (unsigned)n * kHd, &s_bar[c & 1]);
             }
         } else {
             bulk_g2s(s_v + (size_t)(c & 1) * kChunk * kHd, cv + (size_t)t0 * kHd, (unsigned)nk * kHd, &s_bar[c & 1]);
@@ -311,8 +331,8 @@ __global__ void __launch_bounds__(TILED ? kTileThreads : kAttnThreads) attn_kern
             for (int i = 0; i < 2 * L.n_tile_warps; ++i) mbar_init(&s_kbar[i], 1);
         mbar_init_fence();
         if (!TILED) {                          // TILED: the buffers hold K tiles first; the V chunks leave after scoring
-            issue_v(0);
-            if (n_chunks > 1) issue_v(1);
+            issue_v(0, false);
+            if (n_chunks > 1) issue_v(1, false);
         }
     }
 
@@ -386,8 +406,16 @@ __global__ void __launch_bounds__(TILED ? kTileThreads : kAttnThreads) attn_kern
             unsigned char* ring = s_v + (size_t)warp * 2 * kTileBytes;
             uint64_t* kbar = s_kbar + 2 * warp;
             auto issue_tile = [&](int k) {
-                mbar_expect_tx(&kbar[k & 1], (unsigned)kTileBytes);
-                tma_load_k_tile(ring + (size_t)(k & 1) * kTileBytes, &kmap, (int)row_base + (warp + k * n_sc) * kTileKeys, seq, &kbar[k & 1]);
+                if constexpr (PAGED) {                       // up to four 16-key blocks, each wherever the table says
+                    const int tt0 = (warp + k * n_sc) * kTileKeys;
+                    const int nb = min(kTileKeys / 16, (T - tt0 + 15) >> 4);
+                    mbar_expect_tx(&kbar[k & 1], (unsigned)nb * 16 * kHd);
+                    for (int i = 0; i < nb; ++i)
+                        tma_load_k_rows(ring + (size_t)(k & 1) * kTileBytes + (size_t)i * 16 * kHd, &kmap, (int)rowi(tt0 + 16 * i), &kbar[k & 1]);
+                } else {
+                    mbar_expect_tx(&kbar[k & 1], (unsigned)kTileBytes);
+                    tma_load_k_tile(ring + (size_t)(k & 1) * kTileBytes, &kmap, (int)row_base + (warp + k * n_sc) * kTileKeys, seq, &kbar[k & 1]);
+                }
             };
             if (lane == 0) {
                 if (my_tiles > 0) issue_tile(0);
@@ -403,6 +431,51 @@ __global__ void __launch_bounds__(TILED ? kTileThreads : kAttnThreads) attn_kern
                 const unsigned char* rowA = newA ? reinterpret_cast<const unsigned char*>(s_new8) : tile + lane * kHd;
                 const unsigned char* rowB = newB ? reinterpret_cast<const unsigned char*>(s_new8) : tile + (lane + 32) * kHd;
                 const uint32_t xa = newA ? 0u : (uint32_t)(lane & 7), xb = newB ? 0u : (uint32_t)(lane & 7);
+                if constexpr (PAGED) {
+                    // the paged cache's dot product and score (differences 1 and 2 below), two keys per lane, one head
+                    // at a time: 2 x 16 accumulators live; the maxima are taken from the stored scores afterwards
+                    float ksc2[2];
+#pragma unroll
+                    for (int s2 = 0; s2 < 2; ++s2) {
+                        const int t = s2 ? tB : tA;
+                        ksc2[s2] = t < T ? ((a.append && t == pos) ? s_stat[2 * GH] : __ldcg(sk + rowi(t))) : 0.0f;
+                    }
+#pragma unroll 1
+                    for (int g = 0; g < GH; ++g) {
+                        float acc[2][16];
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) acc[0][e] = acc[1][e] = 0.0f;
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) {
+                            const uint4 ka = *reinterpret_cast<const uint4*>(rowA + (((uint32_t)c ^ xa) << 4));
+                            const uint4 kb = *reinterpret_cast<const uint4*>(rowB + (((uint32_t)c ^ xb) << 4));
+                            const uint32_t wa[4] = {ka.x ^ 0x80808080u, ka.y ^ 0x80808080u, ka.z ^ 0x80808080u, ka.w ^ 0x80808080u};
+                            const uint32_t wb[4] = {kb.x ^ 0x80808080u, kb.y ^ 0x80808080u, kb.z ^ 0x80808080u, kb.w ^ 0x80808080u};
+                            const float4* q4 = reinterpret_cast<const float4*>(s_q + g * kHd + c * 16);
+                            const float4 qa = q4[0], qb = q4[1], qc = q4[2], qd = q4[3];
+                            const float qv[16] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w,
+                                                  qc.x, qc.y, qc.z, qc.w, qd.x, qd.y, qd.z, qd.w};
+#pragma unroll
+                            for (int e = 0; e < 16; ++e) {
+                                acc[0][e] = __fmaf_rn(qv[e], s8_to_f(wa[e >> 2], e & 3), acc[0][e]);
+                                acc[1][e] = __fmaf_rn(qv[e], s8_to_f(wb[e >> 2], e & 3), acc[1][e]);
+                            }
+                        }
+#pragma unroll
+                        for (int s2 = 0; s2 < 2; ++s2) {
+                            const int t = s2 ? tB : tA;
+                            if (t < T) {
+                                float dot = 0.0f;
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) dot = __fadd_rn(dot, __fadd_rn(acc[s2][j], acc[s2][j + 8]));
+                                s_sc[(size_t)g * tp + t] = __fmul_rn(__fmul_rn(dot, ksc2[s2]), sm_scale);
+                            }
+                        }
+                    }
+                    __syncwarp();                             // every lane has read the tile: the stage can be refilled
+                    if (lane == 0 && k + 2 < my_tiles) issue_tile(k + 2);
+                    continue;
+                }
                 float acc[2][GH][8];
 #pragma unroll
                 for (int s2 = 0; s2 < 2; ++s2)
@@ -547,6 +620,12 @@ __global__ void __launch_bounds__(TILED ? kTileThreads : kAttnThreads) attn_kern
             }
         }
     }
+    if constexpr (TILED && PAGED) {               // maxima from the stored scores (the scoring loop keeps no per-head registers)
+        __syncthreads();
+#pragma unroll
+        for (int g = 0; g < GH; ++g)
+            for (int t = tid; t < T; t += NT) tmax[g] = fmaxf(tmax[g], s_sc[(size_t)g * tp + t]);
+    }
 #pragma unroll
     for (int g = 0; g < GH; ++g) {
         const float m = warp_max(tmax[g]);
@@ -563,8 +642,8 @@ __global__ void __launch_bounds__(TILED ? kTileThreads : kAttnThreads) attn_kern
 
     // ---- e_t = expf(score - max), in parallel (:826) -----------------------------------------------
     if (TILED && tid == 0) {                   // scoring is over: the ring region now takes the V chunks
-        issue_v(0);
-        if (n_chunks > 1) issue_v(1);
+        issue_v(0, true);
+        if (n_chunks > 1) issue_v(1, true);
     }
     exp_in_place<GH>(s_sc, T, tp, s_stat, tid, NT);
     __syncthreads();
@@ -577,15 +656,20 @@ __global__ void __launch_bounds__(TILED ? kTileThreads : kAttnThreads) attn_kern
     __syncthreads();
     TZ_PH(3);
     // ---- weights p_t * s_v[t] (:830, :844) ------------------------------------------------------------
+    {
+        float inv_sum[GH];
 #pragma unroll
-    for (int g = 0; g < GH; ++g) {
-        float* row = s_sc + (size_t)g * tp;
-        const float inv_sum = s_stat[GH + g];
-        for (int t = tid; t < T; t += NT) {
+        for (int g = 0; g < GH; ++g) inv_sum[g] = s_stat[GH + g];
+#pragma unroll 4
+        for (int t = tid; t < T; t += NT) {          // one value scale per key serves all the heads
             const float vs = (a.append && t == pos) ? s_stat[2 * GH + 1] : ((pre_vs_ok && t == tid) ? pre_vs : __ldcg(sv + rowi(t)));
-            const float p = row[t] * inv_sum;
-            // difference 4 (:416): keys whose weight is under 1e-7 are skipped; a zero weight leaves every sum as it was
-            row[t] = (PAGED && p < 1e-7f) ? 0.0f : p * vs;
+#pragma unroll
+            for (int g = 0; g < GH; ++g) {
+                float* row = s_sc + (size_t)g * tp;
+                const float p = row[t] * inv_sum[g];
+                // difference 4 (:416): keys whose weight is under 1e-7 are skipped; a zero weight leaves every sum as it was
+                row[t] = (PAGED && p < 1e-7f) ? 0.0f : p * vs;
+            }
         }
     }
     __syncthreads();
@@ -607,7 +691,7 @@ __global__ void __launch_bounds__(TILED ? kTileThreads : kAttnThreads) attn_kern
         }
         if (tid < kHd) value_sum_chunk<GH>(vb + tid, s_sc + t0, tp, nkeys, o);
         __syncthreads();                                         // buffer free again
-        if (tid == 0 && c + 2 < n_chunks) issue_v(c + 2);
+        if (tid == 0 && c + 2 < n_chunks) issue_v(c + 2, true);
     }
     if (timed_out) atomicExch(&g_attn_timeouts, 1);
     if (tid < kHd) {
@@ -618,7 +702,8 @@ __global__ void __launch_bounds__(TILED ? kTileThreads : kAttnThreads) attn_kern
 }
 
 // The K cache as a 3-D byte tensor {128, rows per sequence, sequences} for the scoring warps' tile loads.
-static int make_k_tensor_map(const tenzo_attention_args& a, CUtensorMap* out) {
+// Block pools (paged): a 2-D byte matrix {128, every row of the pool}, read in boxes of one block slice (16 rows).
+static int make_k_tensor_map(const tenzo_attention_args& a, CUtensorMap* out, bool paged) {
     typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -629,6 +714,16 @@ static int make_k_tensor_map(const tenzo_attention_args& a, CUtensorMap* out) {
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn)
             return -4;
         encode = reinterpret_cast<EncodeFn>(fn);
+    }
+    if (paged) {
+        const cuuint64_t rows = (cuuint64_t)a.n_pool_blocks * a.n_layers * a.n_kv * 16;
+        const cuuint64_t dims[2] = {(cuuint64_t)kHd, rows};
+        const cuuint64_t strides[1] = {(cuuint64_t)kHd};
+        const cuuint32_t box[2] = {(cuuint32_t)kHd, 16u};
+        const cuuint32_t estr[2] = {1u, 1u};
+        const CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a.cache_k, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        return r == CUDA_SUCCESS ? 0 : -4;
     }
     // rows reachable from the layers up to this one; tiles that run past them are zero-filled and their keys are never used
     const cuuint64_t rows = (cuuint64_t)(a.layer + 1) * a.n_kv * a.max_seq;
@@ -646,8 +741,9 @@ static int launch_attn(const AttnLaunch& L, cudaStream_t st) {
     CUtensorMap kmap;
     std::memset(&kmap, 0, sizeof kmap);
     if (TILED)
-        if (int rc = make_k_tensor_map(L.a, &kmap)) return rc;
-    const size_t smem = TILED ? AttnSmem<GH>::bytes_tiled(L.a.max_len, L.n_tile_warps) : AttnSmem<GH>::bytes(L.a.max_len);
+        if (int rc = make_k_tensor_map(L.a, &kmap, PAGED)) return rc;
+    const size_t smem = (TILED ? AttnSmem<GH>::bytes_tiled(L.a.max_len, L.n_tile_warps) : AttnSmem<GH>::bytes(L.a.max_len)) +
+                        (PAGED ? AttnSmem<GH>::table_bytes(L.a.max_len) : 0);
     cudaError_t e = cudaFuncSetAttribute(attn_kernel<GH, TILED, PAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     cudaLaunchConfig_t cfg = {};
@@ -665,7 +761,7 @@ static int launch_attn(const AttnLaunch& L, cudaStream_t st) {
 }
 
 template <int GH>
-static int tile_warps_for(int max_len) { return AttnSmem<GH>::tile_warps_that_fit(max_len); }
+static int tile_warps_for(int max_len, bool paged = false) { return AttnSmem<GH>::tile_warps_that_fit(max_len, paged); }
 
 // Query heads per CTA: as many as share a kv head, halved while that leaves SMs idle or the score
 // vectors [max_len][GH] would not fit in shared memory.
@@ -707,7 +803,7 @@ extern "C" int tenzo_cuda_attention_int8(const tenzo_attention_args* args, void*
     if (!a.q || !a.out || !a.cache_k || !a.cache_v || !a.scale_k || !a.scale_v || !a.pos) return -1;
     if (a.append && (!a.k || !a.v)) return -1;
     if (a.head_dim != kHd) return -5;
-    if (a.block_table && (a.n_layers <= 0 || a.layer < 0 || a.layer >= a.n_layers || a.table_stride < 0 || a.tiles == 1)) return a.tiles == 1 ? -5 : -1;
+    if (a.block_table && (a.n_layers <= 0 || a.layer < 0 || a.layer >= a.n_layers || a.table_stride < 0 || a.n_pool_blocks < 0)) return -1;
     if (a.n_q <= 0 || a.n_kv <= 0 || a.n_q % a.n_kv || a.batch <= 0 || a.max_len <= 0 || a.max_len > a.max_seq) return -1;
     if ((a.rope_cos == nullptr) != (a.rope_sin == nullptr)) return -1;
     const int group = a.n_q / a.n_kv;
@@ -721,7 +817,28 @@ extern "C" int tenzo_cuda_attention_int8(const tenzo_attention_args* args, void*
     L.gh = pick_heads_per_cta(a.batch, a.n_q, group, a.max_len);
     if (a.heads_per_cta == 1 || a.heads_per_cta == 2 || a.heads_per_cta == 4 || a.heads_per_cta == 8)
         if (a.heads_per_cta <= group && (size_t)a.heads_per_cta * a.max_len * sizeof(float) <= (size_t)kScoreSmemBytes) L.gh = a.heads_per_cta;
-    if (a.block_table) {                     // block pools: per-lane loads through the block table
+    if (a.block_table) {
+        // block pools: K through TMA tiles of four blocks when there are many (sequence, kv head) items and the pool
+        // size is known (the tensor map needs it); per-lane loads through the block table otherwise
+        int ptw = 0;
+        switch (L.gh) {
+            case 1: ptw = tile_warps_for<1>(a.max_len, true); break;
+            case 2: ptw = tile_warps_for<2>(a.max_len, true); break;
+            case 4: ptw = tile_warps_for<4>(a.max_len, true); break;
+            default: break;
+        }
+        const long long pool_rows = (long long)a.n_pool_blocks * a.n_layers * a.n_kv * 16;
+        const bool ptiled = a.tiles != 2 && ptw >= 4 && (a.tiles == 1 || a.batch * a.n_kv >= 64) && a.n_pool_blocks > 0 &&
+                            pool_rows < (1LL << 31) && (reinterpret_cast<uintptr_t>(a.cache_k) & 15) == 0;
+        if (a.tiles == 1 && !ptiled) return -5;
+        if (ptiled) {
+            L.n_tile_warps = ptw;
+            switch (L.gh) {
+                case 1: return launch_attn<1, true, true>(L, st);
+                case 2: return launch_attn<2, true, true>(L, st);
+                default: return launch_attn<4, true, true>(L, st);
+            }
+        }
         L.n_tile_warps = 0;
         switch (L.gh) {
             case 1: return launch_attn<1, false, true>(L, st);

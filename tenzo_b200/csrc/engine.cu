@@ -399,7 +399,7 @@ void Engine::enqueue_layer(int l, int max_len, bool gemv_only) {
     a.max_seq = cfg.max_seq_len; a.batch = batch; a.max_len = max_len; a.append = 1;
     a.use_pdl = use_pdl;
     a.q_stride = a.kv_stride = qd + 2 * kvd;
-    if (paged) { a.block_table = d_table; a.table_stride = table_stride; a.n_layers = L; }
+    if (paged) { a.block_table = d_table; a.table_stride = table_stride; a.n_layers = L; a.n_pool_blocks = total_blocks; }
     if (!gemv_only) {
         TZ_KERNEL(tenzo_cuda_attention_int8(&a, stream));
         launches += 1;
@@ -513,7 +513,7 @@ void Engine::prefill_chunk(const int* tokens, int M) {
         a.pos = pf_pos; a.rope_cos = rope_cos; a.rope_sin = rope_sin;
         a.layer = l; a.n_q = cfg.num_q_heads; a.n_kv = cfg.num_kv_heads; a.head_dim = 128;
         a.max_seq = cfg.max_seq_len; a.batch = M; a.max_len = max_len; a.append = 0; a.tiles = 2;
-        if (paged) { a.block_table = d_table; a.table_stride = 0; a.n_layers = L; }      // every query row reads sequence 0's table
+        if (paged) { a.block_table = d_table; a.table_stride = 0; a.n_layers = L; a.n_pool_blocks = total_blocks; }      // every query row reads sequence 0's table
         TZ_KERNEL(tenzo_cuda_attention_int8(&a, stream));
         g.x = pf_attn; g.x_stride = qd; g.norm_w = d.attn_sub_norm; g.w = d.o; g.K = h;
         g.n_blocks = h / 64; g.seg_end[0] = g.seg_end[1] = g.seg_end[2] = g.n_blocks; g.seg_scale[0] = d.s_o;

@@ -108,6 +108,7 @@ def attention_int8(q, k, v, cache_k, cache_v, scale_k, scale_v, pos, *, layer, n
     if block_table is not None:
         assert block_table.dtype == torch.int32 and block_table.is_contiguous()
         a.block_table, a.table_stride, a.n_layers = _ptr(block_table), (block_table.stride(0) if block_table.dim() == 2 else 0), n_layers
+        a.n_pool_blocks = cache_k.shape[0]
     _ok(lib.tenzo_cuda_attention_int8(C.byref(a), _stream()), "tenzo_cuda_attention_int8")
     return out
 

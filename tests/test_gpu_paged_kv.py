@@ -57,13 +57,16 @@ def test_paged_attention_token_by_token_against_reference_vectors(cuda_lib, gold
 
 @pytest.mark.parametrize("nq,nkv", [(8, 2), (8, 1), (4, 4)])
 @pytest.mark.parametrize("heads_per_cta", [0, 1, 2, 4, 8])
-def test_paged_attention_many_sequences_share_one_pool(cuda_lib, nq, nkv, heads_per_cta):
+@pytest.mark.parametrize("tiles", [2, 1])
+def test_paged_attention_many_sequences_share_one_pool(cuda_lib, nq, nkv, heads_per_cta, tiles):
     """Ragged lengths, interleaved blocks of several sequences in one pool, every heads-per-CTA variant, with and
-    without the append."""
+    without the append; keys read per lane through the table (tiles = 2) and as TMA tiles of four blocks (tiles = 1)."""
     from tenzo_b200 import kernels
+    if tiles == 1 and heads_per_cta == 8 and nq // nkv == 8:
+        pytest.skip("eight heads per CTA exist only with per-lane loads")
     O = ora.load_oracle()
     L, layer, per_seq = 3, 2, 41
-    lens = [1, 15, 16, 17, 128, 129, 257, 300, 640]
+    lens = [1, 15, 16, 17, 63, 64, 65, 128, 129, 257, 300, 640]
     B = len(lens)
     blocks = B * per_seq
     rng = np.random.default_rng([61, nq, nkv])
@@ -80,7 +83,7 @@ def test_paged_attention_many_sequences_share_one_pool(cuda_lib, nq, nkv, heads_
     pos = np.array([n - 1 for n in lens], np.int32)
     dpk, dpv, dsk, dsv = dev(pk), dev(pv), dev(psk), dev(psv)
     common = dict(layer=layer, n_q=nq, n_kv=nkv, max_seq=per_seq * 16, rope_cos=dev(cs), rope_sin=dev(sn), heads_per_cta=heads_per_cta,
-                  block_table=dev(table), n_layers=L)
+                  block_table=dev(table), n_layers=L, tiles=tiles)
     out = kernels.attention_int8(dev(q), dev(k), dev(v), dpk, dpv, dsk, dsv, dev(pos), **common)
     torch.cuda.synchronize()
     opk, opv, osk, osv = pk.reshape(-1).copy(), pv.reshape(-1).copy(), psk.reshape(-1).copy(), psv.reshape(-1).copy()
@@ -93,6 +96,41 @@ def test_paged_attention_many_sequences_share_one_pool(cuda_lib, nq, nkv, heads_
     again = kernels.attention_int8(dev(q), None, None, dpk, dpv, dsk, dsv, dev(pos), append=False, **common)
     assert np.array_equal(host(again), host(out))
     assert np.array_equal(host(dpk).reshape(-1), opk) and np.array_equal(host(dsv).reshape(-1), osv)
+    assert cuda_lib.tenzo_cuda_attention_take_timeouts() == 0
+
+
+def test_paged_attention_tma_tiles_long_context(cuda_lib):
+    """Contexts long enough that a scoring warp refills its two-stage ring several times (12 warps x 64 keys x 2 stages =
+    1536 keys), blocks scattered over the pool, GQA group 4."""
+    from tenzo_b200 import kernels
+    O = ora.load_oracle()
+    nq, nkv, L, layer, per_seq = 8, 2, 2, 0, 200
+    lens = [1, 1536, 1537, 2000, 3100, 3137]
+    B = len(lens)
+    blocks = B * per_seq
+    rng = np.random.default_rng(62)
+    table = rng.permutation(blocks).astype(np.int32).reshape(B, per_seq)
+    pk = rng.integers(-127, 128, (blocks, L, nkv, 16, 128)).astype(np.int8)
+    pv = rng.integers(-127, 128, (blocks, L, nkv, 16, 128)).astype(np.int8)
+    psk = (0.01 + 0.02 * rng.random((blocks, L, nkv, 16))).astype(np.float32)
+    psv = (0.01 + 0.02 * rng.random((blocks, L, nkv, 16))).astype(np.float32)
+    q = rng.standard_normal((B, nq * 128)).astype(np.float32)
+    k = rng.standard_normal((B, nkv * 128)).astype(np.float32)
+    v = rng.standard_normal((B, nkv * 128)).astype(np.float32)
+    cs, sn = rope_tables(per_seq * 16, 10000.0)
+    pos = np.array([n - 1 for n in lens], np.int32)
+    outs = {}
+    for tiles in (1, 2):
+        dpk, dpv, dsk, dsv = dev(pk), dev(pv), dev(psk), dev(psv)
+        outs[tiles] = host(kernels.attention_int8(dev(q), dev(k), dev(v), dpk, dpv, dsk, dsv, dev(pos), layer=layer, n_q=nq, n_kv=nkv,
+                                                  max_seq=per_seq * 16, rope_cos=dev(cs), rope_sin=dev(sn), block_table=dev(table),
+                                                  n_layers=L, tiles=tiles))
+    assert np.array_equal(outs[1], outs[2])
+    opk, opv, osk, osv = pk.reshape(-1).copy(), pv.reshape(-1).copy(), psk.reshape(-1).copy(), psv.reshape(-1).copy()
+    for b in range(B):
+        o = oracle_paged(O, layer, int(pos[b]), nq, nkv, L, q[b], k[b], v[b], opk, opv, osk, osv, table[b])
+        assert np.array_equal(outs[1][b], o), f"sequence {b} (length {lens[b]})"
+    assert np.array_equal(host(dpk).reshape(-1), opk) and np.array_equal(host(dsk).reshape(-1), osk)
     assert cuda_lib.tenzo_cuda_attention_take_timeouts() == 0
 
 
