@@ -138,7 +138,8 @@ typedef struct {
 } tenzo_attention_args;
 
 TENZO_API int tenzo_cuda_attention_int8(const tenzo_attention_args* args, void* stream);
-/* As tenzo_cuda_tl1_gemv_take_timeouts, for the attention kernel's bounded waits on its V-chunk copies. */
+/* As tenzo_cuda_tl1_gemv_take_timeouts, for the attention kernel's bounded waits on its V-chunk copies (1). Also
+ * returns 2 when a launch found a pos[s] outside [0, max_len): that CTA wrote nothing. */
 TENZO_API int tenzo_cuda_attention_take_timeouts(void);
 /* Query heads one CTA will process for this shape (1..n_q/n_kv); informational. */
 TENZO_API int tenzo_cuda_attention_heads_per_cta(int batch, int n_q, int n_kv, int max_len);
@@ -189,9 +190,10 @@ TENZO_API int tenzo_cuda_topk_candidates(const float* logits, int vocab, int k, 
 TENZO_API int tenzo_cuda_topk_max_candidates(void);
 
 /* ---- INT8 embedding row dequantisation ---------------------------------------------------------
- * Replaces embedding_lookup's int8 branch (:1299-1315): x = (float)W8[tok] * scale[tok]. */
+ * Replaces embedding_lookup's int8 branch (:1299-1315): x = (float)W8[tok] * scale[tok].
+ * vocab > 0: token ids outside [0, vocab) are read as row 0 rather than past the table; 0 = unchecked. */
 TENZO_API int tenzo_cuda_embedding_i8(const int8_t* w, const float* row_scales, int hidden,
-                                      const int* tokens, int batch, float* x, int x_stride, void* stream);
+                                      const int* tokens, int batch, float* x, int x_stride, int vocab, void* stream);
 
 /* ---- checkpoint rows -> TL1 layout --------------------------------------------------------------
  * Replaces pack_ternary_weights_raw (:1842-1884): raw [N/4][K] bytes (row r in bits 2*(r%4)) to

@@ -168,7 +168,7 @@ def declare_kernel_abi(L):
     L.tenzo_cuda_topk_candidates.restype, L.tenzo_cuda_topk_candidates.argtypes = i32, [vp, i32, i32, vp, vp, vp, vp]
     L.tenzo_cuda_topk_max_candidates.restype, L.tenzo_cuda_topk_max_candidates.argtypes = i32, []
     L.tenzo_cuda_lm_head_scratch_bytes.restype, L.tenzo_cuda_lm_head_scratch_bytes.argtypes = sz, [i32]
-    L.tenzo_cuda_embedding_i8.restype, L.tenzo_cuda_embedding_i8.argtypes = i32, [vp, vp, i32, vp, i32, vp, i32, vp]
+    L.tenzo_cuda_embedding_i8.restype, L.tenzo_cuda_embedding_i8.argtypes = i32, [vp, vp, i32, vp, i32, vp, i32, i32, vp]
     L.tenzo_cuda_tl1_pack_rows2bit.restype, L.tenzo_cuda_tl1_pack_rows2bit.argtypes = i32, [vp, i32, i32, vp, vp]
     L.tenzo_hal_initialize.restype, L.tenzo_hal_initialize.argtypes = i32, []
     L.tenzo_hal_bitlinear_tl1_host.restype = i32

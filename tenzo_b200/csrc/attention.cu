@@ -105,7 +105,7 @@ __device__ __forceinline__ void tma_load_k_rows(void* dst, const CUtensorMap* ma
                  ::"r"(smem_addr(dst)), "l"(map), "r"(0), "r"(row0), "r"(smem_addr(bar)) : "memory");
 }
 
-__device__ int g_attn_timeouts = 0;   // set when a bounded wait on a V-chunk copy gave up
+__device__ int g_attn_timeouts = 0;   // 1: a bounded wait on a V-chunk copy gave up; 2: a position outside [0, max_len) was refused
 
 #ifdef TZ_ATTN_TRACE
 __device__ unsigned long long g_attn_phase[8];
@@ -266,6 +266,12 @@ __global__ void __launch_bounds__(TILED ? kTileThreads : kAttnThreads) attn_kern
     if (a.use_pdl) pdl_wait();
     TZ_PH_DECL;
     const int pos = a.pos[seq];
+    // max_len sizes the score vectors and the staged block table: a position outside [0, max_len) would write past
+    // them, so the CTA flags it (the host reads the flag like a give-up) and leaves without touching memory.
+    if (pos < 0 || pos >= a.max_len) {
+        if (tid == 0) atomicExch(&g_attn_timeouts, 2);
+        return;
+    }
     const int T = pos + 1;
     const int n_chunks = (T + kChunk - 1) / kChunk;
 

@@ -58,11 +58,14 @@ void set_error(const std::string& m) { g_last_error = m; }
         if (_r < 0) throw std::runtime_error(std::string(#expr) + " rejected its arguments");   \
     } while (0)
 
-__global__ void advance_kernel(int* pos, int* tokens, const int* next, int batch, int feed_back) {
+__global__ void advance_kernel(int* pos, int* tokens, const int* next, int batch, int feed_back, int vocab) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < batch) {
         pos[i] += 1;
-        if (feed_back) tokens[i] = next[i];
+        if (feed_back) {
+            const int t = next[i];
+            tokens[i] = (t >= 0 && t < vocab) ? t : 0;
+        }
     }
 }
 
@@ -143,7 +146,18 @@ static int env_flag(const char* name, int dflt) {
     return s ? std::atoi(s) : dflt;
 }
 
+// A constructor that throws never runs the destructor, so what it had acquired by then (stream, events, device and
+// pinned memory) is released here before the exception leaves.
 Engine::Engine(const tenzo_config_t& c, const tenzo_ext_options_t& o) : cfg(c) {
+    try {
+        init(c, o);
+    } catch (...) {
+        release_all();
+        throw;
+    }
+}
+
+void Engine::init(const tenzo_config_t& c, const tenzo_ext_options_t& o) {
     batch = o.batch > 0 ? o.batch : 1;
     rope_theta = o.rope_theta > 0.0f ? o.rope_theta : 10000.0f;   // TenzoEngine.cpp:456
     use_graph = o.use_graph >= 0 ? o.use_graph : env_flag("TENZO_CUDA_GRAPH", 1);
@@ -231,20 +245,37 @@ Engine::Engine(const tenzo_config_t& c, const tenzo_ext_options_t& o) : cfg(c) {
     TZ_CUDA(cudaStreamSynchronize(stream));
 }
 
-Engine::~Engine() {
-    cudaStreamSynchronize(stream);
+// Everything the engine owns, safe to call on a partly constructed object (the constructor calls it when it throws).
+void Engine::release_all() {
+    if (stream) cudaStreamSynchronize(stream);
     for (auto& kv : graphs) cudaGraphExecDestroy(kv.second);
+    graphs.clear();
     for (void* p : owned) cudaFree(p);
+    owned.clear();
     if (h_pin) cudaFreeHost(h_pin);
     if (h_table) cudaFreeHost(h_table);
     if (h_cand) cudaFreeHost(h_cand);
-    for (void* p : {(void*)pf_x, (void*)pf_qkv, (void*)pf_attn, (void*)pf_h1, (void*)pf_act, (void*)pf_tokens, (void*)pf_pos, pf_ws})
-        if (p) cudaFree(p);
+    h_pin = nullptr; h_table = nullptr; h_cand = nullptr;
+    free_prefill_rows();
     if (d_sample_past) cudaFree(d_sample_past);
     if (d_history) cudaFree(d_history);
-    cudaEventDestroy(ev0);
-    cudaEventDestroy(ev1);
-    cudaStreamDestroy(stream);
+    d_sample_past = nullptr; d_history = nullptr;
+    if (ev0) cudaEventDestroy(ev0);
+    if (ev1) cudaEventDestroy(ev1);
+    if (stream) cudaStreamDestroy(stream);
+    ev0 = ev1 = nullptr;
+    stream = nullptr;
+}
+
+Engine::~Engine() { release_all(); }
+
+void Engine::free_prefill_rows() {
+    void** ptrs[] = {(void**)&pf_x, (void**)&pf_qkv, (void**)&pf_attn, (void**)&pf_h1, (void**)&pf_act, (void**)&pf_tokens, (void**)&pf_pos, &pf_ws};
+    for (void** p : ptrs) {
+        if (*p) cudaFree(*p);
+        *p = nullptr;
+    }
+    pf_cap = 0;
 }
 
 void Engine::reserve_blocks(int s, int len) {
@@ -437,7 +468,7 @@ void Engine::enqueue_layer(int l, int max_len, bool gemv_only) {
 
 void Engine::enqueue_step(bool with_logits, bool feed_back, int max_len) {
     if (!lm_w) throw std::runtime_error("LM head / embedding was never set");
-    TZ_KERNEL(tenzo_cuda_embedding_i8(lm_w, lm_scales, h, d_tokens, batch, b_x, h, stream));
+    TZ_KERNEL(tenzo_cuda_embedding_i8(lm_w, lm_scales, h, d_tokens, batch, b_x, h, V, stream));
     launches += 1;
     for (int l = 0; l < L; ++l) enqueue_layer(l, max_len);
     if (with_logits) {
@@ -445,7 +476,7 @@ void Engine::enqueue_step(bool with_logits, bool feed_back, int max_len) {
                                         d_next, lm_scratch, use_pdl, stream));
         launches += batch >= 16 && h % 128 == 0 ? 3 : 2;   // (quantiser +) LM head + argmax finish
     }
-    advance_kernel<<<(batch + 127) / 128, 128, 0, stream>>>(d_pos, d_tokens, d_next, batch, feed_back ? 1 : 0);
+    advance_kernel<<<(batch + 127) / 128, 128, 0, stream>>>(d_pos, d_tokens, d_next, batch, feed_back ? 1 : 0, V);
     TZ_CUDA(cudaGetLastError());
     launches += 1;
 }
@@ -464,18 +495,24 @@ void Engine::prefill_chunk(const int* tokens, int M) {
     for (int i = 0; i < M; ++i)
         if (tokens[i] < 0 || tokens[i] >= V) throw std::out_of_range("token id outside [0, vocab_size)");
     if (M > pf_cap) {
-        for (void* p : {(void*)pf_x, (void*)pf_qkv, (void*)pf_attn, (void*)pf_h1, (void*)pf_act, (void*)pf_tokens, (void*)pf_pos, pf_ws})
-            if (p) cudaFree(p);
-        pf_cap = M;
+        // Free first, forget the old pointers, and claim the new capacity only once every allocation has succeeded: a
+        // failed cudaMalloc must leave the engine with no rows rather than with freed ones.
+        free_prefill_rows();
         const size_t m = (size_t)M;
-        TZ_CUDA(cudaMalloc((void**)&pf_x, m * h * 4));
-        TZ_CUDA(cudaMalloc((void**)&pf_qkv, m * (qd + 2 * kvd) * 4));
-        TZ_CUDA(cudaMalloc((void**)&pf_attn, m * qd * 4));
-        TZ_CUDA(cudaMalloc((void**)&pf_h1, m * h * 4));
-        TZ_CUDA(cudaMalloc((void**)&pf_act, m * ffn * 4));
-        TZ_CUDA(cudaMalloc((void**)&pf_tokens, m * 4));
-        TZ_CUDA(cudaMalloc((void**)&pf_pos, m * 4));
-        TZ_CUDA(cudaMalloc(&pf_ws, tenzo_cuda_tl1_gemv_workspace_bytes(M > 1 ? M : 2, h > ffn ? h : ffn)));
+        try {
+            TZ_CUDA(cudaMalloc((void**)&pf_x, m * h * 4));
+            TZ_CUDA(cudaMalloc((void**)&pf_qkv, m * (qd + 2 * kvd) * 4));
+            TZ_CUDA(cudaMalloc((void**)&pf_attn, m * qd * 4));
+            TZ_CUDA(cudaMalloc((void**)&pf_h1, m * h * 4));
+            TZ_CUDA(cudaMalloc((void**)&pf_act, m * ffn * 4));
+            TZ_CUDA(cudaMalloc((void**)&pf_tokens, m * 4));
+            TZ_CUDA(cudaMalloc((void**)&pf_pos, m * 4));
+            TZ_CUDA(cudaMalloc(&pf_ws, tenzo_cuda_tl1_gemv_workspace_bytes(M > 1 ? M : 2, h > ffn ? h : ffn)));
+        } catch (...) {
+            free_prefill_rows();
+            throw;
+        }
+        pf_cap = M;
     }
     const int pos0 = seq_len[0];
     prepare_kv(M);
@@ -484,7 +521,7 @@ void Engine::prefill_chunk(const int* tokens, int M) {
     TZ_CUDA(cudaMemcpyAsync(pf_tokens, tokens, (size_t)M * 4, cudaMemcpyHostToDevice, stream));
     TZ_CUDA(cudaMemcpyAsync(pf_pos, hp.data(), (size_t)M * 4, cudaMemcpyHostToDevice, stream));
     TZ_CUDA(cudaEventRecord(ev0, stream));
-    TZ_KERNEL(tenzo_cuda_embedding_i8(lm_w, lm_scales, h, pf_tokens, M, pf_x, h, stream));
+    TZ_KERNEL(tenzo_cuda_embedding_i8(lm_w, lm_scales, h, pf_tokens, M, pf_x, h, V, stream));
     launches += 1;
     const int gemv_kernels = M > 1 ? 2 : 1;
     const int max_len = bucket_for(pos0 + M, cfg.max_seq_len);
@@ -605,8 +642,11 @@ void Engine::push_state(const int* tokens) {
 // The TL1 kernel's waits on asynchronous copies are bounded; a give-up is reported here instead of
 // hanging the device. Polled sparsely on the per-token path (the query synchronises).
 void Engine::check_device_status(bool force) {
-    if (!force && (++status_poll & 31) != 0) return;
-    if (tenzo_cuda_attention_take_timeouts() > 0) throw std::runtime_error("an attention kernel gave up waiting for a KV copy; results are invalid");
+    // The flags live in device memory, so reading them costs a few synchronising copies: every call for batched engines
+    // (a step there is milliseconds), every 32nd token on the single-sequence kernel chain.
+    if (!force && batch == 1 && (++status_poll & 31) != 0) return;
+    if (tenzo_cuda_attention_take_timeouts() > 0)
+        throw std::runtime_error("an attention kernel gave up waiting for a KV copy or refused a position outside its bound; results are invalid");
     if (tenzo_cuda_lm_head_take_timeouts() > 0) throw std::runtime_error("the LM head kernel gave up waiting for a tile copy; results are invalid");
     if (tenzo_cuda_tl1_gemv_take_timeouts() > 0) throw std::runtime_error("a TL1 kernel gave up waiting for its weight copy; results are invalid");
 }

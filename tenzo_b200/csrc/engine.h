@@ -43,6 +43,7 @@ class Engine {
 public:
     Engine(const tenzo_config_t& cfg, const tenzo_ext_options_t& opt);
     ~Engine();
+    void init(const tenzo_config_t& cfg, const tenzo_ext_options_t& opt);
     Engine(const Engine&) = delete;
     Engine& operator=(const Engine&) = delete;
 
@@ -62,6 +63,8 @@ public:
     void enqueue_layer(int l, int max_len, bool gemv_only = false);
     float bench_gemv_stack(int iters, unsigned long long* n_launches);
     void invalidate_graphs();
+    void free_prefill_rows();
+    void release_all();
     void* upload(const void* host, size_t bytes);
     float last_ms();
     void check_device_status(bool force);

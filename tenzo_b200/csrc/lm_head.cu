@@ -141,6 +141,7 @@ __global__ void __launch_bounds__(kLmThreads) lm_head_kernel(
             if (logits) logits[(size_t)(seq0 + lane) * vocab + v] = lg;
             if (acc_out) acc_out[(size_t)(seq0 + lane) * vocab + v] = mine;
             if (better(lg, v, best_v, best_i)) { best_v = lg; best_i = v; }
+            if (v == 0 && lg != lg) { best_v = INFINITY; best_i = 0; }   // a NaN at index 0 is never displaced (strict '>', :1747-1753)
         }
     }
     if (lane < NS) { s_best[warp * NS + lane].val = best_v; s_best[warp * NS + lane].idx = best_i; }
@@ -167,12 +168,16 @@ __global__ void __launch_bounds__(256) argmax_finish_kernel(const LmBest* cta_be
         if (tid < h && better(s[tid + h].val, s[tid + h].idx, s[tid].val, s[tid].idx)) s[tid] = s[tid + h];
         __syncthreads();
     }
-    if (tid == 0) argmax_out[seq] = s[0].idx;
+    // nothing compared greater (every logit NaN or -inf): the reference's scan stays at index 0 (:1746)
+    if (tid == 0) argmax_out[seq] = s[0].idx == 0x7fffffff ? 0 : s[0].idx;
 }
 
+// vocab > 0: ids outside [0, vocab) are read as row 0 instead of reaching past the table.
 __global__ void embedding_i8_kernel(const int8_t* __restrict__ w, const float* __restrict__ row_scales, int hidden,
-                                    const int* __restrict__ tokens, float* x, int x_stride) {
-    const int seq = blockIdx.x, tok = tokens[seq];
+                                    const int* __restrict__ tokens, float* x, int x_stride, int vocab) {
+    const int seq = blockIdx.x;
+    int tok = tokens[seq];
+    if (vocab > 0 && (tok < 0 || tok >= vocab)) tok = 0;
     const int8_t* row = w + (size_t)tok * hidden;
     const float s = row_scales[tok];
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) x[(size_t)seq * x_stride + i] = (float)row[i] * s;   // :1313
@@ -321,9 +326,9 @@ extern "C" int tenzo_cuda_lm_head_i8_static(const float* x, const float* norm_w,
 extern "C" int tenzo_cuda_lm_head_static_max_batch(void) { return tz::kLmStaticMaxBatch; }
 
 extern "C" int tenzo_cuda_embedding_i8(const int8_t* w, const float* row_scales, int hidden, const int* tokens,
-                                       int batch, float* x, int x_stride, void* stream) {
-    if (!w || !row_scales || !tokens || !x || hidden <= 0 || batch <= 0) return -1;
-    tz::embedding_i8_kernel<<<batch, 256, 0, static_cast<cudaStream_t>(stream)>>>(w, row_scales, hidden, tokens, x, x_stride);
+                                       int batch, float* x, int x_stride, int vocab, void* stream) {
+    if (!w || !row_scales || !tokens || !x || hidden <= 0 || batch <= 0 || vocab < 0) return -1;
+    tz::embedding_i8_kernel<<<batch, 256, 0, static_cast<cudaStream_t>(stream)>>>(w, row_scales, hidden, tokens, x, x_stride, vocab);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? 0 : (int)e;
 }

@@ -167,6 +167,7 @@ __global__ void __launch_bounds__(kLmuThreads, 1) lm_head_umma_kernel(const LmUm
                     const float val = col[rr];
                     if (idx < L.vocab && better(val, idx, b.val, b.idx)) { b.val = val; b.idx = idx; }
                 }
+                if (tile == 0 && col[0] != col[0]) { b.val = INFINITY; b.idx = 0; }   // a NaN at index 0 is never displaced (:1747-1753)
                 L.cand[(size_t)seq * L.n_tiles + tile] = b;
             }
         }

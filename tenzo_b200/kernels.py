@@ -143,7 +143,7 @@ def embedding_i8(w, row_scales, tokens):
     lib = load_library()
     batch, hidden = tokens.shape[0], w.shape[1]
     x = torch.empty(batch, hidden, dtype=torch.float32, device=w.device)
-    _ok(lib.tenzo_cuda_embedding_i8(_ptr(w), _ptr(row_scales), hidden, _ptr(tokens), batch, _ptr(x), hidden, _stream()),
+    _ok(lib.tenzo_cuda_embedding_i8(_ptr(w), _ptr(row_scales), hidden, _ptr(tokens), batch, _ptr(x), hidden, w.shape[0], _stream()),
         "tenzo_cuda_embedding_i8")
     return x
 

@@ -21,7 +21,10 @@ def test_static_scratch_lm_head_matches_allocating_entry_point(cuda_lib):
     s = torch.from_numpy((0.001 + 0.001 * rng.random(V)).astype(np.float32)).cuda()
     nw = torch.from_numpy((1 + 0.1 * rng.standard_normal(H)).astype(np.float32)).cuda()
     assert cuda_lib.tenzo_cuda_lm_head_static_max_batch() == 32
-    for call, batch in enumerate((3, 1)):           # second call: smaller batch over the first call's leftovers
+    # 32 fills the built-in array exactly; 17 and 32 are sizes at which the allocating entry point switches to its
+    # tensor-core kernel while this one must stay on the warp-per-row kernel; the last call is a smaller batch over
+    # the earlier calls' leftovers
+    for call, batch in enumerate((3, 32, 17, 1)):
         x = torch.from_numpy(rng.standard_normal((batch, H)).astype(np.float32)).cuda()
         want_logits, _, want_arg = kernels.lm_head_i8(x, w, s, norm_w=nw)
         logits = torch.full((batch, V), float("nan"), dtype=torch.float32, device="cuda")
