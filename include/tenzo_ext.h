@@ -19,6 +19,11 @@ typedef struct {
     float rope_theta;   /* <= 0 selects the reference's 10000 */
     int use_graph;      /* 1: replay each decode step as a CUDA graph; 0: plain launches; -1 default */
     int use_pdl;        /* 1: programmatic dependent launch between kernels; 0: off; -1 default */
+    int persistent;     /* batch 1 only. 1: run each token as ONE persistent cooperative kernel (grid-wide barriers between
+                           the operators, weights streamed ahead through shared memory) when the shapes allow it; 0: the
+                           chain of one kernel per operator; -1 default (0, or the TENZO_PERSISTENT environment variable).
+                           Results are bit-identical either way; on B200 the chain is the faster of the two (the barriers and
+                           L2 round trips of the one-kernel form cost more than the launches they replace). */
 } tenzo_ext_options_t;
 
 TENZO_API tenzo_ext_options_t tenzo_ext_default_options(void);
@@ -71,6 +76,12 @@ TENZO_API float tenzo_ext_last_device_ms(tenzo_engine_t engine);
  * or LM head in between, and returns the CUDA-event time in ms (< 0 on failure). *launches
  * receives the number of GEMV kernels timed. */
 TENZO_API float tenzo_ext_bench_gemv_stack(tenzo_engine_t engine, int iters, unsigned long long* launches);
+/* Measurement aid for the persistent single-sequence kernel: nanoseconds (GPU global timer, read by one thread of the
+ * first CTA at every grid-wide barrier) spent since the last reset in each phase kind - [0] norm + q|k|v product,
+ * [1] attention, [2] out product, [3] gate|up product, [4] down product, [5] final norm + LM head, [6] argmax and exit.
+ * Returns 1 and fills out8[8] when that kernel is in use, 0 when the engine runs the per-operator kernel chain, -1 on
+ * failure. Synchronises with the engine's stream. */
+TENZO_API int tenzo_ext_persistent_phase_ns(tenzo_engine_t engine, unsigned long long* out8, int reset);
 /* Number of kernels launched (or replayed through a graph) since the engine was created. */
 TENZO_API unsigned long long tenzo_ext_kernel_launches(tenzo_engine_t engine);
 /* Message for the most recent failure on this thread ("" if none). */

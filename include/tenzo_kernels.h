@@ -135,12 +135,27 @@ typedef struct {
     int n_layers;
     int n_pool_blocks;      /* blocks in the pools; 0 = not given, which rules out the TMA-tile variant (tiles == 1 then
                                returns -5): its tensor map needs the pool's extent */
+    /* mode 0 (default): the reference's fp32 operation order, bit-identical outputs (above).
+     * mode 1: tolerance mode. Same function, free evaluation order: the keys of a sequence are split over CTAs and
+     * warps (online softmax, partials merged by log-sum-exp), both products run as fp16 tensor-core MMAs with fp32
+     * accumulation (INT8 K/V are exact in fp16; the rotated query and the weights are rounded to fp16), exp is the
+     * hardware ex2. Outputs agree with mode 0 to about 1e-4 of the output's largest magnitude (the specification asks
+     * 1e-3 for floating-point outputs); the cache bytes written for the new token are identical in both modes.
+     * Contiguous cache only (block_table must be NULL), 16-byte aligned caches and scales, max_seq a multiple of 4;
+     * returns -5 otherwise. */
+    int mode;
+    int split_keys;         /* mode 1: keys per CTA (rounded up to 128); 0 = choose automatically */
+    void* workspace;        /* mode 1: tenzo_cuda_attention_workspace_bytes(...) bytes, 16-byte aligned, for the partial
+                               results of the splits (contents need not be kept) */
+    size_t workspace_bytes;
 } tenzo_attention_args;
 
 TENZO_API int tenzo_cuda_attention_int8(const tenzo_attention_args* args, void* stream);
 /* As tenzo_cuda_tl1_gemv_take_timeouts, for the attention kernel's bounded waits on its V-chunk copies (1). Also
  * returns 2 when a launch found a pos[s] outside [0, max_len): that CTA wrote nothing. */
 TENZO_API int tenzo_cuda_attention_take_timeouts(void);
+/* Scratch bytes mode 1 may need for these sizes (an upper bound over every split it can choose). */
+TENZO_API size_t tenzo_cuda_attention_workspace_bytes(int batch, int n_q, int n_kv, int max_len);
 /* Query heads one CTA will process for this shape (1..n_q/n_kv); informational. */
 TENZO_API int tenzo_cuda_attention_heads_per_cta(int batch, int n_q, int n_kv, int max_len);
 

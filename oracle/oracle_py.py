@@ -118,20 +118,21 @@ from tenzo_b200.abi import TenzoConfig, TenzoSampling, TenzoLayerWeights, declar
 
 
 def ref_available(kind: str = "kernels") -> bool:
-    return (HERE / "_ref" / {"kernels": "libtenzo_ref_kernels.so", "fast": "libtenzo_ref_fast.so",
-                             "plain": "libtenzo_ref.so"}[kind]).exists()
+    return (HERE / "_ref" / _REF_FILES[kind]).exists()
 
 
+_REF_FILES = {"kernels": "libtenzo_ref_kernels.so", "fast": "libtenzo_ref_fast.so", "plain": "libtenzo_ref.so",
+              "kernels_fast": "libtenzo_ref_kernels_fast.so"}
 _refs: dict[str, C.CDLL] = {}
 
 
 def load_ref(kind: str = "kernels"):
-    """Load a compiled-reference library: 'kernels' (parity + trampolines), 'plain' or 'fast'."""
+    """Load a compiled-reference library: 'kernels' (parity + trampolines), 'plain', 'fast' (the reference's default
+    flags, for timing) or 'kernels_fast' (trampolines, default flags)."""
     if kind in _refs:
         return _refs[kind]
-    name = {"kernels": "libtenzo_ref_kernels.so", "fast": "libtenzo_ref_fast.so", "plain": "libtenzo_ref.so"}[kind]
-    L = declare_tenzo_abi(C.CDLL(str(HERE / "_ref" / name), mode=os.RTLD_LOCAL))
-    if kind == "kernels":
+    L = declare_tenzo_abi(C.CDLL(str(HERE / "_ref" / _REF_FILES[kind]), mode=os.RTLD_LOCAL))
+    if kind in ("kernels", "kernels_fast"):
         vp, i32, i64, f32 = C.c_void_p, C.c_int, C.c_int64, C.c_float
         sig = {
             "refk_build_lut": (f32, [c_f32p, i64, c_u8p]),

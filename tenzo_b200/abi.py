@@ -39,7 +39,7 @@ class TenzoLayerWeights(C.Structure):
 
 
 class TenzoExtOptions(C.Structure):
-    _fields_ = [("batch", C.c_int), ("rope_theta", C.c_float), ("use_graph", C.c_int), ("use_pdl", C.c_int)]
+    _fields_ = [("batch", C.c_int), ("rope_theta", C.c_float), ("use_graph", C.c_int), ("use_pdl", C.c_int), ("persistent", C.c_int)]
 
 
 class Tl1GemvArgs(C.Structure):
@@ -65,6 +65,7 @@ class AttentionArgs(C.Structure):
         ("batch", C.c_int), ("max_len", C.c_int), ("append", C.c_int),
         ("heads_per_cta", C.c_int), ("use_pdl", C.c_int), ("tiles", C.c_int),
         ("block_table", C.c_void_p), ("table_stride", C.c_int), ("n_layers", C.c_int), ("n_pool_blocks", C.c_int),
+        ("mode", C.c_int), ("split_keys", C.c_int), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
     ]
 
 
@@ -79,6 +80,7 @@ EXT_SYMBOLS = [
     "tenzo_ext_kv_fill_random", "tenzo_ext_set_seq_len", "tenzo_ext_get_seq_len", "tenzo_ext_read_buffer",
     "tenzo_ext_write_x", "tenzo_ext_run_layer", "tenzo_ext_synchronize", "tenzo_ext_last_device_ms",
     "tenzo_ext_kernel_launches", "tenzo_ext_last_error", "tenzo_ext_bench_gemv_stack", "tenzo_ext_rope_tables", "tenzo_ext_parse_manifest", "tenzo_ext_sample_pairs", "tenzo_ext_prefill_chunk",
+    "tenzo_ext_persistent_phase_ns",
 ]
 KERNEL_SYMBOLS = [
     "tenzo_cuda_tl1_gemv", "tenzo_cuda_tl1_gemv_ksplit", "tenzo_cuda_tl1_gemm_ksplit", "tenzo_cuda_tl1_gemv_workspace_bytes", "tenzo_cuda_tl1_gemv_take_timeouts", "tenzo_cuda_rmsnorm_quant", "tenzo_cuda_attention_int8",

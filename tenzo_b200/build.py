@@ -18,7 +18,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "lib" / "libtenzo_runtime.so"
-SOURCES = ["tl1_gemv.cu", "tl1_umma.cu", "norm_quant.cu", "attention.cu", "lm_head.cu", "lm_head_umma.cu", "sampler.cu", "engine.cu", "capi.cu",
+SOURCES = ["tl1_gemv.cu", "tl1_umma.cu", "norm_quant.cu", "attention.cu", "attention_fast.cu", "lm_head.cu", "lm_head_umma.cu", "sampler.cu", "decode_persistent.cu", "engine.cu", "capi.cu",
            "cuda_runtime_hal.cu", "model_loader.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -52,7 +52,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     procs = []
     for src in SOURCES:
         obj = objdir / (src[:-3] + ".o")
-        cmd = [nvcc, *NVCC_FLAGS, "-c", str(CSRC / src), "-o", str(obj)]
+        cmd = [nvcc, *NVCC_FLAGS, *os.environ.get("TENZO_NVCC_EXTRA", "").split(), "-c", str(CSRC / src), "-o", str(obj)]
         procs.append((src, obj, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     objs, log = [], []
     for src, obj, p in procs:

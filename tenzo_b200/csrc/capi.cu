@@ -83,6 +83,7 @@ tenzo_ext_options_t tenzo_ext_default_options(void) {
     o.rope_theta = 10000.0f;
     o.use_graph = -1;
     o.use_pdl = -1;
+    o.persistent = -1;
     return o;
 }
 
@@ -374,6 +375,21 @@ float tenzo_ext_bench_gemv_stack(tenzo_engine_t engine, int iters, unsigned long
 }
 
 unsigned long long tenzo_ext_kernel_launches(tenzo_engine_t engine) { return live(engine) ? engine->impl->launches : 0ull; }
+
+int tenzo_ext_persistent_phase_ns(tenzo_engine_t engine, unsigned long long* out8, int reset) {
+    if (!live(engine) || !out8) return -1;
+    tz::Engine& e = *engine->impl;
+    if (!e.pc_usable() || !e.pc_phase_ns) return 0;
+    cudaStreamSynchronize(e.stream);
+    if (cudaMemcpy(out8, e.pc_phase_ns, 8 * sizeof(unsigned long long), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (reset == 2) {                      // experiments: out8 has room for 72 values, the optional timeline follows the sums
+        if (cudaMemcpy(out8, e.pc_phase_ns, 72 * sizeof(unsigned long long), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    } else if (reset) {
+        cudaMemset(e.pc_phase_ns, 0, 8 * sizeof(unsigned long long));
+    }
+    return 1;
+}
+
 
 tenzo_status_t tenzo_ext_prefill_chunk(tenzo_engine_t engine, const int* tokens, int n) {
     if (!live(engine) || !tokens || n < 0) return TENZO_ERROR_INVALID_ARGUMENT;

@@ -162,6 +162,7 @@ void Engine::init(const tenzo_config_t& c, const tenzo_ext_options_t& o) {
     rope_theta = o.rope_theta > 0.0f ? o.rope_theta : 10000.0f;   // TenzoEngine.cpp:456
     use_graph = o.use_graph >= 0 ? o.use_graph : env_flag("TENZO_CUDA_GRAPH", 1);
     use_pdl = o.use_pdl >= 0 ? o.use_pdl : env_flag("TENZO_CUDA_PDL", 1);
+    persistent = o.persistent >= 0 ? o.persistent : env_flag("TENZO_PERSISTENT", 0);
     paged = c.kv_mode && std::strcmp(c.kv_mode, "paged_int8") == 0;       // TenzoEngine.cpp:1220
     cfg.kv_mode = paged ? "paged_int8" : "int8_fused";
     cfg.device = "cuda";
@@ -255,7 +256,8 @@ void Engine::release_all() {
     if (h_pin) cudaFreeHost(h_pin);
     if (h_table) cudaFreeHost(h_table);
     if (h_cand) cudaFreeHost(h_cand);
-    h_pin = nullptr; h_table = nullptr; h_cand = nullptr;
+    if (pc_host) cudaFreeHost(pc_host);
+    h_pin = nullptr; h_table = nullptr; h_cand = nullptr; pc_host = nullptr;
     free_prefill_rows();
     if (d_sample_past) cudaFree(d_sample_past);
     if (d_history) cudaFree(d_history);
@@ -391,6 +393,7 @@ void Engine::set_lm_head(const int8_t* w, const float* scales) {
 }
 
 void Engine::invalidate_graphs() {
+    pc_built = false;                      // the persistent kernel's layer table is rebuilt from the new pointers
     if (graphs.empty()) return;
     cudaStreamSynchronize(stream);
     for (auto& kv : graphs) cudaGraphExecDestroy(kv.second);
@@ -595,7 +598,9 @@ void Engine::run_step(bool with_logits, bool feed_back) {
     }
     const int max_len = bucket_for(longest, cfg.max_seq_len);
     prepare_kv(1);
-    if (!use_graph) {
+    if (pc_usable() && longest <= pc_score_cap(max_len)) {
+        pc_step(with_logits, feed_back, max_len);
+    } else if (!use_graph) {
         enqueue_step(with_logits, feed_back, max_len);
     } else {
         const int key = (with_logits ? 1 : 0) | (feed_back ? 2 : 0) | (max_len << 2);
@@ -657,9 +662,30 @@ void Engine::prefill(const int* tokens) {
     run_step(false, false);
     TZ_CUDA(cudaEventRecord(ev1, stream));
     TZ_CUDA(cudaStreamSynchronize(stream));
+    pc_check();
 }
 
 void Engine::generate(const int* cur, int* out) {
+    if (pc_usable() && seq_len[0] + 1 <= pc_score_cap(bucket_for(seq_len[0] + 1, cfg.max_seq_len))) {
+        // persistent kernel: token and position travel as kernel arguments, the result comes back through a mapped
+        // host word - no copies in either direction
+        if (!cur || cur[0] < 0 || cur[0] >= V) throw std::out_of_range("token id outside [0, vocab_size)");
+        pc_token_arg = cur[0];
+        pc_pos_arg = seq_len[0];
+        TZ_CUDA(cudaEventRecord(ev0, stream));
+        try {
+            run_step(true, false);
+        } catch (...) {
+            pc_token_arg = pc_pos_arg = -1;
+            throw;
+        }
+        pc_token_arg = pc_pos_arg = -1;
+        TZ_CUDA(cudaEventRecord(ev1, stream));
+        TZ_CUDA(cudaStreamSynchronize(stream));
+        pc_check();
+        out[0] = pc_host[1];
+        return;
+    }
     push_state(cur);
     TZ_CUDA(cudaEventRecord(ev0, stream));
     run_step(true, false);
@@ -688,6 +714,7 @@ void Engine::decode_greedy(const int* first, int n_steps, int* out) {
     TZ_CUDA(cudaEventRecord(ev1, stream));
     TZ_CUDA(cudaMemcpyAsync(out, d_history, (size_t)n_steps * batch * 4, cudaMemcpyDeviceToHost, stream));
     TZ_CUDA(cudaStreamSynchronize(stream));
+    pc_check();
     check_device_status(true);
 }
 
@@ -736,6 +763,107 @@ float Engine::bench_gemv_stack(int iters, unsigned long long* n_launches) {
     launches += per_iter * iters;
     if (n_launches) *n_launches = per_iter * iters;
     return last_ms();
+}
+
+
+// ---- the persistent single-sequence kernel (decode_persistent.cu) ------------------------------------------------------
+// Keys the kernel's attention phase has room for at this bucket (0 when the shapes do not fit it at all).
+int Engine::pc_score_cap(int max_len) {
+    PcSmemPlan pl;
+    if (!pc_plan(h, qd, kvd, ffn, cfg.num_q_heads, cfg.num_kv_heads, V, L, max_len, pc_grid, &pl)) return 0;
+    return pl.score_cap;
+}
+
+bool Engine::pc_usable() {
+    if (!persistent || batch != 1 || paged) return false;
+    if (pc_built) return pc_ok;
+    pc_built = true;
+    pc_ok = false;
+    if (!lm_w) return false;
+    for (const LayerDev& d : layers)
+        if (!d.set || !d.has_mlp) return false;
+    if (!pc_grid) pc_grid = pc_grid_size();
+    PcSmemPlan pl;
+    if (!pc_grid || !pc_plan(h, qd, kvd, ffn, cfg.num_q_heads, cfg.num_kv_heads, V, L, 256 < cfg.max_seq_len ? 256 : cfg.max_seq_len, pc_grid, &pl))
+        return false;
+    if (!pc_layers) {
+        auto dalloc = [&](size_t bytes) -> void* {
+            void* ptr = nullptr;
+            TZ_CUDA(cudaMalloc(&ptr, bytes));
+            owned.push_back(ptr);
+            TZ_CUDA(cudaMemsetAsync(ptr, 0, bytes, stream));
+            return ptr;
+        };
+        pc_layers = (PcLayer*)dalloc((size_t)L * sizeof(PcLayer));
+        pc_acc = (int32_t*)dalloc(pc_acc_ints(h, qd, kvd, ffn) * sizeof(int32_t));
+        pc_bar = (unsigned*)dalloc(256);
+        pc_status = (int*)dalloc(256);
+        pc_best = (LmBest*)dalloc((size_t)pc_grid * sizeof(LmBest));
+        pc_phase_ns = (unsigned long long*)dalloc(72 * sizeof(unsigned long long));
+        TZ_CUDA(cudaHostAlloc((void**)&pc_host, 64, cudaHostAllocMapped));
+        std::memset(pc_host, 0, 64);
+        TZ_CUDA(cudaHostGetDevicePointer((void**)&pc_host_dev, pc_host, 0));
+        pc_bar_base = 0;
+    }
+    std::vector<PcLayer> tab(L);
+    for (int l = 0; l < L; ++l) {
+        const LayerDev& d = layers[l];
+        PcLayer& t = tab[l];
+        t.qkv = d.qkv; t.o = d.o; t.gu = d.gateup; t.down = d.down;
+        t.in_norm = d.in_norm; t.attn_sub_norm = d.attn_sub_norm; t.post_norm = d.post_norm; t.ffn_sub_norm = d.ffn_sub_norm;
+        t.s_q = d.s_q; t.s_k = d.s_k; t.s_v = d.s_v; t.s_o = d.s_o; t.s_gate = d.s_gate; t.s_up = d.s_up; t.s_down = d.s_down;
+    }
+    TZ_CUDA(cudaStreamSynchronize(stream));
+    TZ_CUDA(cudaMemcpy(pc_layers, tab.data(), (size_t)L * sizeof(PcLayer), cudaMemcpyHostToDevice));
+    pc_ok = true;
+    return true;
+}
+
+void Engine::pc_step(bool with_logits, bool feed_back, int max_len) {
+    PcParams p;
+    std::memset(&p, 0, sizeof p);
+    if (!pc_plan(h, qd, kvd, ffn, cfg.num_q_heads, cfg.num_kv_heads, V, L, max_len, pc_grid, &p.plan))
+        throw std::runtime_error("the persistent decode kernel does not fit this context length");
+    p.layers = pc_layers;
+    p.n_layers = L; p.h = h; p.qd = qd; p.kvd = kvd; p.ffn = ffn; p.V = V;
+    p.n_q = cfg.num_q_heads; p.n_kv = cfg.num_kv_heads; p.max_seq = cfg.max_seq_len;
+    p.lm_w = lm_w; p.lm_scales = lm_scales; p.final_norm = final_norm;
+    p.tokens = d_tokens; p.pos = d_pos; p.token_arg = pc_token_arg; p.pos_arg = pc_pos_arg;
+    p.next = d_next; p.host_next = pc_host_dev + 1;
+    p.cache_k = cache_k; p.cache_v = cache_v; p.scale_k = scale_k; p.scale_v = scale_v;
+    p.rope_cos = rope_cos; p.rope_sin = rope_sin;
+    p.acc = pc_acc; p.attn_out = b_attn;
+    p.b_x = b_x; p.b_qkv = b_qkv; p.b_h1 = b_h1; p.b_act = b_act; p.b_logits = b_logits;
+    p.cta_best = pc_best;
+    p.bar_counter = pc_bar; p.bar_base = pc_bar_base;
+    p.status = pc_status; p.host_status = pc_host_dev;
+    p.phase_ns = pc_phase_ns;
+    p.with_logits = with_logits ? 1 : 0;
+    p.feed_back = feed_back ? 1 : 0;
+    p.eps = 1e-5f;
+    TZ_CUDA(pc_launch(p, pc_grid, stream));
+    pc_bar_base += (unsigned)pc_barriers_per_launch(L) * (unsigned)pc_grid;
+    launches += 1;
+}
+
+// The barrier word and the accumulators are only consistent after a launch that ran to its end: start over.
+void Engine::pc_reset_scratch() {
+    if (!pc_layers) return;
+    cudaStreamSynchronize(stream);
+    cudaMemset(pc_bar, 0, 256);
+    cudaMemset(pc_status, 0, 256);
+    cudaMemset(pc_acc, 0, pc_acc_ints(h, qd, kvd, ffn) * sizeof(int32_t));
+    pc_host[0] = 0;
+    pc_bar_base = 0;
+}
+
+void Engine::pc_check() {
+    if (!pc_host || pc_host[0] == 0) return;
+    const int code = pc_host[0];
+    pc_reset_scratch();
+    static const char* what[] = {"", "a grid-wide barrier", "a weight copy", "a value-cache copy", "a position inside its bounds"};
+    throw std::runtime_error(std::string("the persistent decode kernel gave up waiting for ") + (code >= 1 && code <= 4 ? what[code] : "something") +
+                             "; results of that step are invalid");
 }
 
 float Engine::last_ms() {

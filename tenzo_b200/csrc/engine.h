@@ -9,6 +9,7 @@
 
 #include "../../include/tenzo.h"
 #include "../../include/tenzo_ext.h"
+#include "decode_persistent.h"
 
 namespace tz {
 
@@ -118,6 +119,28 @@ public:
     std::map<int, cudaGraphExec_t> graphs;
     std::map<int, unsigned long long> graph_kernels;
     unsigned long long launches = 0;
+
+    // Single-sequence engines: the whole token as one persistent cooperative kernel (decode_persistent.cu) instead of the
+    // kernel chain, whenever the shapes fit it (pc_usable). Its scratch is owned here: zeroed accumulators, the barrier
+    // word (only ever grows; pc_bar_base tracks it), status and result words the host can read without a copy.
+    int persistent = 0;                  // option / TENZO_PERSISTENT (off unless asked for: measured slower than the kernel chain)
+    bool pc_built = false, pc_ok = false;
+    int pc_grid = 0;
+    PcLayer* pc_layers = nullptr;
+    int32_t* pc_acc = nullptr;
+    unsigned* pc_bar = nullptr;
+    unsigned pc_bar_base = 0;
+    int* pc_status = nullptr;
+    int* pc_host = nullptr;              // mapped pinned: [0] status mirror, [1] next token
+    int* pc_host_dev = nullptr;          // the device's view of it
+    LmBest* pc_best = nullptr;
+    unsigned long long* pc_phase_ns = nullptr;
+    int pc_token_arg = -1, pc_pos_arg = -1;
+    int pc_score_cap(int max_len);
+    bool pc_usable();                    // builds the layer table on first use; false = use the kernel chain
+    void pc_step(bool with_logits, bool feed_back, int max_len);
+    void pc_check();                     // after a synchronisation: throws (and re-arms the scratch) if a launch gave up
+    void pc_reset_scratch();
 };
 
 }  // namespace tz

@@ -95,7 +95,13 @@ __device__ __forceinline__ unsigned long long gtime() { unsigned long long t; as
 #define TZ_TRACE_FLUSH do {} while (0)
 #endif
 
-constexpr int kChunks = 8;         // bulk copies (and mbarriers) per row block: compute starts when the first lands
+#ifndef TZ_GEMV_CHUNKS
+#define TZ_GEMV_CHUNKS 1
+#endif
+// Bulk copies (and mbarriers) per row block. One: a bulk copy costs about the same whatever its size (measured: an SM
+// completes roughly one copy per 0.45 us up to 16 KB), so splitting a 40 KB slice into eight pieces to start computing on
+// the first cost more than it gained (decode went 820 -> 865 tok/s with one copy).
+constexpr int kChunks = TZ_GEMV_CHUNKS;
 
 __device__ int g_tl1_timeouts = 0; // set when a bounded mbarrier wait gave up (the result of that launch is invalid)
 

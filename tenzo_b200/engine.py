@@ -24,13 +24,13 @@ def _p(a: np.ndarray | None, ty):
 
 class Engine:
     def __init__(self, config: abi.TenzoConfig | None = None, *, batch: int = 1, rope_theta: float = 10000.0,
-                 use_graph: int = -1, use_pdl: int = -1, **overrides):
+                 use_graph: int = -1, use_pdl: int = -1, persistent: int = -1, **overrides):
         self.lib = load_library()
         cfg = config if config is not None else self.lib.tenzo_default_config()
         for k, v in overrides.items():
             setattr(cfg, k, v)
         self.config = cfg
-        opt = abi.TenzoExtOptions(batch, rope_theta, use_graph, use_pdl)
+        opt = abi.TenzoExtOptions(batch, rope_theta, use_graph, use_pdl, persistent)
         self._h = self.lib.tenzo_ext_create_engine(C.byref(cfg), C.byref(opt))
         if not self._h:
             raise RuntimeError("Failed to initialize Tenzo execution engine: " + self.last_error())
@@ -176,6 +176,17 @@ class Engine:
 
     def last_device_ms(self) -> float:
         return float(self.lib.tenzo_ext_last_device_ms(self._h))
+
+    def persistent_phase_ns(self, reset: bool = True):
+        """Per-phase nanoseconds of the persistent single-sequence kernel since the last reset, or None when the engine
+        runs the per-operator kernel chain."""
+        out = (C.c_ulonglong * 8)()
+        self.lib.tenzo_ext_persistent_phase_ns.restype = C.c_int
+        self.lib.tenzo_ext_persistent_phase_ns.argtypes = [C.c_void_p, C.POINTER(C.c_ulonglong), C.c_int]
+        rc = self.lib.tenzo_ext_persistent_phase_ns(self._h, out, int(reset))
+        if rc < 0:
+            raise RuntimeError("tenzo_ext_persistent_phase_ns failed")
+        return [int(v) for v in out] if rc == 1 else None
 
     def kernel_launches(self) -> int:
         return int(self.lib.tenzo_ext_kernel_launches(self._h))

@@ -85,7 +85,7 @@ def rmsnorm_quant(x: torch.Tensor, norm_w=None, *, do_norm=True, eps=1e-5, qmax=
 
 def attention_int8(q, k, v, cache_k, cache_v, scale_k, scale_v, pos, *, layer, n_q, n_kv, max_seq, rope_cos=None,
                    rope_sin=None, append=True, max_len=None, use_pdl=False, heads_per_cta=0, out=None, tiles=0,
-                   block_table=None, n_layers=0):
+                   block_table=None, n_layers=0, mode=0, split_keys=0, workspace=None):
     """q [batch, n_q*128], k/v [batch, n_kv*128]; caches [batch, layers, n_kv, max_seq, 128] int8 and
     [batch, layers, n_kv, max_seq] fp32; pos int32 [batch]. Returns out [batch, n_q*128].
     With block_table (int32 [batch, blocks per sequence]) the caches are the paged_int8 pools
@@ -109,6 +109,12 @@ def attention_int8(q, k, v, cache_k, cache_v, scale_k, scale_v, pos, *, layer, n
         assert block_table.dtype == torch.int32 and block_table.is_contiguous()
         a.block_table, a.table_stride, a.n_layers = _ptr(block_table), (block_table.stride(0) if block_table.dim() == 2 else 0), n_layers
         a.n_pool_blocks = cache_k.shape[0]
+    if mode == 1:
+        lib.tenzo_cuda_attention_workspace_bytes.restype = C.c_size_t
+        need = lib.tenzo_cuda_attention_workspace_bytes(batch, n_q, n_kv, max_len)
+        if workspace is None:
+            workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
+        a.mode, a.split_keys, a.workspace, a.workspace_bytes = 1, split_keys, _ptr(workspace), workspace.numel()
     _ok(lib.tenzo_cuda_attention_int8(C.byref(a), _stream()), "tenzo_cuda_attention_int8")
     return out
 

@@ -331,3 +331,56 @@ class TensorParallelDecoder:
     def logits_slice(self):
         """This rank's [B, V/R] logits of the last step."""
         return self.logits_loc
+
+
+def parity_check(group=None, use_graph: bool = True, say=None) -> bool:
+    """The tensor-parallel decoder next to the single-GPU engine on one seeded model (the synthetic 8B shape cut to 2 layers
+    and a 16384-row vocabulary; 32 sequences, 3 prompt tokens + 6 greedy steps), on the process group that is already
+    initialised (or a single process). True when, on every rank, the token streams are identical and this rank's slice of
+    the last step's logits equals the engine's bits for the first and the last sequence. Collective: every rank of the
+    group must call it."""
+    import torch
+    import torch.distributed as dist
+    from . import synth
+    from .engine import Engine
+    say = say or (lambda m: None)
+    cfg = dict(synth.SYNTH_8B, num_layers=2, vocab_size=16384, max_seq_len=64)
+    B, prompt_len, steps = 32, 3, 6
+    model = synth.SyntheticModel(cfg, seed=5)
+    prompts = np.stack([synth.prompt_tokens(100 + b, prompt_len, cfg["vocab_size"]) for b in range(B)])     # [B, prompt_len]
+    say("model built")
+    eng = Engine(model.config_struct(), batch=B).load_synthetic(model)
+    for t in range(prompt_len - 1):
+        eng.prefill_tokens(prompts[:, t])
+    want = eng.decode_greedy(prompts[:, -1], steps - 1)                   # [steps - 1, B]
+    last = eng.generate_steps(want[-1])                                   # the last step also leaves its logits behind
+    want = np.concatenate([want, np.asarray(last)[None]])
+    want_logits = np.stack([eng.read_buffer(15, seq=b, count=cfg["vocab_size"]) for b in (0, B - 1)])
+    eng.close()
+    say("single-GPU engine done")
+    dec = TensorParallelDecoder(model, B, cfg["max_seq_len"], group=group, use_graph=use_graph)
+    say("shards loaded")
+    for t in range(prompt_len - 1):
+        dec.step(prompts[:, t])
+        torch.cuda.synchronize()
+    got = []
+    nxt = dec.step(prompts[:, -1])
+    got.append(nxt.cpu().numpy().copy())
+    for _ in range(steps - 1):
+        nxt = dec.step()
+        got.append(nxt.cpu().numpy().copy())
+    got = np.stack(got)
+    say("decode done")
+    v0, vn = dec.p.vocab_rows
+    mine = dec.logits_slice().cpu().numpy()
+    ok = bool(np.array_equal(got, want) and np.array_equal(mine[0], want_logits[0, v0:v0 + vn]) and
+              np.array_equal(mine[B - 1], want_logits[1, v0:v0 + vn]))
+    if not ok:
+        say(f"MISMATCH: tokens equal={np.array_equal(got, want)}, first differing step={np.argwhere(got != want)[:1].tolist()}")
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        flag = torch.tensor([1 if ok else 0], device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+        ok = bool(flag.item())
+    del dec
+    torch.cuda.empty_cache()
+    return ok
