@@ -24,6 +24,11 @@ typedef struct {
                            chain of one kernel per operator; -1 default (0, or the TENZO_PERSISTENT environment variable).
                            Results are bit-identical either way; on B200 the chain is the faster of the two (the barriers and
                            L2 round trips of the one-kernel form cost more than the launches they replace). */
+    int attention_mode; /* 0: attention in the reference's fp32 operation order, bit-identical outputs (default; greedy
+                           streams equal the reference's). 1: tolerance mode for the kernel-chain engine (see
+                           tenzo_attention_args.mode in tenzo_kernels.h): split over the keys, tensor-core products, about
+                           1e-4 relative on the attention output, several times faster at long contexts. -1 default (0, or
+                           the TENZO_ATTENTION_MODE environment variable). Contiguous KV cache only. */
 } tenzo_ext_options_t;
 
 TENZO_API tenzo_ext_options_t tenzo_ext_default_options(void);

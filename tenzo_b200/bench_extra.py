@@ -67,7 +67,9 @@ def run_gemv(args):
     bytes_per = N * K // 4 + 4 * K + 4 * N
     gbs = bytes_per * launches / (ms * 1e-3) / 1e9
     peak = _peak()
+    cpu = None if getattr(args, "no_cpu_baseline", False) else _cpu_gemv_baseline(N, K)
     print(json.dumps({
+        "cpu_baseline": cpu,
         "metric": "tl1_gemv_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup),
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
         "data": "synthetic", "config": {"workload": f"gemv: TL1 bitlinear {N}x{K}, batch 1, {n_mat} distinct matrices per step "
@@ -78,6 +80,41 @@ def run_gemv(args):
                      "--no-prefetch; with the next-matrix L2 prefetch on, ncu's cache flush between replays counts that matrix twice (8.9 MB)",
                      "bytes_per_launch": bytes_per, "us_per_launch": ms * 1e3 / launches},
     }), flush=True)
+
+
+def _cpu_gemv_baseline(N, K):
+    """The reference's build_lut + compute_from_lut (src/runtime/TenzoEngine.cpp:22-146, through oracle/_ref) on the host
+    cores over 32 distinct seeded matrices (more than the host's last-level cache), bounded sample."""
+    import sys
+    import time
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[1]
+    for pth in (str(root), str(root / "tests")):
+        if pth not in sys.path:
+            sys.path.insert(0, pth)
+    import bench
+    from oracle import oracle_py as ora
+    threads = bench.use_host_threads()
+    rng = np.random.default_rng(4)
+    mats = [synth.random_tl1_packed(rng, N, K) for _ in range(32)]
+    x = rng.standard_normal(K).astype(np.float32)
+    out, acc = np.zeros(N, np.float32), np.zeros(N, np.int32)
+    P = ora.ptr
+    kind = "kernels_fast" if ora.ref_available("kernels_fast") else ("kernels" if ora.ref_available("kernels") else None)
+    if kind:
+        L = ora.load_ref(kind)
+        one = lambda w: L.refk_bitlinear_tl1(P(x, ora.c_f32p), P(w.view(np.int8), ora.c_i8p), N, K, 0.016, P(out, ora.c_f32p), P(acc, ora.c_i32p))
+    else:
+        O = ora.load_oracle()
+        one = lambda w: O.ora_bitlinear_tl1(P(x, ora.c_f32p), P(w, ora.c_u8p), N, K, 0.016, P(out, ora.c_f32p), P(acc, ora.c_i32p))
+    one(mats[0])
+    n, t0 = 0, time.perf_counter()
+    while time.perf_counter() - t0 < 3.0:
+        one(mats[n % len(mats)])
+        n += 1
+    dt = time.perf_counter() - t0
+    return {"value": n * (N * K // 4 + 4 * K + 4 * N) / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": "reference" if kind else "port",
+            "sample": f"{n} calls of the reference's TL1 product {N}x{K} cycling over 32 distinct matrices, {dt:.1f} s; {dt / n * 1e6:.0f} us per call"}
 
 
 def _peak_tensor():
@@ -143,19 +180,31 @@ def run_attn(args):
     k = torch.randn(B, nkv * 128, generator=g, device="cuda")
     v = torch.randn(B, nkv * 128, generator=g, device="cuda")
     pos = torch.full((B,), T - 1, dtype=torch.int32, device="cuda")
-    for _ in range(max(3, args.warmup)):
-        kernels.attention_int8(q, k, v, ck, cv, sk, sv, pos, layer=0, n_q=nq, n_kv=nkv, max_seq=T, max_len=T, heads_per_cta=args.heads_per_cta)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    e0.record()
-    for _ in range(args.steps):
-        kernels.attention_int8(q, k, v, ck, cv, sk, sv, pos, layer=0, n_q=nq, n_kv=nkv, max_seq=T, max_len=T, heads_per_cta=args.heads_per_cta)
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / args.steps
+
+    def timed(mode):
+        ws = torch.empty(kernels.attention_workspace_bytes(B, nq, nkv, T), dtype=torch.uint8, device="cuda") if mode == 1 else None
+        run = lambda: kernels.attention_int8(q, k, v, ck, cv, sk, sv, pos, layer=0, n_q=nq, n_kv=nkv, max_seq=T, max_len=T,
+                                             heads_per_cta=args.heads_per_cta, mode=mode, workspace=ws)
+        for _ in range(max(3, args.warmup)):
+            run()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(args.steps):
+            run()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / args.steps
+
     bytes_per = B * nkv * T * (2 * 128 + 8) + B * nq * 128 * 8
-    gbs = bytes_per / (ms * 1e-3) / 1e9
     peak = _peak()
+    ms_fast = timed(1)
+    want = kernels.attention_int8(q, k, v, ck, cv, sk, sv, pos, layer=0, n_q=nq, n_kv=nkv, max_seq=T, max_len=T, append=False)
+    got = kernels.attention_int8(q, k, v, ck, cv, sk, sv, pos, layer=0, n_q=nq, n_kv=nkv, max_seq=T, max_len=T, append=False, mode=1)
+    fast_err = float((got - want).abs().max() / want.abs().max())
+    ms = timed(0)
+    gbs = bytes_per / (ms * 1e-3) / 1e9
+    cpu = _cpu_attention_baseline(nq, nkv, T) if not getattr(args, "no_cpu_baseline", False) else None
     print(json.dumps({
         "metric": "attention_int8_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup),
         "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 x int8", "data": "synthetic",
@@ -166,7 +215,63 @@ def run_attn(args):
                      "frac": gbs / peak[0], "traffic": bytes_per * (265.2 / 259.5),
                      "traffic_source": "ncu at 24 sequences: 260.2 MB read + 5.0 MB written for 259.5 MB algorithmic, scaled by the sequence count",
                      "bytes_per_launch": bytes_per, "us_per_launch": ms * 1e3},
+        "tolerance_mode": {"ms_per_step": ms_fast, "achieved": bytes_per / (ms_fast * 1e-3) / 1e9, "unit": "GB/s",
+                           "frac": bytes_per / (ms_fast * 1e-3) / 1e9 / peak[0], "kernel": "fa_append_kernel + attn_fast_kernel + attn_fast_merge_kernel",
+                           "max_rel_err_vs_exact": fast_err, "tolerance": 1e-3},
+        "cpu_baseline": cpu,
     }), flush=True)
+
+
+def _cpu_attention_baseline(nq, nkv, T):
+    """The reference's own attention (FusedKVCache::forward_attention_raw through oracle/_ref) for ONE sequence at this
+    context on the host cores: sequences per second, bounded sample."""
+    import sys
+    import time
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[1]
+    for pth in (str(root), str(root / "tests")):
+        if pth not in sys.path:
+            sys.path.insert(0, pth)
+    import bench
+    from oracle import oracle_py as ora
+    threads = bench.use_host_threads()
+    kind = "kernels_fast" if ora.ref_available("kernels_fast") else ("kernels" if ora.ref_available("kernels") else None)
+    rng = np.random.default_rng(3)
+    q = rng.standard_normal(nq * 128).astype(np.float32)
+    k = rng.standard_normal(nkv * 128).astype(np.float32)
+    v = rng.standard_normal(nkv * 128).astype(np.float32)
+    out = np.zeros(nq * 128, np.float32)
+    P = ora.ptr
+    if kind:
+        L = ora.load_ref(kind)
+        kv = L.refk_kv_create(1, nq, nkv, 128, T)
+        rows = nkv * T
+        ora.view(L.refk_kv_k(kv), rows * 128, np.int8)[:] = rng.integers(-127, 128, rows * 128, dtype=np.int8)
+        ora.view(L.refk_kv_v(kv), rows * 128, np.int8)[:] = rng.integers(-127, 128, rows * 128, dtype=np.int8)
+        ora.view(L.refk_kv_k_scales(kv), rows, np.float32)[:] = (0.01 + 0.02 * rng.random(rows)).astype(np.float32)
+        ora.view(L.refk_kv_v_scales(kv), rows, np.float32)[:] = (0.01 + 0.02 * rng.random(rows)).astype(np.float32)
+
+        def one():
+            L.refk_kv_set_len(kv, T - 1)
+            L.refk_kv_attention(kv, 0, P(q.copy(), ora.c_f32p), P(k.copy(), ora.c_f32p), P(v.copy(), ora.c_f32p), P(out, ora.c_f32p))
+    else:
+        O = ora.load_oracle()
+        ck, cv = rng.integers(-127, 128, nkv * T * 128, dtype=np.int8), rng.integers(-127, 128, nkv * T * 128, dtype=np.int8)
+        sk, sv = (0.01 + 0.02 * rng.random(nkv * T)).astype(np.float32), (0.01 + 0.02 * rng.random(nkv * T)).astype(np.float32)
+
+        def one():
+            O.ora_attention_int8(0, T - 1, nq, nkv, 128, T, 10000.0, P(q.copy(), ora.c_f32p), P(k.copy(), ora.c_f32p), P(v.copy(), ora.c_f32p),
+                                 P(out, ora.c_f32p), P(ck, ora.c_i8p), P(cv, ora.c_i8p), P(sk, ora.c_f32p), P(sv, ora.c_f32p))
+    one()
+    n, t0 = 0, time.perf_counter()
+    while time.perf_counter() - t0 < 3.0:
+        one()
+        n += 1
+    dt = time.perf_counter() - t0
+    bytes_seq = nkv * T * 264
+    return {"value": n * bytes_seq / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": "reference" if kind else "port",
+            "sample": f"{n} calls of the reference's attention for ONE sequence at context {T} ({bytes_seq / 1e6:.1f} MB of KV each), {dt:.1f} s; "
+                      f"{n / dt:.1f} sequences/s"}
 
 
 def run_decode_batch(args):
@@ -180,9 +285,9 @@ def run_decode_batch(args):
     from .sharding import shard_sequences
     _, B = shard_sequences(args.batch, world, rank)     # sequences are sharded across ranks, no data-path collective
     ctx = args.context
-    cfg = dict(synth.BITNET_2B, max_seq_len=ctx + args.steps + max(3, args.warmup) + 8)
+    cfg = dict(synth.BITNET_2B, max_seq_len=(ctx + args.steps + max(3, args.warmup) + 8 + 3) // 4 * 4)
     model = synth.SyntheticModel(cfg, seed=0)
-    eng = Engine(model.config_struct(kv_mode=args.kv_mode), batch=B).load_synthetic(model)
+    eng = Engine(model.config_struct(kv_mode=args.kv_mode), batch=B, attention_mode=args.attention_mode).load_synthetic(model)
     eng.kv_fill_random(ctx, seed=rank)
     first = synth.prompt_tokens(1000 + rank, B, cfg["vocab_size"])
     warm = eng.decode_greedy(first, max(3, args.warmup))
@@ -203,7 +308,8 @@ def run_decode_batch(args):
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
             "config": {"workload": f"decode_batch: BitNet-2B shape, global batch {args.batch}, context {ctx} (device-filled KV), "
-                                   f"{B} sequences per GPU", "parallelism": f"dp{world}", "kv_mode": args.kv_mode},
+                                   f"{B} sequences per GPU", "parallelism": f"dp{world}", "kv_mode": args.kv_mode,
+                       "attention_mode": args.attention_mode},
             "gpu_launches": int(launches),
         }), flush=True)
     eng.close()

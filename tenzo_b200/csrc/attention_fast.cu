@@ -10,9 +10,10 @@
 //     (max, sum, output) triple per query head - the usual online softmax. Partial triples are merged by log-sum-exp,
 //     first across the warps of a CTA, then across CTAs by a second small kernel.
 //   * Both products run on the tensor cores as fp16 MMAs with fp32 accumulation (mma.sync.m16n8k16). INT8 K and V are
-//     exact in fp16; bytes become halves with one PRMT and one HSUB2 per pair (0x64xx is 1024 + x in fp16). The query is
-//     rounded to fp16 after the rotation and the weights p_t * s_v[t] after the exponential (scaled by 2^10 so that small
-//     weights stay normal numbers): relative errors of 2^-11 per element, far inside the tolerance after the sums.
+//     exact in fp16; bytes become halves with one PRMT and one HSUB2 per pair (0x64xx is 1024 + x in fp16). The rotated
+//     query enters as two fp16 parts (hi + lo, two MMAs per step), the weights p_t * s_v[t] are rounded to fp16 after the
+//     exponential (scaled by 2^10 so that small weights stay normal numbers): a relative error of 2^-11 per weight that
+//     averages out over the keys.
 //   * Q.K^T: A = the query heads of the kv head (rows 0..G-1 of 16), B = keys straight from the swizzled tile (a lane's
 //     32-bit word is two k-pairs; the k order inside a 16-wide step is permuted identically in A). P.V: the score
 //     accumulators are already in A-fragment layout; B comes from ldmatrix.trans over the INT8 tile read as 16-bit
@@ -177,14 +178,20 @@ __global__ void __launch_bounds__(kFaThreads, 2) attn_fast_kernel(const FaLaunch
         }
     }
     __syncthreads();
-    uint32_t qa[8][2];
+    // q = hi + lo with both parts in fp16: the product with the (exact) keys is then accurate to about 2^-22 of |q||k|,
+    // where a single rounding of q to fp16 (2^-11) would put most of the tolerance budget into the scores
+    uint32_t qa[8][2], ql[8][2];
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks) {
-        qa[ks][0] = qa[ks][1] = 0u;
+        qa[ks][0] = qa[ks][1] = ql[ks][0] = ql[ks][1] = 0u;
         if (g < G) {
             const float4 v = *reinterpret_cast<const float4*>(s_q + g * kHd + ks * 16 + t4 * 4);
             qa[ks][0] = fa_pack_h2(v.x, v.y);        // k = 2*t4, 2*t4+1      <-> dims 16ks + 4t4 + {0,1}
             qa[ks][1] = fa_pack_h2(v.z, v.w);        // k = 2*t4+8, 2*t4+9    <-> dims 16ks + 4t4 + {2,3}
+            const float2 h0 = __half22float2(*reinterpret_cast<const __half2*>(&qa[ks][0]));
+            const float2 h1 = __half22float2(*reinterpret_cast<const __half2*>(&qa[ks][1]));
+            ql[ks][0] = fa_pack_h2(v.x - h0.x, v.y - h0.y);
+            ql[ks][1] = fa_pack_h2(v.z - h1.x, v.w - h1.y);
         }
     }
 
@@ -219,7 +226,9 @@ __global__ void __launch_bounds__(kFaThreads, 2) attn_fast_kernel(const FaLaunch
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks) {
                 const uint32_t w = *reinterpret_cast<const uint32_t*>(krow + ((ks ^ g) << 4)) ^ 0x80808080u;
-                fa_mma_f16(s[nt], qa[ks][0], 0u, qa[ks][1], 0u, fa_bytes_to_h2(w, 0x5140u), fa_bytes_to_h2(w, 0x7362u));
+                const uint32_t b0 = fa_bytes_to_h2(w, 0x5140u), b1 = fa_bytes_to_h2(w, 0x7362u);
+                fa_mma_f16(s[nt], qa[ks][0], 0u, qa[ks][1], 0u, b0, b1);
+                fa_mma_f16(s[nt], ql[ks][0], 0u, ql[ks][1], 0u, b0, b1);
             }
         }
         // ---- online softmax for row g; this lane holds keys 8nt + 2t4 + {0,1} --------------------------------------

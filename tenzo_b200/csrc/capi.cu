@@ -84,6 +84,7 @@ tenzo_ext_options_t tenzo_ext_default_options(void) {
     o.use_graph = -1;
     o.use_pdl = -1;
     o.persistent = -1;
+    o.attention_mode = -1;
     return o;
 }
 

@@ -163,6 +163,8 @@ void Engine::init(const tenzo_config_t& c, const tenzo_ext_options_t& o) {
     use_graph = o.use_graph >= 0 ? o.use_graph : env_flag("TENZO_CUDA_GRAPH", 1);
     use_pdl = o.use_pdl >= 0 ? o.use_pdl : env_flag("TENZO_CUDA_PDL", 1);
     persistent = o.persistent >= 0 ? o.persistent : env_flag("TENZO_PERSISTENT", 0);
+    attention_mode = o.attention_mode >= 0 ? o.attention_mode : env_flag("TENZO_ATTENTION_MODE", 0);
+    if (attention_mode != 0 && attention_mode != 1) throw std::invalid_argument("attention_mode must be 0 or 1");
     paged = c.kv_mode && std::strcmp(c.kv_mode, "paged_int8") == 0;       // TenzoEngine.cpp:1220
     cfg.kv_mode = paged ? "paged_int8" : "int8_fused";
     cfg.device = "cuda";
@@ -237,6 +239,13 @@ void Engine::init(const tenzo_config_t& c, const tenzo_ext_options_t& o) {
 
     lm_scratch = dalloc(tenzo_cuda_lm_head_scratch_bytes(batch));
     gemv_ws = dalloc(tenzo_cuda_tl1_gemv_workspace_bytes(batch, h > ffn ? h : ffn));
+    if (attention_mode == 1) {
+        if (paged) throw std::invalid_argument("attention_mode 1 needs the contiguous KV cache (kv_mode int8_fused)");
+        if (cfg.max_seq_len % 4) throw std::invalid_argument("attention_mode 1 needs max_seq_len to be a multiple of 4 (16-byte rows of scales)");
+        attn_ws_bytes = tenzo_cuda_attention_workspace_bytes(batch, cfg.num_q_heads, cfg.num_kv_heads, cfg.max_seq_len);
+        attn_ws = dalloc(attn_ws_bytes);
+        persistent = 0;                                   // the one-kernel form has only the exact-order attention
+    }
 
     TZ_CUDA(cudaMallocHost(&h_pin, (3 * B + 16) * sizeof(int)));
     h_tokens = h_pin;
@@ -434,9 +443,10 @@ void Engine::enqueue_layer(int l, int max_len, bool gemv_only) {
     a.use_pdl = use_pdl;
     a.q_stride = a.kv_stride = qd + 2 * kvd;
     if (paged) { a.block_table = d_table; a.table_stride = table_stride; a.n_layers = L; a.n_pool_blocks = total_blocks; }
+    a.mode = attention_mode; a.workspace = attn_ws; a.workspace_bytes = attn_ws_bytes;
     if (!gemv_only) {
         TZ_KERNEL(tenzo_cuda_attention_int8(&a, stream));
-        launches += 1;
+        launches += attention_mode == 1 ? 3 : 1;          // tolerance mode: append, split kernel, merge
     }
 
     // out projection + residual

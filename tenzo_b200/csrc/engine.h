@@ -107,6 +107,9 @@ public:
     size_t kv_rows_per_seq = 0;
     float *rope_cos = nullptr, *rope_sin = nullptr;
     void *lm_scratch = nullptr, *gemv_ws = nullptr;
+    int attention_mode = 0;              // 1: tolerance-mode attention (attention_fast.cu) in the kernel chain
+    void* attn_ws = nullptr;
+    size_t attn_ws_bytes = 0;
     float *pf_x = nullptr, *pf_qkv = nullptr, *pf_attn = nullptr, *pf_h1 = nullptr, *pf_act = nullptr;   // chunked prefill rows
     int *pf_tokens = nullptr, *pf_pos = nullptr, pf_cap = 0;
     void* pf_ws = nullptr;

@@ -24,13 +24,13 @@ def _p(a: np.ndarray | None, ty):
 
 class Engine:
     def __init__(self, config: abi.TenzoConfig | None = None, *, batch: int = 1, rope_theta: float = 10000.0,
-                 use_graph: int = -1, use_pdl: int = -1, persistent: int = -1, **overrides):
+                 use_graph: int = -1, use_pdl: int = -1, persistent: int = -1, attention_mode: int = -1, **overrides):
         self.lib = load_library()
         cfg = config if config is not None else self.lib.tenzo_default_config()
         for k, v in overrides.items():
             setattr(cfg, k, v)
         self.config = cfg
-        opt = abi.TenzoExtOptions(batch, rope_theta, use_graph, use_pdl, persistent)
+        opt = abi.TenzoExtOptions(batch, rope_theta, use_graph, use_pdl, persistent, attention_mode)
         self._h = self.lib.tenzo_ext_create_engine(C.byref(cfg), C.byref(opt))
         if not self._h:
             raise RuntimeError("Failed to initialize Tenzo execution engine: " + self.last_error())

@@ -83,6 +83,13 @@ def rmsnorm_quant(x: torch.Tensor, norm_w=None, *, do_norm=True, eps=1e-5, qmax=
     return y, q, s
 
 
+def attention_workspace_bytes(batch, n_q, n_kv, max_len) -> int:
+    lib = load_library()
+    lib.tenzo_cuda_attention_workspace_bytes.restype = C.c_size_t
+    lib.tenzo_cuda_attention_workspace_bytes.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int]
+    return int(lib.tenzo_cuda_attention_workspace_bytes(batch, n_q, n_kv, max_len))
+
+
 def attention_int8(q, k, v, cache_k, cache_v, scale_k, scale_v, pos, *, layer, n_q, n_kv, max_seq, rope_cos=None,
                    rope_sin=None, append=True, max_len=None, use_pdl=False, heads_per_cta=0, out=None, tiles=0,
                    block_table=None, n_layers=0, mode=0, split_keys=0, workspace=None):
@@ -110,10 +117,8 @@ def attention_int8(q, k, v, cache_k, cache_v, scale_k, scale_v, pos, *, layer, n
         a.block_table, a.table_stride, a.n_layers = _ptr(block_table), (block_table.stride(0) if block_table.dim() == 2 else 0), n_layers
         a.n_pool_blocks = cache_k.shape[0]
     if mode == 1:
-        lib.tenzo_cuda_attention_workspace_bytes.restype = C.c_size_t
-        need = lib.tenzo_cuda_attention_workspace_bytes(batch, n_q, n_kv, max_len)
         if workspace is None:
-            workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
+            workspace = torch.empty(attention_workspace_bytes(batch, n_q, n_kv, max_len), dtype=torch.uint8, device=q.device)
         a.mode, a.split_keys, a.workspace, a.workspace_bytes = 1, split_keys, _ptr(workspace), workspace.numel()
     _ok(lib.tenzo_cuda_attention_int8(C.byref(a), _stream()), "tenzo_cuda_attention_int8")
     return out
