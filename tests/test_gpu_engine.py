@@ -271,7 +271,7 @@ def test_backend_class_host_pointer_calls(cuda_lib):
     nw = (1 + 0.1 * rng.standard_normal(K)).astype(np.float32)
     y = np.zeros(K, np.float32)
     assert lib.tenzo_hal_rmsnorm_host(x.ctypes.data_as(abi.c_f32p), nw.ctypes.data_as(abi.c_f32p), y.ctypes.data_as(abi.c_f32p), K, 1e-5) == 1
-    assert rel_err(y, cpu_rms_norm(x, nw)) < 1e-6
+    assert np.array_equal(y, cpu_rms_norm(x, nw)), "the backend class's RMSNorm is the engine's kernel: same bits as the CPU's"
     A, Bm = rng.standard_normal((5, 70)).astype(np.float32), rng.standard_normal((70, 33)).astype(np.float32)
     Cm = np.zeros((5, 33), np.float32)
     assert lib.tenzo_hal_gemm_f32_host(A.ctypes.data_as(abi.c_f32p), Bm.ctypes.data_as(abi.c_f32p), Cm.ctypes.data_as(abi.c_f32p), 5, 70, 33) == 1
@@ -342,3 +342,37 @@ def test_chunked_prefill_equals_token_by_token(cuda_lib):
                 for got, ref_part in zip(e.kv_export(0, l, 300), kv_ref[l]):
                     assert np.array_equal(got, ref_part), f"layer {l}, chunks {chunks}"
             assert np.array_equal(e.decode_greedy([int(prompt[-1])], 12)[:, 0], want), f"chunks {chunks}"
+
+
+def test_stochastic_streams_equal_the_reference_on_the_same_rand_sequence(cuda_lib):
+    """The reference draws from libc's process-global rand() (TenzoEngine.cpp:1800) and so does this library: seed it,
+    run 64 sampled steps (temperature, top-k, top-p, repetition penalty over the running history) on the compiled
+    reference, seed it again, run the same on the GPU engine - the logits are bit-identical, so the streams must be."""
+    if not ora.ref_available("kernels"):
+        pytest.skip("needs the compiled reference (oracle/_ref)")
+    from helpers import RefEngine
+    from tenzo_b200 import abi
+    libc = C.CDLL("libc.so.6")
+    m = synth.SyntheticModel(synth.TINY, seed=3)
+    prompt = synth.prompt_tokens(11, 9, synth.TINY["vocab_size"])
+    for temperature, top_p, top_k, rep in ((0.7, 0.9, 40, 1.15), (1.3, 1.0, 64, 1.0), (0.4, 0.5, 5, 1.3)):
+        ref = RefEngine(m)
+        for t in prompt[:-1]:
+            ref.prefill(int(t))
+        libc.srand(1234)
+        cur, want, hist = int(prompt[-1]), [], [int(t) for t in prompt]
+        for _ in range(64):
+            cur = ref.generate(cur, temperature=temperature, top_p=top_p, top_k=top_k, rep=rep, past=hist)
+            want.append(cur)
+            hist.append(cur)
+        ref.close()
+        with gpu_engine(m) as e:
+            for t in prompt[:-1]:
+                e.prefill_token(int(t))
+            libc.srand(1234)
+            cur, got, hist = int(prompt[-1]), [], [int(t) for t in prompt]
+            for _ in range(64):
+                cur = e.generate_step(cur, abi.TenzoSampling(temperature, top_p, top_k, rep), past_tokens=hist)
+                got.append(cur)
+                hist.append(cur)
+        assert got == want, (temperature, top_p, top_k, rep, int(np.argmax(np.asarray(got) != np.asarray(want))))

@@ -37,3 +37,26 @@ def test_first_maximum_and_top_k_membership():
     # heap minimum already equals it and is not strictly greater - and lists the larger pair first
     assert sample(L, logits, None, abi.TenzoSampling(1.0, 1.0, 2, 1.0), 0.0) == 3
     assert sample(L, logits, None, abi.TenzoSampling(1.0, 1.0, 2, 1.0), 1.0) == 1
+
+
+def test_host_sampler_equals_the_oracle_sampler_on_the_same_draw():
+    """tenzo_ext_sample_pairs against the C restatement of the reference's sampler (TenzoEngine.cpp:1757-1806; itself pinned
+    to the compiled reference in test_oracle_vs_reference.py) on 300 random logit vectors - ties, every top-k and top-p
+    regime - with the uniform draw passed in, including a NaN logit in the greedy branch."""
+    from oracle import oracle_py as ora
+    L, O = load_library(), ora.load_oracle()
+    rng = np.random.default_rng(23)
+    for trial in range(300):
+        V = int(rng.integers(70, 4000))
+        if trial % 3 == 0:
+            logits = (rng.integers(-40, 40, V) * np.float32(0.25)).astype(np.float32)        # many ties
+        else:
+            logits = (rng.standard_normal(V) * 3).astype(np.float32)
+        p = abi.TenzoSampling(float(rng.choice([0.0, 0.3, 0.7, 1.5])), float(rng.choice([0.3, 0.9, 1.0])), int(rng.integers(1, 80)), 1.0)
+        for r in (0.0, float(rng.random()), 0.999, 1.0):
+            want = O.ora_sample(ora.ptr(logits.copy(), ora.c_f32p), V, p.temperature, p.top_p, p.top_k, 1.0, None, 0, r)
+            assert sample(L, logits, None, p, r) == want, (trial, V, p.temperature, p.top_p, p.top_k, r)
+    greedy = abi.TenzoSampling(0.0, 0.9, 40, 1.0)
+    for logits in (np.array([np.nan, 1.0, 2.0], np.float32), np.array([1.0, np.nan, 2.0, 2.0], np.float32), np.full(5, np.nan, np.float32)):
+        want = O.ora_sample(ora.ptr(logits.copy(), ora.c_f32p), len(logits), 0.0, 0.9, 40, 1.0, None, 0, 0.5)
+        assert sample(L, logits, None, greedy, 0.5) == want
