@@ -57,4 +57,14 @@ private:
 
 }  // namespace tenzo
 
+// Flat C handles on the class, for callers without a C++ toolchain (ctypes, cgo, ...): 1 = done, 0 = nothing was done.
+extern "C" {
+__attribute__((visibility("default"))) int tenzo_hal_initialize(void);
+__attribute__((visibility("default"))) int tenzo_hal_bitlinear_tl1_host(const float* act, const uint8_t* w, float* out, size_t M, size_t K, size_t N, float scale);
+__attribute__((visibility("default"))) int tenzo_hal_rmsnorm_host(const float* in, const float* w, float* out, size_t dim, float eps);
+__attribute__((visibility("default"))) int tenzo_hal_gemm_f32_host(const float* A, const float* B, float* C, size_t M, size_t K, size_t N);
+// execute* calls of the class that have reached the device so far in this process
+__attribute__((visibility("default"))) unsigned long long tenzo_hal_call_count(void);
+}
+
 #endif  // TENZO_CUDA_RUNTIME_H

@@ -122,17 +122,18 @@ def ref_available(kind: str = "kernels") -> bool:
 
 
 _REF_FILES = {"kernels": "libtenzo_ref_kernels.so", "fast": "libtenzo_ref_fast.so", "plain": "libtenzo_ref.so",
-              "kernels_fast": "libtenzo_ref_kernels_fast.so"}
+              "kernels_fast": "libtenzo_ref_kernels_fast.so", "cuda": "libtenzo_ref_cuda.so"}
 _refs: dict[str, C.CDLL] = {}
 
 
 def load_ref(kind: str = "kernels"):
     """Load a compiled-reference library: 'kernels' (parity + trampolines), 'plain', 'fast' (the reference's default
-    flags, for timing) or 'kernels_fast' (trampolines, default flags)."""
+    flags, for timing), 'kernels_fast' (trampolines, default flags) or 'cuda' (the reference engine compiled against this
+    repository's CUDARuntime.h and linked to libtenzo_runtime.so: its device = "cuda" path runs on the GPU)."""
     if kind in _refs:
         return _refs[kind]
     L = declare_tenzo_abi(C.CDLL(str(HERE / "_ref" / _REF_FILES[kind]), mode=os.RTLD_LOCAL))
-    if kind in ("kernels", "kernels_fast"):
+    if kind in ("kernels", "kernels_fast", "cuda"):
         vp, i32, i64, f32 = C.c_void_p, C.c_int, C.c_int64, C.c_float
         sig = {
             "refk_build_lut": (f32, [c_f32p, i64, c_u8p]),

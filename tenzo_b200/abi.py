@@ -89,7 +89,7 @@ KERNEL_SYMBOLS = [
     "tenzo_cuda_lm_head_static_max_batch", "tenzo_cuda_lm_head_take_timeouts", "tenzo_cuda_repetition_penalty",
     "tenzo_cuda_topk_candidates", "tenzo_cuda_topk_max_candidates",
 ]
-HAL_SYMBOLS = ["tenzo_hal_initialize", "tenzo_hal_bitlinear_tl1_host", "tenzo_hal_rmsnorm_host", "tenzo_hal_gemm_f32_host"]
+HAL_SYMBOLS = ["tenzo_hal_initialize", "tenzo_hal_bitlinear_tl1_host", "tenzo_hal_rmsnorm_host", "tenzo_hal_gemm_f32_host", "tenzo_hal_call_count"]
 
 
 def declare_tenzo_abi(L):
@@ -177,4 +177,5 @@ def declare_kernel_abi(L):
     L.tenzo_hal_bitlinear_tl1_host.argtypes = [c_f32p, c_u8p, c_f32p, sz, sz, sz, f32]
     L.tenzo_hal_rmsnorm_host.restype, L.tenzo_hal_rmsnorm_host.argtypes = i32, [c_f32p, c_f32p, c_f32p, sz, f32]
     L.tenzo_hal_gemm_f32_host.restype, L.tenzo_hal_gemm_f32_host.argtypes = i32, [c_f32p, c_f32p, c_f32p, sz, sz, sz]
+    L.tenzo_hal_call_count.restype, L.tenzo_hal_call_count.argtypes = C.c_ulonglong, []
     return L

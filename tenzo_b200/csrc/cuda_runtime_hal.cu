@@ -75,9 +75,12 @@ bool CUDARuntime::ensure(size_t act_bytes, size_t w_bytes, size_t out_bytes) {
     return grow(d_act_, act_cap_, act_bytes) && grow(d_w_, w_cap_, w_bytes) && grow(d_out_, out_cap_, out_bytes);
 }
 
+static unsigned long long g_hal_calls = 0;   // execute* calls that reached the device (see tenzo_hal_call_count)
+
 bool CUDARuntime::executeBitLinearTL1(const float* act, const uint8_t* weight, float* out,
                                       size_t M, size_t K, size_t N, float scale) {
     if (!initialized_ && !initialize()) return false;
+    ++g_hal_calls;
     if (!act || !weight || !out || M == 0 || K == 0 || N == 0 || (K & 1) || (N % 64) || K > 16384) return false;
     cudaStream_t st = static_cast<cudaStream_t>(stream_);
     const size_t wb = N * K / 4, nb = N / 64;
@@ -100,6 +103,7 @@ bool CUDARuntime::executeBitLinearTL1(const float* act, const uint8_t* weight, f
 
 bool CUDARuntime::executeRMSNorm(const float* in, const float* weight, float* out, size_t dim, float eps) {
     if (!initialized_ && !initialize()) return false;
+    ++g_hal_calls;
     if (!in || !out || dim == 0 || dim > 16384) return false;
     cudaStream_t st = static_cast<cudaStream_t>(stream_);
     if (!ensure(dim * 4, dim * 4, dim * 4)) return false;
@@ -139,6 +143,9 @@ __attribute__((visibility("default"))) int tenzo_hal_bitlinear_tl1_host(const fl
 __attribute__((visibility("default"))) int tenzo_hal_rmsnorm_host(const float* in, const float* w, float* out, size_t dim, float eps) {
     return tenzo::CUDARuntime::getInstance().executeRMSNorm(in, w, out, dim, eps) ? 1 : 0;
 }
+// How many execute* calls of the backend class have run so far in this process: lets a host that links an engine against the
+// class check that its device path really went through it.
+__attribute__((visibility("default"))) unsigned long long tenzo_hal_call_count(void) { return tenzo::g_hal_calls; }
 __attribute__((visibility("default"))) int tenzo_hal_gemm_f32_host(const float* A, const float* B, float* C, size_t M, size_t K, size_t N) {
     return tenzo::CUDARuntime::getInstance().executeGemmF32(A, B, C, M, K, N) ? 1 : 0;
 }

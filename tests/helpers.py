@@ -19,10 +19,12 @@ from tenzo_b200 import abi, synth  # noqa: E402
 class RefEngine:
     """The unmodified reference engine (compiled by oracle/Makefile) loaded with a SyntheticModel."""
 
-    def __init__(self, model: synth.SyntheticModel, max_seq_len: int | None = None, kind: str = "kernels", kv_mode: str = "int8_fused"):
+    def __init__(self, model: synth.SyntheticModel, max_seq_len: int | None = None, kind: str = "kernels", kv_mode: str = "int8_fused",
+                 device: bytes = b"cpu"):
         self.L = ora.load_ref(kind)
         self.model = model
         self.cfg = model.config_struct(kv_mode=kv_mode, **({"max_seq_len": max_seq_len} if max_seq_len else {}))
+        self.cfg.device = device
         self.h = self.L.tenzo_create_engine(C.byref(self.cfg))
         assert self.h
         self._keep = []
