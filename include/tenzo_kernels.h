@@ -82,6 +82,11 @@ TENZO_API size_t tenzo_cuda_tl1_gemv_workspace_bytes(int batch, int K);
  * since the last call gave up waiting — its output is then invalid; 0 otherwise; -1 if the query failed.
  * Synchronises with the device. */
 TENZO_API int tenzo_cuda_tl1_gemv_take_timeouts(void);
+/* Test aid: launches a tiny kernel whose wait on a copy that is never issued runs out (after 2^8 polls), so that the flag
+ * above is raised exactly as a real give-up raises it, without any fault or hang (the kernel finishes normally). Lets a
+ * host exercise its own handling of the failure: the next tenzo_cuda_tl1_gemv_take_timeouts() returns 1, and an engine
+ * call that checks the flags fails with its documented status. */
+TENZO_API int tenzo_cuda_selftest_wait_expiry(void* stream);
 
 /* ---- standalone fused RMSNorm + per-token absmax quantiser ------------------------------------
  * Replaces rms_norm_raw (:148-166) followed by the quantiser half of build_lut (:27-42,

@@ -83,7 +83,7 @@ EXT_SYMBOLS = [
     "tenzo_ext_persistent_phase_ns",
 ]
 KERNEL_SYMBOLS = [
-    "tenzo_cuda_tl1_gemv", "tenzo_cuda_tl1_gemv_ksplit", "tenzo_cuda_tl1_gemm_ksplit", "tenzo_cuda_tl1_gemv_workspace_bytes", "tenzo_cuda_tl1_gemv_take_timeouts", "tenzo_cuda_rmsnorm_quant", "tenzo_cuda_attention_int8",
+    "tenzo_cuda_tl1_gemv", "tenzo_cuda_tl1_gemv_ksplit", "tenzo_cuda_tl1_gemm_ksplit", "tenzo_cuda_tl1_gemv_workspace_bytes", "tenzo_cuda_tl1_gemv_take_timeouts", "tenzo_cuda_selftest_wait_expiry", "tenzo_cuda_rmsnorm_quant", "tenzo_cuda_attention_int8",
     "tenzo_cuda_attention_heads_per_cta", "tenzo_cuda_attention_take_timeouts", "tenzo_cuda_attention_workspace_bytes", "tenzo_cuda_lm_head_i8", "tenzo_cuda_lm_head_scratch_bytes",
     "tenzo_cuda_embedding_i8", "tenzo_cuda_tl1_pack_rows2bit", "tenzo_cuda_lm_head_i8_static",
     "tenzo_cuda_lm_head_static_max_batch", "tenzo_cuda_lm_head_take_timeouts", "tenzo_cuda_repetition_penalty",

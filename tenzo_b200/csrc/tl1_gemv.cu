@@ -453,6 +453,40 @@ extern "C" int tenzo_cuda_tl1_gemv_ksplit(int n_blocks, int K, int epilogue) {
     return tz::pick_ksplit(n_blocks, K, epilogue, 1);
 }
 
+namespace tz {
+// Self-test of the give-up path of the bounded waits: barrier A is told to expect 32 bytes that nobody sends, so the wait
+// on it (a short one: 2^8 polls) runs out, the kernel raises the same flag a real give-up raises and carries on; barrier
+// B tracks the one 16-byte copy the kernel does issue and is waited for before the CTA's shared memory goes away. Nothing
+// here can fault or hang: both waits are bounded, and the only memory touched is the kernel's own.
+__global__ void __launch_bounds__(32) wait_expiry_selftest_kernel(const unsigned char* src16) {
+    __shared__ __align__(16) unsigned char s_dst[16];
+    __shared__ uint64_t s_bar[2];
+    if (threadIdx.x == 0) {
+        mbar_init(&s_bar[0], 1);
+        mbar_init(&s_bar[1], 1);
+        mbar_init_fence();
+        mbar_expect_tx(&s_bar[0], 32);
+        mbar_expect_tx(&s_bar[1], 16);
+        bulk_g2s(s_dst, src16, 16, &s_bar[1]);
+        bool done = false;
+        for (int it = 0; it < (1 << 8) && !done; ++it) done = mbar_test(&s_bar[0], 0);
+        if (!done) atomicExch(&g_tl1_timeouts, 1);
+        mbar_wait_bounded(&s_bar[1], 0);
+    }
+}
+}  // namespace tz
+
+extern "C" int tenzo_cuda_selftest_wait_expiry(void* stream) {
+    static unsigned char* src = nullptr;
+    if (!src) {
+        if (cudaMalloc((void**)&src, 256) != cudaSuccess) return (int)cudaErrorMemoryAllocation;
+        cudaMemset(src, 0, 256);
+    }
+    tz::wait_expiry_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(src);
+    const cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : (int)e;
+}
+
 extern "C" int tenzo_cuda_tl1_gemv_take_timeouts(void) {
     int v = 0, zero = 0;
     if (cudaMemcpyFromSymbol(&v, tz::g_tl1_timeouts, sizeof v) != cudaSuccess) return -1;
