@@ -14,6 +14,7 @@
 //   tl1_gemv  post_norm + quant + [gate|up] rows, relu(g)^2*u           [:1594-1620]
 //   tl1_gemv  ffn_sub_norm + quant + down rows, x = h1 + .              [:1622-1628]
 #include <cuda_runtime.h>
+#include <nvtx3/nvToolsExt.h>
 
 #include <cmath>
 #include <cstdio>
@@ -145,6 +146,15 @@ static int env_flag(const char* name, int dflt) {
     const char* s = std::getenv(name);
     return s ? std::atoi(s) : dflt;
 }
+
+// Named ranges around the engine's public operations for timeline tools (the reference marks nothing; its only
+// instrumentation is the wall-clock tok/s of its CLI). Off unless TENZO_NVTX=1: a range push is a call into the tools
+// interface on every token.
+struct NvtxRange {
+    bool on;
+    explicit NvtxRange(const char* name) : on(env_flag("TENZO_NVTX", 0) != 0) { if (on) nvtxRangePushA(name); }
+    ~NvtxRange() { if (on) nvtxRangePop(); }
+};
 
 // A constructor that throws never runs the destructor, so what it had acquired by then (stream, events, device and
 // pinned memory) is released here before the exception leaves.
@@ -501,6 +511,7 @@ static int bucket_for(int len, int max_seq);
 // keys 0..pos0+i). Row i of every product is the same arithmetic as feeding token i alone, so the cache and the state
 // after the chunk are bit-identical to M calls of prefill().
 void Engine::prefill_chunk(const int* tokens, int M) {
+    NvtxRange range("tenzo.prefill_chunk");
     if (batch != 1) throw std::invalid_argument("chunked prefill is for single-sequence engines");
     if (M <= 0) return;
     if (!lm_w) throw std::runtime_error("LM head / embedding was never set");
@@ -667,6 +678,7 @@ void Engine::check_device_status(bool force) {
 }
 
 void Engine::prefill(const int* tokens) {
+    NvtxRange range("tenzo.prefill_token");
     push_state(tokens);
     TZ_CUDA(cudaEventRecord(ev0, stream));
     run_step(false, false);
@@ -676,6 +688,7 @@ void Engine::prefill(const int* tokens) {
 }
 
 void Engine::generate(const int* cur, int* out) {
+    NvtxRange range("tenzo.generate_step");
     if (pc_usable() && seq_len[0] + 1 <= pc_score_cap(bucket_for(seq_len[0] + 1, cfg.max_seq_len))) {
         // persistent kernel: token and position travel as kernel arguments, the result comes back through a mapped
         // host word - no copies in either direction
@@ -707,6 +720,7 @@ void Engine::generate(const int* cur, int* out) {
 }
 
 void Engine::decode_greedy(const int* first, int n_steps, int* out) {
+    NvtxRange range("tenzo.decode_greedy");
     if (n_steps <= 0) return;
     if ((size_t)n_steps * batch > history_cap) {
         if (d_history) cudaFree(d_history);

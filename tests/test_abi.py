@@ -2,6 +2,7 @@
 headers declare, struct layouts match the reference's tenzo.h, and the entry points that need no
 device behave as the reference's do (TenzoEngine.cpp:2088-2114, null-handle branches :2129-2200)."""
 import ctypes as C
+import os
 import re
 from pathlib import Path
 
@@ -58,7 +59,7 @@ def test_c_header_layout_agrees_with_ctypes(tmp_path):
                    'sizeof(tenzo_config_t),offsetof(tenzo_config_t,kv_mode),sizeof(tenzo_sampling_params_t),'
                    'sizeof(tenzo_layer_weights_t),offsetof(tenzo_layer_weights_t,down_scale),offsetof(tenzo_layer_weights_t,in_norm));return 0;}')
     outs = []
-    for inc in (ROOT / "include", Path("/root/reference/include")):
+    for inc in (ROOT / "include", Path(os.environ.get("TENZO_REFERENCE", ROOT.parent / "reference")) / "include"):
         if not (inc / "tenzo.h").exists():
             continue
         exe = tmp_path / ("p_" + inc.parent.name)

@@ -15,7 +15,7 @@ from pathlib import Path
 import pytest
 
 ROOT = Path(__file__).resolve().parents[1]
-REF = Path(os.environ.get("TENZO_REFERENCE", "/root/reference"))
+REF = Path(os.environ.get("TENZO_REFERENCE", ROOT.parent / "reference"))
 
 
 @pytest.fixture(scope="module")
