@@ -1,26 +1,37 @@
-// Batched TL1 bitlinear on the 5th-generation tensor cores (tcgen05.mma kind::i8, accumulators in
-// tensor memory) for sm_100a. Used by tenzo_cuda_tl1_gemv when there are at least 16 sequences.
+// Batched TL1 bitlinear on the 5th-generation tensor cores (tcgen05.mma kind::i8, accumulators AND the weight
+// operand in tensor memory) for sm_100a. Used by tenzo_cuda_tl1_gemv when there are at least 16 sequences.
 //
 // Replaces, for many sequences at once, the same reference code as tl1_gemv.cu
 // (src/runtime/TenzoEngine.cpp:22-166 and the call shapes :1547-1628 of the reference): integer
 // accumulators are exact, so the result is bit-identical to the one-sequence path.
 //
-//   D[128 weight rows][N sequences] (int32, TMEM) += A[128][K] (u8 codes 0,1,2) * B[K][N] (s8 activations)
+//   D[128 weight rows][N sequences] (int32, TMEM) += A[128][K] (u8 codes 0,1,2, TMEM) * B[K][N] (s8 activations, smem)
 //   sum_k w*a = sum_k code*a - sum_k a          (w = code - 1; the per-sequence sum comes from the quantiser)
 //
-// One CTA per 128-row tile (two 64-row TL1 blocks; for the GLU epilogue the gate block and its up
-// block, so the activation is applied inside the CTA). K is walked in 128-byte chunks; per chunk
-//   warp 0 (one lane)   bulk-copies the packed 2-bit weights eight chunks at a time (2 x 16 KB; issuing a copy
-//                       costs a few hundred cycles, so few large ones) into a two-group ring (64 KB in flight
-//                       per CTA covers HBM latency) and TMA-loads the activation tile
-//                       [N][128 B] into a 3- or 4-stage ring with the 128-byte swizzle the tensor core expects;
-//   warps 2-5 / 6-9     (alternate chunks) expand the 2-bit codes to bytes and write the A tile [128][128 B] in the same
-//                       swizzled K-major layout (a 4x4 byte transpose per 4 column pairs with PRMT, then
-//                       mask/shift/interleave), fence it to the async proxy and arrive;
-//   warp 1 (one lane)   issues four tcgen05.mma (K = 32 each) and commits them to the stage's "empty"
-//                       barrier, which is what lets the producer refill the stage.
-// After the last chunk a final commit signals the epilogue (warps 2-5: one TMEM lane = one weight
-// row per thread, tcgen05.ld 16 sequences at a time, scale / residual / ReLU^2*GLU, coalesced stores).
+// One CTA per 128-row tile (two 64-row TL1 blocks; for the GLU epilogue the gate block and its up block, so the
+// activation is applied inside the CTA). K is walked in 128-byte chunks through a ring of 4 or 8 slots; per chunk
+//   warp 0 (lane 0)     bulk-copies the packed 2-bit weights eight chunks at a time (2 x 16 KB) into a two-group ring,
+//                       the first two groups first thing in the kernel (weights depend on no earlier kernel); lanes
+//                       1-31 fetch the per-sequence scale and sum for the epilogue;
+//   warps 2-5 / 6-9     (alternate chunks) expand the 2-bit codes to bytes in registers and write them straight into
+//                       the slot's 32 columns of tensor memory (tcgen05.st 16x256b: no shared-memory A tile, no
+//                       proxy fence). Lane quarter q of a group takes one nibble half of one row block; a thread's
+//                       four TMEM lanes are the four rows of ONE packed word, so a thread loads sixteen words per
+//                       chunk and every byte of them is used. The row order inside a quarter is therefore permuted
+//                       (TMEM lane l holds row 4*(l&7) + (l>>3)); the epilogue undoes it. The warps of a group
+//                       take turns TMA-loading the chunk's activation tile [N][128 B] (128-byte swizzle) into the
+//                       slot right after they have seen it free: a dedicated thread doing a poll, an expect_tx and
+//                       a TMA issue per chunk was the slowest role of the pipeline (about 800 cycles per chunk);
+//   warps 1, 10-12      (lane 0 each) take every fourth chunk: one poll of the slot's barrier (expand arrivals + the
+//                       TMA's bytes), four tcgen05.mma (K = 32 each, A from tensor memory), one commit that frees the
+//                       slot. A poll costs the issuing thread about 180 cycles, a commit about 80 and the loop
+//                       another 270 (measured), more than the MMAs of a chunk take below 256 sequences, so one
+//                       issuing thread bounds the loop; four hide it. Integer accumulation is order-free, so the only
+//                       ordering needed between them is that chunk 0 (which overwrites) completes first.
+// After the last chunk every issuing thread commits to one barrier, which starts the epilogue on all eight expand
+// warps (two groups on alternate 32-sequence column units; TMEM lane = weight row, tcgen05.ld 16 sequences at a
+// time, scale / residual / ReLU^2*GLU, the unit assembled in shared memory and sent off by its own TMA store while
+// the next one is computed).
 // Few row tiles (the out, down and q|k|v projections have 20 to 30) would leave most SMs idle, so K is then split
 // across the 2, 4 or 8 CTAs of a thread-block cluster: each accumulates its share of the chunks in its own tensor
 // memory and parks its int32 partial tile in shared memory; after a hardware cluster barrier every CTA takes the
@@ -40,15 +51,18 @@ namespace cg = cooperative_groups;
 
 namespace tz {
 
-constexpr int kUmmaThreads = 320;              // warp 0 producer, warp 1 MMA, warps 2-5 and 6-9 expand alternate chunks
-constexpr int kMaxStages = 4;                  // A/B tile stages (3 when the activation tile is 32 KB)
-constexpr int kPGroup = 8;                     // chunks of packed weights per bulk copy (16 KB per row block)
-constexpr int kPGroups = 2;                    // such groups in the ring: up to 64 KB of packed weights in flight
-constexpr int kKc = 128;                       // bytes of K per stage (one swizzle atom row)
+constexpr int kExpandGroups = 4;               // groups of four warps that expand alternate chunks (and run the epilogue)
+constexpr int kUmmaThreads = 32 * (2 + 4 * kExpandGroups + 3);   // warp 0 producer, warp 1 and the last three MMA issue, the rest expand
+constexpr int kMmaThreads = 4;
+constexpr int kMaxSlots = 16;                  // ring of chunk slots: as many as tensor memory and shared memory allow (4 at 256 sequences, 12 at 64)
+constexpr int kPGroup = 4;                     // chunks of packed weights per bulk copy (8 KB per row block)
+constexpr int kMaxPGroups = 4;                 // such groups in the ring: up to 64 KB of packed weights in flight
+constexpr int kKc = 128;                       // bytes of K per chunk (one swizzle atom row)
 constexpr int kTileRows = 128;
-constexpr int kABytes = kTileRows * kKc;       // 16 KB
 constexpr int kPBytes = 2 * (kKc / 2) * 32;    // packed weights of one chunk, two row blocks: 4 KB
 constexpr int kMaxN = 256;
+constexpr int kTmemCols = 512;                 // columns 0..N-1 accumulators, then 32 columns per slot for the A operand
+constexpr int kSmemBudget = 216 * 1024;        // activation ring + packed-weight ring
 
 struct UmmaLaunch {
     tenzo_tl1_gemv_args a;
@@ -56,321 +70,429 @@ struct UmmaLaunch {
     const int* sum_a;        // [batch] sum_k a_k
     int units;               // tiles along the rows
     int n_box;               // sequences per CTA, padded to a multiple of 16 (<= 256)
-    int tmem_cols;           // power of two >= max(32, n_box)
-    int n_stages;            // A/B tile stages
+    int n_slots;             // ring slots (A in tensor memory, activation tile in shared memory)
+    int n_pgroups;           // groups of kPGroup chunks in the packed-weight ring
     int ksplit;              // CTAs of a cluster that share one tile's K range (1 = no cluster)
+    int store_cols;          // sequences per TMA store of the epilogue (32 without a cluster, 16 with one)
 };
 
 __device__ int g_umma_timeouts = 0;
 
+// Optional in-kernel timeline (compile with -DTZ_UMMA_TRACE): CTA-local clock64 stamps per phase, read back through
+// tenzo_trace_umma; compiled out of the library build.
+#ifdef TZ_UMMA_TRACE
+__device__ long long g_umma_trace[160 * 16];
+#define UT(i) (g_umma_trace[(blockIdx.x % 160) * 16 + (i)] = clock64())
+#define UTG(i) do { long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); g_umma_trace[(blockIdx.x % 160) * 16 + (i)] = t_; } while (0)
+#else
+#define UT(i) ((void)0)
+#define UTG(i) ((void)0)
+#endif
+
+// Optional self-check (compile with -DTZ_UMMA_CHECK): every shared-memory range handed to a copy engine and every
+// tensor-memory column range is checked against the allocation first; a violation is recorded (code, value, limit) and
+// the access skipped. Read back through tenzo_check_umma; compiled out of the library build.
+#ifdef TZ_UMMA_CHECK
+__device__ unsigned long long g_umma_check[4];
+__device__ __forceinline__ bool umma_check(bool good, int code, unsigned long long v, unsigned long long lim) {
+    if (!good && atomicCAS(&g_umma_check[0], 0ull, (unsigned long long)code) == 0ull) { g_umma_check[1] = v; g_umma_check[2] = lim; g_umma_check[3] = blockIdx.x; }
+    return good;
+}
+#define UCHK(good, code, v, lim) umma_check((good), (code), (unsigned long long)(v), (unsigned long long)(lim))
+#else
+#define UCHK(good, code, v, lim) true
+#endif
 
 __device__ __forceinline__ float umma_seg_scale(const tenzo_tl1_gemv_args& a, int block) {
     return block < a.seg_end[0] ? a.seg_scale[0] : (block < a.seg_end[1] ? a.seg_scale[1] : a.seg_scale[2]);
 }
 
 struct UmmaSmem {
-    // [1024-aligned] stages x { A 16 KB | B n_box*128 } | packed ring kPGroups x 2 blocks x 16 KB | barriers | tmem slot | GLU exchange [16][64] floats | inv[256] | sum_a[256]
-    static __host__ __device__ int stage_bytes(int n_box) { return kABytes + n_box * kKc; }
-    static __host__ __device__ int stages_for(int n_box) { return n_box > 128 ? 3 : kMaxStages; }
-    static constexpr int n_bars = 3 * kMaxStages + 2 * kPGroups + 1;
+    // [1024-aligned] ring n_slots x { B n_box*128 } | packed ring n_pgroups x 2 blocks x 8 KB | barriers | tmem slot | inv[256] | sum_a[256]
+    static __host__ __device__ int pgroups_for(int) { return kMaxPGroups; }
+    static __host__ __device__ int tmem_a(int n_box) { return (n_box + 31) & ~31; }          // first column of the A slots
+    static __host__ __device__ int slots_for(int n_box) {
+        const int by_tmem = (kTmemCols - tmem_a(n_box)) / 32, by_smem = (kSmemBudget - pgroups_for(n_box) * kPGroup * kPBytes) / (n_box * kKc);
+        const int r = by_tmem < by_smem ? by_tmem : by_smem;
+        // A multiple of four (the expand groups and the issuing threads): slot s then always belongs to group s % 4 and
+        // thread s % 4, so every phase of a slot's barriers is seen, in order, by the same waiter. (A parity wait
+        // cannot tell phase k from phase k - 2: with five slots a thread that ran ahead of its neighbour took a slot's
+        // previous phase for the one it waited for and multiplied a tile that had not arrived.)
+        return (r < kMaxSlots ? r : kMaxSlots) & ~3;
+    }
+    static constexpr int n_bars = 2 * kMaxSlots + 2 * kMaxPGroups + 3;
     static __host__ __device__ size_t bytes(int n_box) {
-        return 1024 + (size_t)stages_for(n_box) * stage_bytes(n_box) + (size_t)kPGroups * kPGroup * kPBytes + ((8 * n_bars + 15) & ~15) + 16 + 16 * 64 * 4 + 2 * kMaxN * 4;
+        return 1024 + (size_t)slots_for(n_box) * n_box * kKc + (size_t)pgroups_for(n_box) * kPGroup * kPBytes + ((8 * n_bars + 15) & ~15) + 16 + 2 * kMaxN * 4;
     }
 };
 
+// One 16-sequence block of the epilogue: r = accumulators of TMEM lane m (weight row `row`, `rr` inside its block).
+template <int EPI>
+__device__ __forceinline__ void umma_epilogue_block(const tenzo_tl1_gemv_args& a, uint32_t (&r)[16], const float* s_inv, const int* s_sum, float wscale,
+                                                    int c0, int seq0, int block, int rr, int row, bool up_half, float* s_out_cols, float* s_glu_cols, bool ok) {
+    float v[16];
+#pragma unroll
+    for (int i = 0; i < 16; i += 4) {
+        const int4 sv = *reinterpret_cast<const int4*>(s_sum + c0 + i);
+        const float4 iv = *reinterpret_cast<const float4*>(s_inv + c0 + i);
+        const int s4[4] = {sv.x, sv.y, sv.z, sv.w};
+        const float i4[4] = {iv.x, iv.y, iv.z, iv.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int accv = (int)r[i + e] - s4[e];
+            r[i + e] = (uint32_t)accv;
+            v[i + e] = (float)accv * (i4[e] * wscale);      // :1554, :118
+        }
+    }
+    if (a.acc_out && ok && block >= 0) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+            if (seq0 + c0 + i < a.batch) a.acc_out[(size_t)(seq0 + c0 + i) * a.n_blocks * 64 + block * 64 + rr] = (int)r[i];
+    }
+    if (EPI == TENZO_EPI_RELU2_GLU) {
+        if (up_half) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) s_glu_cols[i * 64 + rr] = v[i];
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const float rl = fmaxf(0.0f, v[i]);
+                s_out_cols[i * 64 + rr] = (rl * rl) * s_glu_cols[i * 64 + rr];   // :1618-1619
+            }
+        }
+    } else if (EPI == TENZO_EPI_RESIDUAL) {
+        float res[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int seq = seq0 + c0 + i;
+            res[i] = (seq < a.batch && block >= 0) ? __ldcg(a.resid + (size_t)seq * a.out_stride + block * 64 + rr) : 0.0f;
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) s_out_cols[i * 128 + row] = res[i] + v[i];                          // :1590
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) s_out_cols[i * 128 + row] = v[i];
+    }
+}
+
+template <int EPI, bool CLUSTER>
 __global__ void __launch_bounds__(kUmmaThreads, 1) tl1_umma_kernel(const UmmaLaunch L, const __grid_constant__ CUtensorMap amap,
-                                                                   const __grid_constant__ CUtensorMap omap,
-                                                                   const __grid_constant__ CUtensorMap omap16) {
+                                                                   const __grid_constant__ CUtensorMap omap) {
     const tenzo_tl1_gemv_args& a = L.a;
     extern __shared__ unsigned char smem_raw[];
     const uint32_t base_off = ((smem_addr(smem_raw) + 1023u) & ~1023u) - smem_addr(smem_raw);
-    unsigned char* stages = smem_raw + base_off;
-    const int stage_bytes = UmmaSmem::stage_bytes(L.n_box), S = L.n_stages;
-    unsigned char* pring = stages + (size_t)S * stage_bytes;                  // [kPGroups][2 row blocks][kPGroup chunks][64][32] packed weights
-    uint64_t* bars = reinterpret_cast<uint64_t*>(pring + (size_t)kPGroups * kPGroup * kPBytes);
-    uint64_t* bar_raw = bars;                          // [S] activation tile has landed
-    uint64_t* bar_ready = bars + kMaxStages;           // [S] A tile expanded (one arrival per expanding warp)
-    uint64_t* bar_empty = bars + 2 * kMaxStages;       // [S] the stage's MMAs have completed
-    uint64_t* bar_p = bars + 3 * kMaxStages;           // [kPGroups] packed weights have landed
-    uint64_t* bar_pfree = bar_p + kPGroups;            // [kPGroups] packed weights consumed (one arrival per expanding warp per chunk)
-    uint64_t* bar_accum = bar_pfree + kPGroups;        // all MMAs have completed
+    unsigned char* ring = smem_raw + base_off;
+    const int N = L.n_box, R = L.n_slots, slot_bytes = N * kKc;
+    const int PG = L.n_pgroups;
+    unsigned char* pring = ring + (size_t)R * slot_bytes;                       // [PG][2 row blocks][kPGroup chunks][64][32] packed weights
+    uint64_t* bars = reinterpret_cast<uint64_t*>(pring + (size_t)PG * kPGroup * kPBytes);
+    const uint32_t tmem_a0 = (uint32_t)UmmaSmem::tmem_a(N);
+    uint64_t* bar_full = bars;                         // [R] A expanded (one arrival per expanding warp) and the activation tile landed
+    uint64_t* bar_empty = bars + kMaxSlots;            // [R] the slot's MMAs have completed
+    uint64_t* bar_p = bars + 2 * kMaxSlots;            // [PG] packed weights have landed
+    uint64_t* bar_pfree = bar_p + kMaxPGroups;         // [PG] packed weights consumed (one arrival per expanding warp per chunk)
+    uint64_t* bar_accum = bar_pfree + kMaxPGroups;        // every issuing thread's MMAs have completed
+    uint64_t* bar_first = bar_accum + 1;               // chunk 0 (the one that overwrites the accumulators) has completed
+    uint64_t* bar_meta = bar_first + 1;                // per-sequence scale and sum are in shared memory
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned char*>(bars) + ((8 * UmmaSmem::n_bars + 15) & ~15));   // 16-byte aligned
-    float* s_glu = reinterpret_cast<float*>(tmem_slot + 4);   // [16][64]
-    float* s_inv = s_glu + 16 * 64;                           // [kMaxN] m/31 of this CTA's sequences
+    float* s_inv = reinterpret_cast<float*>(tmem_slot + 4);   // [kMaxN] m/31 of this CTA's sequences
     int* s_sum = reinterpret_cast<int*>(s_inv + kMaxN);       // [kMaxN] sum_k a_k
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const bool glu = a.epilogue == TENZO_EPI_RELU2_GLU;
+    if (tid == 0) { UT(0); UTG(10); }
+#ifdef TZ_UMMA_CHECK
+    uint32_t dyn_bytes;
+    asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_bytes));
+    const unsigned char* smem_end = smem_raw + dyn_bytes;
+    UCHK(reinterpret_cast<const unsigned char*>(s_sum + kMaxN) <= smem_end, 7, reinterpret_cast<const unsigned char*>(s_sum + kMaxN) - smem_raw, dyn_bytes);
+#endif
+    constexpr bool glu = EPI == TENZO_EPI_RELU2_GLU;
     const int tile = blockIdx.x, seq0 = blockIdx.y * kMaxN;
     const int blk0 = glu ? tile : 2 * tile;
     const int blk1 = glu ? tile + L.units : (2 * tile + 1 < a.n_blocks ? 2 * tile + 1 : -1);
-    const int ksplit = L.ksplit;
-    const int split = ksplit > 1 ? (int)cg::this_cluster().block_rank() : 0;      // cluster = the CTAs with this tile's blockIdx.z = 0..ksplit-1
+    const int ksplit = CLUSTER ? L.ksplit : 1;
+    const int split = CLUSTER ? (int)cg::this_cluster().block_rank() : 0;         // cluster = the CTAs with this tile's blockIdx.z = 0..ksplit-1
     const int all_chunks = a.K / kKc;
     const int c_begin = split * all_chunks / ksplit;                                // this CTA's chunks of K: never empty (all_chunks >= ksplit)
     const int n_chunks = (split + 1) * all_chunks / ksplit - c_begin;
-    const int N = L.n_box;
 
+    const size_t blk_bytes = (size_t)(a.K / 2) * 32;
+    const int n_groups = (n_chunks + kPGroup - 1) / kPGroup;
+    auto request_group = [&](int g) {                      // packed weights of chunks 8g .. 8g+7, both row blocks
+        const int slot = g % PG;
+        const int chunks = min(kPGroup, n_chunks - g * kPGroup);
+        const unsigned bytes = (unsigned)chunks * (kPBytes / 2);
+        unsigned char* sP = pring + (size_t)slot * kPGroup * kPBytes;
+        if (!UCHK(sP + 2 * kPGroup * (kPBytes / 2) <= reinterpret_cast<unsigned char*>(bars) && slot < PG && chunks > 0, 1, sP - smem_raw, g)) return;
+        mbar_expect_tx(&bar_p[slot], blk1 >= 0 ? 2 * bytes : bytes);
+        const size_t k_off = (size_t)(c_begin + g * kPGroup) * (kPBytes / 2);
+        bulk_g2s(sP, a.w + (size_t)blk0 * blk_bytes + k_off, bytes, &bar_p[slot]);
+        if (blk1 >= 0) bulk_g2s(sP + kPGroup * (kPBytes / 2), a.w + (size_t)blk1 * blk_bytes + k_off, bytes, &bar_p[slot]);
+    };
     if (tid == 0) {
-        for (int s = 0; s < S; ++s) {
-            mbar_init(&bar_raw[s], 1);
-            mbar_init(&bar_ready[s], 4);
-            mbar_init(&bar_empty[s], 1);
-        }
-        for (int s = 0; s < kPGroups; ++s) {
-            mbar_init(&bar_p[s], 1);
-            mbar_init(&bar_pfree[s], 4 * kPGroup);
-        }
-        mbar_init(bar_accum, 1);
+        // The weights depend on no earlier kernel and their latency is the longest in the prologue: ask for the first
+        // two groups before anything else (an mbarrier operation costs its thread about a hundred cycles, so the
+        // other barriers are initialised by other threads meanwhile).
+        for (int g = 0; g < PG; ++g) mbar_init(&bar_p[g], 1);
         mbar_init_fence();
-    }
-    l2_prefetch_slice(a.prefetch, a.prefetch_bytes);       // the next kernel's weights
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(L.tmem_cols) : "memory");
+        for (int g = 0; g < n_groups && g < PG; ++g) request_group(g);
+        UT(2);
+    } else if (warp == 2) {
+        if (lane < R) {
+            mbar_init(&bar_full[lane], 5);             // four expanding warps + the expect_tx of the warp that requests the activation tile
+            mbar_init(&bar_empty[lane], 1);
+        } else if (lane >= 16 && lane < 16 + kMaxPGroups) {
+            mbar_init(&bar_pfree[lane - 16], 4 * kPGroup);
+        } else if (lane == 24) {
+            mbar_init(bar_accum, kMmaThreads);
+        } else if (lane == 25) {
+            mbar_init(bar_first, 1);
+        } else if (lane == 26) {
+            mbar_init(bar_meta, 1);
+        }
+        mbar_init_fence();
+    } else if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    if (warp >= 3) l2_prefetch_slice(a.prefetch, a.prefetch_bytes);       // the next kernel's weights
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
-    if (a.use_pdl) {
-        pdl_wait();
-        pdl_launch_dependents();
-    }
+    if (a.use_pdl) pdl_launch_dependents();
+    if (tid == 0) UT(1);
     bool timed_out = false, epi_ok = false;
-    for (int i = tid; i < N; i += kUmmaThreads) {              // per-sequence epilogue operands (read after the final barrier)
-        const int seq = seq0 + i;
-        s_inv[i] = seq < a.batch ? __ldcg(L.inv + seq) : 0.0f;
-        s_sum[i] = seq < a.batch ? __ldcg(L.sum_a + seq) : 0;
-    }
-    __syncthreads();
+    const int mma_t = warp == 1 ? 0 : warp - (1 + 4 * kExpandGroups);        // issuing thread 0..3: warp 1 and the three warps after the expand warps
 
     if (warp == 0) {
-        // ---- producer -----------------------------------------------------------------------------
         if (lane == 0) {
-            const size_t blk_bytes = (size_t)(a.K / 2) * 32;
-            int gp = 0;                                   // next group of packed chunks to request
-            const int n_groups = (n_chunks + kPGroup - 1) / kPGroup;
-            for (int j = 0; j < n_chunks && !timed_out; ++j) {
-                for (; gp < n_groups && gp <= j / kPGroup + 1; ++gp) {
-                    const int slot = gp % kPGroups, guse = gp / kPGroups;
-                    if (guse > 0 && !mbar_test(&bar_pfree[slot], (unsigned)(guse - 1) & 1u)) {
-                        if (gp > j / kPGroup) break;               // the group after the current one: do not hold up the activation tiles
-                        if (!mbar_spin_bounded(&bar_pfree[slot], (unsigned)(guse - 1) & 1u)) { timed_out = true; break; }
-                    }
-                    const int chunks = min(kPGroup, n_chunks - gp * kPGroup);
-                    const unsigned bytes = (unsigned)chunks * (kPBytes / 2);
-                    unsigned char* sP = pring + (size_t)slot * kPGroup * kPBytes;
-                    mbar_expect_tx(&bar_p[slot], blk1 >= 0 ? 2 * bytes : bytes);
-                    const size_t k_off = (size_t)(c_begin + gp * kPGroup) * (kPBytes / 2);
-                    bulk_g2s(sP, a.w + (size_t)blk0 * blk_bytes + k_off, bytes, &bar_p[slot]);
-                    if (blk1 >= 0) bulk_g2s(sP + kPGroup * (kPBytes / 2), a.w + (size_t)blk1 * blk_bytes + k_off, bytes, &bar_p[slot]);
-                }
-                if (timed_out) break;
-                const int s = j % S, use = j / S;
-                if (use > 0 && !mbar_spin_bounded(&bar_empty[s], (unsigned)(use - 1) & 1u)) { timed_out = true; break; }
-                mbar_expect_tx(&bar_raw[s], (unsigned)(N * kKc));
-                tma_load_2d(stages + (size_t)s * stage_bytes + kABytes, &amap, (c_begin + j) * kKc, seq0, &bar_raw[s]);
+            // ---- producer: the remaining groups of packed weights, each as soon as its ring half is free -------
+            for (int gp = PG; gp < n_groups; ++gp) {
+                const int slot = gp % PG, guse = gp / PG;
+                if (!mbar_spin_bounded(&bar_pfree[slot], (unsigned)(guse - 1) & 1u)) { timed_out = true; break; }
+                request_group(gp);
             }
+        } else {
+            // ---- per-sequence epilogue operands (quantiser outputs) ---------------------------------------
+            if (a.use_pdl) pdl_wait();
+            for (int i = lane - 1; i < N; i += 31) {
+                const int seq = seq0 + i;
+                s_inv[i] = seq < a.batch ? __ldcg(L.inv + seq) : 0.0f;
+                s_sum[i] = seq < a.batch ? __ldcg(L.sum_a + seq) : 0;
+            }
+            __syncwarp(0xfffffffeu);
+            if (lane == 1) mbar_arrive(bar_meta);
         }
-    } else if (warp == 1) {
-        // ---- MMA issue ------------------------------------------------------------------------------
+    } else if (warp == 1 || warp >= 2 + 4 * kExpandGroups) {
+        // ---- MMA issue: thread t takes chunks t, t + 4, ... ---------------------------------------------------
         if (lane == 0) {
             // c = s32, a = u8, b = s8, both K-major, N at bit 17 (>>3), M at bit 24 (>>4)
             const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(kTileRows >> 4) << 24);
-            for (int j = 0; j < n_chunks; ++j) {
-                const int s = j % S, use = j / S;
-                if (!mbar_spin_bounded(&bar_ready[s], (unsigned)use & 1u)) { timed_out = true; break; }
-                if (!mbar_spin_bounded(&bar_raw[s], (unsigned)use & 1u)) { timed_out = true; break; }
+            if (mma_t > 0 && mma_t < n_chunks && !mbar_spin_bounded(bar_first, 0u)) timed_out = true;
+            for (int j = mma_t; j < n_chunks && !timed_out; j += kMmaThreads) {
+                const int s = j % R, use = j / R;
+                if (!mbar_spin_bounded(&bar_full[s], (unsigned)use & 1u)) { timed_out = true; break; }
                 tc_fence_after();
-                const uint32_t sa = smem_addr(stages + (size_t)s * stage_bytes);
-                const uint64_t da = umma_desc_sw128(sa), db = umma_desc_sw128(sa + kABytes);
+                if (j == 16) UT(5);
+                const uint32_t ta = tmem_base + tmem_a0 + (uint32_t)(32 * s);
+                const uint64_t db = umma_desc_sw128(smem_addr(ring + (size_t)s * slot_bytes));
+                if (UCHK(tmem_a0 + 32 * s + 32 <= (uint32_t)kTmemCols && s < R && ring + (size_t)(s + 1) * slot_bytes <= pring, 5, s, j))
 #pragma unroll
                 for (int k4 = 0; k4 < kKc / 32; ++k4)
-                    umma_i8(tmem_base, da + (uint64_t)(2 * k4), db + (uint64_t)(2 * k4), idesc, (j > 0 || k4 > 0) ? 1u : 0u);
+                    umma_i8_ta(tmem_base, ta + (uint32_t)(8 * k4), db + (uint64_t)(2 * k4), idesc, (j > 0 || k4 > 0) ? 1u : 0u);
                 umma_commit(&bar_empty[s]);
+                if (j == 0) umma_commit(bar_first);
             }
             umma_commit(bar_accum);
         }
     } else {
-        // ---- expand the 2-bit codes into the A tile ---------------------------------------------------
-        // lane bits 0-1: kk8 & 3, bit 2: c4 & 1, bits 3-4: c4 >> 1; warp: kk8 >> 2 and the row block. A quarter
-        // warp then stores eight different 16-byte chunk positions (no bank conflicts on the A tile).
-        const int uw = (warp - 2) & 3, grp = (warp - 2) >> 2;   // two groups of four warps take alternate chunks
-        const int kk8 = (lane & 3) | ((uw & 1) << 2), c4 = ((lane >> 2) & 1) | (((lane >> 3) & 3) << 1), blk = uw >> 1;
+        // ---- expand the 2-bit codes into tensor memory ----------------------------------------------------------
+        // Quarter q = warp & 3 owns TMEM lanes 32q..32q+31 = row block q >> 1, nibble half q & 1. Thread 4g + t holds
+        // lanes g + 8*jj (jj = 0..3) = rows 4g + jj of the half = the four bytes of packed word g of a column pair, and
+        // the columns 8n + 2t, 8n + 2t + 1 = column pairs 16n + 4t .. 16n + 4t + 3. The four words of a (thread, n) are
+        // fetched in the order u ^ t so that a warp's request covers 32 banks; the byte permutes that transpose them
+        // take the order back (selectors chosen per thread).
+        const int q = warp & 3, grp = (warp - 2) >> 2;
+        const int blk = q >> 1, hi = q & 1, g = lane >> 2, t = lane & 3;
+        const bool have = blk == 0 || blk1 >= 0;
+        const uint32_t sel_a = (t & 1) ? 0x1504u : 0x5140u, sel_b = (t & 1) ? 0x3726u : 0x7362u;
+        const uint32_t sel_lo = (t & 2) ? 0x1054u : 0x5410u, sel_hi = (t & 2) ? 0x3276u : 0x7632u;
+        int woff[4];                                           // word offsets of the four loads inside a 16-column-pair set
+#pragma unroll
+        for (int u = 0; u < 4; ++u) woff[u] = (4 * t + (u ^ t)) * 8 + g;
         int seen_group = -1;
-        for (int j = grp; j < n_chunks; j += 2) {
-            const int s = j % S, use = j / S, ps = (j / kPGroup) % kPGroups, puse = (j / kPGroup) / kPGroups;
+        for (int j = grp; j < n_chunks; j += kExpandGroups) {
+            const int s = j % R, use = j / R, ps = (j / kPGroup) % PG, puse = (j / kPGroup) / PG;
             bool ok = true;
-            if (lane == 0 && (j / kPGroup != seen_group)) ok = mbar_spin_bounded(&bar_p[ps], (unsigned)puse & 1u);
+            if (j == 16 && tid == 64) UT(3);
+            if (lane == 0) ok = (use == 0 || mbar_spin_bounded(&bar_empty[s], (unsigned)(use - 1) & 1u));
+            if (j == 16 && tid == 64) UT(12);
+            const int turn = j / kExpandGroups;
+            if (lane == 0 && ok && (turn & 3) == q) {           // the group's warps take turns requesting the activation tile
+                if (a.use_pdl && turn < 4) pdl_wait();          // it comes from the previous kernel (first turn of each warp)
+                if (UCHK(s < R && ring + (size_t)(s + 1) * slot_bytes <= pring, 2, s, j)) {
+                mbar_expect_tx(&bar_full[s], (unsigned)slot_bytes);
+                tma_load_2d(ring + (size_t)s * slot_bytes, &amap, (c_begin + j) * kKc, seq0, &bar_full[s]);
+                }
+            }
+            if (lane == 0 && ok && (j / kPGroup != seen_group)) ok = mbar_spin_bounded(&bar_p[ps], (unsigned)puse & 1u);
             seen_group = j / kPGroup;
-            if (lane == 0 && ok) ok = (use == 0 || mbar_spin_bounded(&bar_empty[s], (unsigned)(use - 1) & 1u));
+            if (j == 0 && tid == 64) UT(6);
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) { timed_out = true; break; }
-            unsigned char* st = stages + (size_t)s * stage_bytes;
+            tc_fence_after();
+            if (j == 16 && tid == 64) UT(13);
             const uint32_t* sP = reinterpret_cast<const uint32_t*>(pring + (size_t)ps * kPGroup * kPBytes + (size_t)blk * kPGroup * (kPBytes / 2) +
                                                                    (size_t)(j % kPGroup) * (kPBytes / 2));
-            uint32_t W[8];
+            uint32_t W[16];
+            const bool sp_ok = UCHK(reinterpret_cast<const unsigned char*>(sP) >= pring && reinterpret_cast<const unsigned char*>(sP + 512) <= reinterpret_cast<unsigned char*>(bars), 3,
+                                    reinterpret_cast<const unsigned char*>(sP) - smem_raw, j);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) W[i] = (blk == 1 && blk1 < 0) ? 0u : sP[(8 * kk8 + i) * 8 + c4];
-            // 4x4 byte transposes: T[h][jj] = bytes (W[4h+0].jj, W[4h+1].jj, W[4h+2].jj, W[4h+3].jj): column pair 8*kk8+4h.. of byte column 4*c4+jj
-            uint32_t T[2][4];
+            for (int n = 0; n < 4; ++n)
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const uint32_t p0 = prmt(W[4 * h], W[4 * h + 1], 0x5140u), p1 = prmt(W[4 * h + 2], W[4 * h + 3], 0x5140u);
-                const uint32_t p2 = prmt(W[4 * h], W[4 * h + 1], 0x7362u), p3 = prmt(W[4 * h + 2], W[4 * h + 3], 0x7362u);
-                T[h][0] = prmt(p0, p1, 0x5410u); T[h][1] = prmt(p0, p1, 0x7632u);
-                T[h][2] = prmt(p2, p3, 0x5410u); T[h][3] = prmt(p2, p3, 0x7632u);
-            }
+                for (int u = 0; u < 4; ++u) W[4 * n + u] = (have && sp_ok) ? sP[n * 128 + woff[u]] : 0u;
             __syncwarp();
             if (lane == 0) mbar_arrive(&bar_pfree[ps]);   // the packed chunk has been consumed into registers
+            uint32_t lo[16], up[16];                       // registers of the two stores: lanes 0-15 (jj = 0, 1) and 16-31 (jj = 2, 3)
 #pragma unroll
-            for (int jj = 0; jj < 4; ++jj) {
+            for (int n = 0; n < 4; ++n) {
+                // 4x4 byte transpose: T[jj] = byte jj of the words of column pairs 16n + 4t + 0..3
+                const uint32_t p0 = prmt(W[4 * n], W[4 * n + 1], sel_a), p1 = prmt(W[4 * n + 2], W[4 * n + 3], sel_a);
+                const uint32_t p2 = prmt(W[4 * n], W[4 * n + 1], sel_b), p3 = prmt(W[4 * n + 2], W[4 * n + 3], sel_b);
+                const uint32_t T[4] = {prmt(p0, p1, sel_lo), prmt(p0, p1, sel_hi), prmt(p2, p3, sel_lo), prmt(p2, p3, sel_hi)};
 #pragma unroll
-                for (int hi = 0; hi < 2; ++hi) {            // low nibble: row 4*c4+jj, high nibble: row 32+4*c4+jj
-                    uint4 o;
-                    uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        const uint32_t n = T[h][jj] >> (4 * hi);
-                        const uint32_t e0 = n & 0x03030303u, e1 = (n >> 2) & 0x03030303u;   // codes of the even / odd columns
-                        ow[2 * h] = prmt(e0, e1, 0x5140u);
-                        ow[2 * h + 1] = prmt(e0, e1, 0x7362u);
-                    }
-                    const int row = blk * 64 + hi * 32 + 4 * c4 + jj;
-                    *reinterpret_cast<uint4*>(st + row * kKc + ((kk8 ^ (row & 7)) << 4)) = o;
+                for (int jj = 0; jj < 4; ++jj) {
+                    const uint32_t nb = T[jj] >> (4 * hi);
+                    const uint32_t e = nb & 0x03030303u, o = (nb >> 2) & 0x03030303u;    // codes of the even / odd columns
+                    uint32_t* dst = (jj < 2 ? lo : up) + 4 * n + 2 * (jj & 1);
+                    dst[0] = prmt(e, o, 0x5140u);
+                    dst[1] = prmt(e, o, 0x7362u);
                 }
             }
-            fence_proxy_async_smem();
+            const uint32_t ta = tmem_base + tmem_a0 + (uint32_t)(32 * s) + ((uint32_t)(32 * q) << 16);
+            if (j == 16 && tid == 64) UT(14);
+            if (UCHK(tmem_a0 + 32 * s + 32 <= (uint32_t)kTmemCols && (tmem_base & 0xffffu) == 0u, 4, tmem_a0 + 32 * s, tmem_base)) {
+            tmem_st_16x256b_x4(ta, lo);
+            tmem_st_16x256b_x4(ta + (16u << 16), up);
+            }
+            tmem_wait_st();
+            if (j == 16 && tid == 64) UT(15);
+            tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&bar_ready[s]);
+            if (lane == 0) mbar_arrive(&bar_full[s]);
+            if (j == 12 && tid == 64) UT(4);
         }
-        if (grp == 0) {
-            // ---- all of this CTA's MMAs have completed; in a cluster it parks its partial tile [N][128] int32 (the
-            //      column blocks its peers will reduce) in the stage memory the pipeline no longer needs ------------------
-            bool ok = true;
-            if (lane == 0) ok = !timed_out && mbar_spin_bounded(bar_accum, 0u);
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) timed_out = true;
-            tc_fence_after();
-            epi_ok = ok;
-            if (ksplit > 1) {
-                const int q = warp & 3, row = 32 * q + lane;
-                int* s_part = reinterpret_cast<int*>(stages);
-                for (int c0 = 0; c0 < N; c0 += 16) {
-                    if ((c0 >> 4) % ksplit == split) continue;       // this CTA's own column blocks stay in tensor memory
-                    uint32_t r[16];
+        // ---- all of this CTA's MMAs have completed; in a cluster it parks its partial tile [N][128 TMEM lanes] int32
+        //      (the column blocks its peers will reduce) in the ring memory the pipeline no longer needs -----------------
+        if (a.use_pdl) pdl_wait();                           // the residual rows come from an earlier kernel (long done by now)
+        bool ok = true;
+        if (lane == 0) ok = !timed_out && mbar_spin_bounded(bar_meta, 0u) && mbar_spin_bounded(bar_accum, 0u);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) timed_out = true;
+        tc_fence_after();
+        if (tid == 64) UT(7);
+        epi_ok = ok;
+        if (CLUSTER) {
+            const int m = 32 * q + lane;
+            int* s_part = reinterpret_cast<int*>(ring);
+            for (int c0 = 16 * grp; c0 < N; c0 += 16 * kExpandGroups) {
+                if ((c0 >> 4) % ksplit == split) continue;       // this CTA's own column blocks stay in tensor memory
+                uint32_t r[16];
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) r[i] = 0u;
-                    if (ok) tmem_ld16(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)c0, r);
+                for (int i = 0; i < 16; ++i) r[i] = 0u;
+                if (ok) tmem_ld16(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)c0, r);
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) s_part[(c0 + i) * 128 + row] = (int)r[i];
-                }
+                for (int i = 0; i < 16; ++i) s_part[(c0 + i) * 128 + m] = (int)r[i];
             }
         }
     }
-    if (ksplit > 1) cg::this_cluster().sync();               // every CTA's partial tile is in place
-    if (warp >= 2 && warp < 6) {
-        // ---- epilogue: TMEM lane = weight row; column blocks split, split + ksplit, ... (all of them without a cluster) ----
+    if (CLUSTER) cg::this_cluster().sync();                  // every CTA's partial tile is in place
+    if (warp >= 2 && warp < 2 + 4 * kExpandGroups) {
+        // ---- epilogue: every group, alternate column units; TMEM lane -> weight row through the quarter's permutation ----
         const bool ok = epi_ok;
-        const int q = warp & 3;                              // this warp may touch TMEM lanes 32q..32q+31
-        const int row = 32 * q + lane, rblk = row >> 6, rr = row & 63;
+        const int q = warp & 3, grp = (warp - 2) >> 2;
+        const int m = 32 * q + lane;                         // TMEM lane
+        const int rblk = q >> 1, rr = 32 * (q & 1) + 4 * (lane & 7) + (lane >> 3), row = 64 * rblk + rr;
         const int block = rblk ? blk1 : blk0;
         const float wscale = block >= 0 ? umma_seg_scale(a, block) : 0.0f;
-        const int* peer[8];
+        // Output columns [sequences][128 rows] (GLU: [..][64]) are assembled in shared memory the pipeline no longer
+        // needs - the rings, which are contiguous; with a cluster behind the partial tile the peers are reading - and
+        // leave unit by unit through TMA stores: rows of 512 (256) contiguous bytes per sequence, clipped at the
+        // matrix edge by the tensor map. GLU: the up half goes through shared memory once for all columns, then the
+        // gate half computes and stores. Space: N*512 bytes without a cluster (at least four slots), N*512 plus 512 per
+        // own column with one (a rank owns at most every other block), which the two rings hold for every N.
+        constexpr int row_floats = glu ? 64 : 128;
+        constexpr int SB = CLUSTER ? 1 : 2;                  // 16-sequence blocks per store unit
+        float* s_out = reinterpret_cast<float*>(ring + (CLUSTER ? (size_t)N * 512 : 0));            // behind the partial tile [N][128] int32
+        float* s_glu = s_out + (size_t)(CLUSTER ? 16 * ((N / 16 + 1) / 2) : N) * 64;                 // behind the GLU output columns (a rank owns at most every other block)
+        const int n_blocks16 = N / 16;
+        const int own_blocks = CLUSTER ? (n_blocks16 - split + ksplit - 1) / ksplit : n_blocks16;
+        const int n_units = (own_blocks + SB - 1) / SB;
+        const bool leader = lane == 0 && q == 0;
+        const uint32_t t_lane = tmem_base + ((uint32_t)(32 * q) << 16);
+#pragma unroll 1
+        for (int phase = glu ? 0 : 1; phase < 2; ++phase) {
+            const bool active = !glu || (phase == 0 ? rblk == 1 : rblk == 0);
+            if (active) {
+#pragma unroll 1
+                for (int un = grp; un < n_units; un += kExpandGroups) {
+                    const int ob0 = un * SB;
+                    const bool two = SB == 2 && ob0 + 1 < own_blocks;
+                    const int c0 = 16 * (CLUSTER ? split + ksplit * ob0 : ob0);
+                    uint32_t r0[16], r1[16];
 #pragma unroll
-        for (int p = 0; p < 8; ++p)
-            peer[p] = (ksplit > 1 && p < ksplit && p != split) ? cg::this_cluster().map_shared_rank(reinterpret_cast<int*>(stages), p) : nullptr;
-        // The output columns [sequences][128 rows] (GLU: [..][64]) are assembled in shared memory the pipeline no
-        // longer needs - the stage memory, or with a cluster the packed-weight ring, because the stage memory then
-        // holds the partial tile the peers are reading - one row per thread, and leave through TMA stores: rows of
-        // 512 (256) contiguous bytes per sequence, clipped at the matrix edge by the tensor map.
-        float* s_out = reinterpret_cast<float*>(ksplit > 1 ? pring : stages);
-        int o0 = 0;                                          // column slot in s_out of the block being processed
-        for (int c0 = 16 * split; c0 < N; c0 += 16 * ksplit, o0 += 16) {
-            uint32_t r[16];
-            if (ok) tmem_ld16(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)c0, r);
+                    for (int i = 0; i < 16; ++i) r0[i] = r1[i] = 0u;
+                    if (ok) {
+                        tmem_ld16_nowait(t_lane + (uint32_t)c0, r0);
+                        if (two) tmem_ld16_nowait(t_lane + (uint32_t)(c0 + 16), r1);
+                        tmem_wait_ld();
+                    }
+                    if (CLUSTER) {
+                        // the peers' partials over distributed shared memory: every load issued before the first is
+                        // used (ranks beyond the cluster and this CTA's own read its own tile and are masked out)
 #pragma unroll
-            for (int p = 0; p < 8; ++p) {
-                if (peer[p]) {
+                        for (int p = 0; p < 8; ++p) {
+                            const bool use_p = p < ksplit && p != split;
+                            const int* peer = cg::this_cluster().map_shared_rank(reinterpret_cast<int*>(ring), use_p ? p : split);
+                            const uint32_t mask = use_p ? 0xffffffffu : 0u;
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) r[i] += (uint32_t)peer[p][(c0 + i) * 128 + row];
-                }
-            }
-            int sums[16];
-            float invs[16], res[16];
-#pragma unroll
-            for (int i = 0; i < 16; i += 4) {
-                const int4 sv = *reinterpret_cast<const int4*>(s_sum + c0 + i);
-                const float4 iv = *reinterpret_cast<const float4*>(s_inv + c0 + i);
-                sums[i] = sv.x; sums[i + 1] = sv.y; sums[i + 2] = sv.z; sums[i + 3] = sv.w;
-                invs[i] = iv.x; invs[i + 1] = iv.y; invs[i + 2] = iv.z; invs[i + 3] = iv.w;
-            }
-            if (a.epilogue == TENZO_EPI_RESIDUAL) {
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const int seq = seq0 + c0 + i;
-                    res[i] = (seq < a.batch && block >= 0) ? __ldcg(a.resid + (size_t)seq * a.out_stride + block * 64 + rr) : 0.0f;
-                }
-            }
-            float v[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const int accv = (int)r[i] - sums[i];
-                r[i] = (uint32_t)accv;
-                v[i] = (float)accv * (invs[i] * wscale);      // :1554, :118
-            }
-            if (a.acc_out && ok && block >= 0) {
-#pragma unroll
-                for (int i = 0; i < 16; ++i)
-                    if (seq0 + c0 + i < a.batch) a.acc_out[(size_t)(seq0 + c0 + i) * a.n_blocks * 64 + block * 64 + rr] = (int)r[i];
-            }
-            if (glu) {
-                if (rblk == 1) {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) s_glu[i * 64 + rr] = v[i];
-                }
-                named_barrier_sync(1, 128);
-                if (rblk == 0) {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const float rl = fmaxf(0.0f, v[i]);
-                        s_out[(o0 + i) * 64 + rr] = (rl * rl) * s_glu[i * 64 + rr];   // :1618-1619
+                            for (int i = 0; i < 16; ++i) r0[i] += mask & (uint32_t)peer[(c0 + i) * 128 + m];
+                        }
+                    }
+                    umma_epilogue_block<EPI>(a, r0, s_inv, s_sum, wscale, c0, seq0, block, rr, row, phase == 0, s_out + (size_t)16 * ob0 * row_floats,
+                                             s_glu + (size_t)16 * ob0 * 64, ok);
+                    if (two)
+                        umma_epilogue_block<EPI>(a, r1, s_inv, s_sum, wscale, c0 + 16, seq0, block, rr, row, phase == 0,
+                                                 s_out + (size_t)16 * (ob0 + 1) * row_floats, s_glu + (size_t)16 * (ob0 + 1) * 64, ok);
+                    if (phase == 1) {
+                        // the unit is complete in shared memory: hand it to the TMA and go on with the next one
+                        fence_proxy_async_smem();
+                        named_barrier_sync(1 + grp, glu ? 64 : 128);
+                        if (leader && ok && seq0 + c0 < a.batch &&
+                            UCHK(reinterpret_cast<unsigned char*>(s_out + (size_t)16 * ob0 * row_floats) + 16 * SB * row_floats * 4 <= reinterpret_cast<unsigned char*>(bars), 6,
+                                 reinterpret_cast<unsigned char*>(s_out + (size_t)16 * ob0 * row_floats) - smem_raw, un)) {             // else nothing but padding
+                            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                                         ::"l"(&omap), "r"((glu ? tile : blk0) * 64), "r"(seq0 + c0), "r"(smem_addr(s_out + (size_t)16 * ob0 * row_floats)) : "memory");
+                            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                        }
                     }
                 }
-                named_barrier_sync(1, 128);
-            } else {
-#pragma unroll
-                for (int i = 0; i < 16; ++i)
-                    s_out[(o0 + i) * 128 + row] = a.epilogue == TENZO_EPI_RESIDUAL ? res[i] + v[i] : v[i];   // :1590
             }
+            if (phase == 0) named_barrier_sync(1 + kExpandGroups, 128 * kExpandGroups);      // every up value is in shared memory
         }
-        fence_proxy_async_smem();
-        named_barrier_sync(1, 128);
-        if (tid == 64 && ok) {
-            if (ksplit == 1) {
-                asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
-                             ::"l"(&omap), "r"((glu ? tile : blk0) * 64), "r"(seq0), "r"(smem_addr(s_out)) : "memory");
-            } else {                                         // one 16-sequence box per column block of this CTA
-                const int row_floats = glu ? 64 : 128;
-                int slot = 0;
-                for (int c0 = 16 * split; c0 < N; c0 += 16 * ksplit, slot += 16) {
-                    if (seq0 + c0 >= a.batch) break;         // nothing but padding from here on
-                    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
-                                 ::"l"(&omap16), "r"((glu ? tile : blk0) * 64), "r"(seq0 + c0), "r"(smem_addr(s_out + slot * row_floats)) : "memory");
-                }
-            }
-            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");     // the tile has left shared memory
-        }
+        if (tid == 64) UT(8);
+        if (leader) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");     // the tiles have left shared memory
+        if (tid == 64) UT(9);
     }
-    if (ksplit > 1) cg::this_cluster().sync();               // every peer has read this CTA's partial tile: it may exit
+    if (CLUSTER) cg::this_cluster().sync();                  // every peer has read this CTA's partial tile: it may exit
     if (timed_out) atomicExch(&g_umma_timeouts, 1);
     tc_fence_before();
     __syncthreads();
+    if (tid == 0) UTG(11);
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(L.tmem_cols) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
     }
 }
 
@@ -405,24 +527,27 @@ int launch_tl1_umma(const tenzo_tl1_gemv_args& a, const int8_t* a8, const float*
     L.units = glu ? a.n_blocks / 2 : (a.n_blocks + 1) / 2;
     const int per_cta = a.batch < kMaxN ? a.batch : kMaxN;
     L.n_box = (per_cta + 15) & ~15;
-    L.tmem_cols = 32;
-    while (L.tmem_cols < L.n_box) L.tmem_cols *= 2;
-    L.n_stages = UmmaSmem::stages_for(L.n_box);
+    L.n_slots = UmmaSmem::slots_for(L.n_box);
+    L.n_pgroups = UmmaSmem::pgroups_for(L.n_box);
     const int seq_tiles = (a.batch + kMaxN - 1) / kMaxN;
     L.ksplit = pick_umma_ksplit(L.units * seq_tiles, a.K / kKc);
-    CUtensorMap amap, omap, omap16;
+    L.store_cols = L.ksplit > 1 ? 16 : 32;
+    CUtensorMap amap, omap;
     // activations [batch][K] int8: B-operand tiles {128 bytes of K, n_box sequences}, 128-byte swizzle
     if (int rc = encode_2d(&amap, CU_TENSOR_MAP_DATA_TYPE_UINT8, a8, (uint64_t)a.K, (uint64_t)a.batch, (uint64_t)a.K, kKc, (uint32_t)L.n_box,
                            CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
-    // output [batch][n_out] fp32: store tiles {128 (GLU: 64) rows of the weight matrix, n_box sequences}
+    // output [batch][n_out] fp32: store units {128 (GLU: 64) rows of the weight matrix, 32 sequences (16: the column
+    // blocks a cluster's CTAs store separately)}
     const uint64_t n_out = (uint64_t)(glu ? a.n_blocks / 2 : a.n_blocks) * 64;
     if (int rc = encode_2d(&omap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a.out, n_out, (uint64_t)a.batch, (uint64_t)a.out_stride * 4, glu ? 64u : 128u,
-                           (uint32_t)L.n_box, CU_TENSOR_MAP_SWIZZLE_NONE)) return rc;
-    // the same matrix in boxes of 16 sequences, for the column blocks a cluster's CTAs store separately
-    if (int rc = encode_2d(&omap16, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a.out, n_out, (uint64_t)a.batch, (uint64_t)a.out_stride * 4, glu ? 64u : 128u,
-                           16u, CU_TENSOR_MAP_SWIZZLE_NONE)) return rc;
+                           (uint32_t)L.store_cols, CU_TENSOR_MAP_SWIZZLE_NONE)) return rc;
     const size_t smem = UmmaSmem::bytes(L.n_box);
-    cudaError_t e = cudaFuncSetAttribute(tl1_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    using Kernel = void (*)(const UmmaLaunch, const CUtensorMap, const CUtensorMap);
+    const bool cl = L.ksplit > 1;
+    Kernel kernel = a.epilogue == TENZO_EPI_RELU2_GLU   ? (cl ? tl1_umma_kernel<TENZO_EPI_RELU2_GLU, true> : tl1_umma_kernel<TENZO_EPI_RELU2_GLU, false>)
+                    : a.epilogue == TENZO_EPI_RESIDUAL ? (cl ? tl1_umma_kernel<TENZO_EPI_RESIDUAL, true> : tl1_umma_kernel<TENZO_EPI_RESIDUAL, false>)
+                                                       : (cl ? tl1_umma_kernel<TENZO_EPI_STORE, true> : tl1_umma_kernel<TENZO_EPI_STORE, false>);
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)L.units, (unsigned)seq_tiles, (unsigned)L.ksplit);
@@ -445,7 +570,7 @@ int launch_tl1_umma(const tenzo_tl1_gemv_args& a, const int8_t* a8, const float*
     }
     cfg.attrs = attr;
     cfg.numAttrs = n_attr;
-    e = cudaLaunchKernelEx(&cfg, tl1_umma_kernel, L, amap, omap, omap16);
+    e = cudaLaunchKernelEx(&cfg, kernel, L, amap, omap);
     return e == cudaSuccess ? 0 : (int)e;
 }
 
@@ -458,6 +583,17 @@ int tl1_umma_take_timeouts() {
 }
 
 }  // namespace tz
+
+#ifdef TZ_UMMA_CHECK
+extern "C" __attribute__((visibility("default"))) int tenzo_check_umma(unsigned long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, tz::g_umma_check, sizeof(unsigned long long) * 4);
+}
+#endif
+#ifdef TZ_UMMA_TRACE
+extern "C" __attribute__((visibility("default"))) int tenzo_trace_umma(long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, tz::g_umma_trace, sizeof(long long) * 160 * 16);
+}
+#endif
 
 extern "C" int tenzo_cuda_tl1_gemm_ksplit(int n_blocks, int K, int batch, int epilogue) {
     if (n_blocks <= 0 || K < tz::kKc || K % tz::kKc || batch < 16) return 0;       // the tensor-core path does not apply
