@@ -61,14 +61,111 @@ __global__ void __launch_bounds__(kNqThreads) rmsnorm_quant_kernel(
 // even columns of column pairs 16*set + 4*i + t (byte i = 0..3), words[seq][set][t][1] the odd
 // columns unscaled; columns beyond K are zero. inv[seq] = max|y|/31. `words` may be null (tensor-core GEMM
 // path: it takes the plain int8 matrix a_out [batch][K] and sum_out[seq] = sum_k a_k instead).
+constexpr int kAqVec = 7;     // float4 values a thread of act_quant_kernel holds: rows up to 7168 floats stay in registers
+
 __global__ void __launch_bounds__(kNqThreads) act_quant_kernel(
     const float* x, const float* __restrict__ norm_w, int do_norm, float eps, int K, int x_stride,
     uint32_t* words, float* inv, int8_t* a_out, int* sum_out, int use_pdl) {
     extern __shared__ float s_y[];            // K floats + 32 scratch
     float* s_f = s_y + K;
     const int tid = threadIdx.x, seq = blockIdx.x;
-    if (use_pdl) pdl_wait();
+    // Let the GEMM that consumes this kernel's output start at once: its prologue (tensor-memory allocation, the first
+    // weight copies, expanding the first weight chunks) depends on nothing here and takes as long as this whole kernel;
+    // it waits for this grid's completion before it touches the activations.
+    if (use_pdl) pdl_launch_dependents();
     const float* xs = x + (size_t)seq * x_stride;
+    // The whole row in registers, every load in flight at once: a loop of load -> store to shared memory issues the
+    // loads one after the other (a later load may not pass an earlier store the compiler cannot tell apart), which made
+    // this kernel ten global-memory latencies long.
+    const bool vec = (K & 3) == 0 && K <= 4 * kAqVec * kNqThreads && (x_stride & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+                     (!norm_w || (reinterpret_cast<uintptr_t>(norm_w) & 15) == 0) && (!a_out || (reinterpret_cast<uintptr_t>(a_out) & 3) == 0);
+    if (vec) {
+        const int k4 = K >> 2;
+        float4 w4[kAqVec], v[kAqVec];
+        const bool has_w = do_norm && norm_w;
+        if (has_w) {                                    // model constants: no need to wait for the previous kernel
+#pragma unroll
+            for (int r = 0; r < kAqVec; ++r) {
+                const int i = tid + r * kNqThreads;
+                w4[r] = i < k4 ? __ldg(reinterpret_cast<const float4*>(norm_w) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+        if (use_pdl) pdl_wait();
+#pragma unroll
+        for (int r = 0; r < kAqVec; ++r) {
+            const int i = tid + r * kNqThreads;
+            v[r] = i < k4 ? __ldcg(reinterpret_cast<const float4*>(xs) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        float m = 0.0f;
+        if (do_norm) {
+#pragma unroll
+            for (int r = 0; r < kAqVec; ++r) {
+                const int i = tid + r * kNqThreads;
+                if (i < k4) reinterpret_cast<float4*>(s_y)[i] = v[r];
+            }
+            __syncthreads();
+            const float ss = sumsq_reference_order(s_y, K, s_f);
+            const float inv_rms = rms_inv(ss, K, eps);
+#pragma unroll
+            for (int r = 0; r < kAqVec; ++r) {          // y = (x * inv_rms) * w, left to right (rms_apply)
+                v[r].x *= inv_rms; v[r].y *= inv_rms; v[r].z *= inv_rms; v[r].w *= inv_rms;
+                if (has_w) { v[r].x *= w4[r].x; v[r].y *= w4[r].y; v[r].z *= w4[r].z; v[r].w *= w4[r].w; }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < kAqVec; ++r) m = fmaxf(fmaxf(m, fmaxf(fabsf(v[r].x), fabsf(v[r].y))), fmaxf(fabsf(v[r].z), fabsf(v[r].w)));
+        m = fmaxf(block_max(m, s_f), 1e-6f);      // TenzoEngine.cpp:28-32
+        const float to_q = 31.0f / m;             // :34
+        if (tid == 0) inv[seq] = m / 31.0f;       // :35
+        if (words) {                              // the packed fragments gather arbitrary columns: through shared memory
+            __syncthreads();
+#pragma unroll
+            for (int r = 0; r < kAqVec; ++r) {
+                const int i = tid + r * kNqThreads;
+                if (i < k4) reinterpret_cast<float4*>(s_y)[i] = v[r];
+            }
+            __syncthreads();
+            const int nsets = ((K >> 1) + 15) / 16;
+            for (int wd = tid; wd < nsets * 8; wd += kNqThreads) {
+                const int s = wd >> 3, tt = (wd >> 1) & 3, odd = wd & 1;
+                uint32_t word = 0;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int col = 2 * (16 * s + 4 * i + tt) + odd;
+                    const int q = col < K ? (int)roundf(s_y[col] * to_q) : 0;   // :41-42
+                    word |= (uint32_t)(uint8_t)(int8_t)(odd ? q : 4 * q) << (8 * i);
+                }
+                words[(size_t)seq * nsets * 8 + wd] = word;
+            }
+        }
+        if (a_out || sum_out) {
+            int part = 0;
+#pragma unroll
+            for (int r = 0; r < kAqVec; ++r) {
+                const int i = tid + r * kNqThreads;
+                const int q0 = (int)roundf(v[r].x * to_q), q1 = (int)roundf(v[r].y * to_q), q2 = (int)roundf(v[r].z * to_q), q3 = (int)roundf(v[r].w * to_q);
+                if (i < k4) {
+                    if (a_out)
+                        reinterpret_cast<uint32_t*>(a_out + (size_t)seq * K)[i] =
+                            (uint32_t)(uint8_t)(int8_t)q0 | ((uint32_t)(uint8_t)(int8_t)q1 << 8) | ((uint32_t)(uint8_t)(int8_t)q2 << 16) | ((uint32_t)(uint8_t)(int8_t)q3 << 24);
+                    part += q0 + q1 + q2 + q3;
+                }
+            }
+            if (sum_out) {                        // sum_k a_k, for kernels that multiply by the unsigned codes w+1
+                int* s_i = reinterpret_cast<int*>(s_f);
+                __syncthreads();
+                if (tid == 0) s_i[0] = 0;
+                __syncthreads();
+                part = __reduce_add_sync(0xffffffffu, part);
+                if ((tid & 31) == 0) atomicAdd(&s_i[0], part);
+                __syncthreads();
+                if (tid == 0) sum_out[seq] = s_i[0];
+            }
+        }
+        return;
+    }
+    // rows that are longer, or not aligned for 16-byte loads: element by element through shared memory
+    if (use_pdl) pdl_wait();
     for (int i = tid; i < K; i += kNqThreads) s_y[i] = __ldcg(xs + i);
     __syncthreads();
     float m = 0.0f;
@@ -85,7 +182,6 @@ __global__ void __launch_bounds__(kNqThreads) act_quant_kernel(
     }
     m = fmaxf(block_max(m, s_f), 1e-6f);      // TenzoEngine.cpp:28-32
     const float to_q = 31.0f / m;             // :34
-    if (use_pdl) pdl_launch_dependents();
     const int nsets = ((K >> 1) + 15) / 16;
     for (int wd = tid; words && wd < nsets * 8; wd += kNqThreads) {
         const int s = wd >> 3, tt = (wd >> 1) & 3, odd = wd & 1;

@@ -55,8 +55,8 @@ constexpr int kExpandGroups = 4;               // groups of four warps that expa
 constexpr int kUmmaThreads = 32 * (2 + 4 * kExpandGroups + 3);   // warp 0 producer, warp 1 and the last three MMA issue, the rest expand
 constexpr int kMmaThreads = 4;
 constexpr int kMaxSlots = 16;                  // ring of chunk slots: as many as tensor memory and shared memory allow (4 at 256 sequences, 12 at 64)
-constexpr int kPGroup = 4;                     // chunks of packed weights per bulk copy (8 KB per row block)
-constexpr int kMaxPGroups = 4;                 // such groups in the ring: up to 64 KB of packed weights in flight
+constexpr int kPGroup = 8;                     // chunks of packed weights per bulk copy (16 KB per row block)
+constexpr int kMaxPGroups = 3;                 // such groups in the ring (3 up to 64 sequences, else 2): 64 KB of packed weights in flight behind the group in use
 constexpr int kKc = 128;                       // bytes of K per chunk (one swizzle atom row)
 constexpr int kTileRows = 128;
 constexpr int kPBytes = 2 * (kKc / 2) * 32;    // packed weights of one chunk, two row blocks: 4 KB
@@ -83,9 +83,12 @@ __device__ int g_umma_timeouts = 0;
 #ifdef TZ_UMMA_TRACE
 __device__ long long g_umma_trace[160 * 16];
 #define UT(i) (g_umma_trace[(blockIdx.x % 160) * 16 + (i)] = clock64())
+__device__ long long g_umma_chunks[64 * 8];      // CTA 0: per chunk, when each role reached it
+#define UC(j, k) do { if (blockIdx.x == 0 && blockIdx.z == 0 && (j) < 64) g_umma_chunks[(j) * 8 + (k)] = clock64(); } while (0)
 #define UTG(i) do { long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); g_umma_trace[(blockIdx.x % 160) * 16 + (i)] = t_; } while (0)
 #else
 #define UT(i) ((void)0)
+#define UC(j, k) ((void)0)
 #define UTG(i) ((void)0)
 #endif
 
@@ -108,8 +111,8 @@ __device__ __forceinline__ float umma_seg_scale(const tenzo_tl1_gemv_args& a, in
 }
 
 struct UmmaSmem {
-    // [1024-aligned] ring n_slots x { B n_box*128 } | packed ring n_pgroups x 2 blocks x 8 KB | barriers | tmem slot | inv[256] | sum_a[256]
-    static __host__ __device__ int pgroups_for(int) { return kMaxPGroups; }
+    // [1024-aligned] ring n_slots x { B n_box*128 } | packed ring n_pgroups x 2 blocks x 16 KB | barriers | tmem slot | inv[256] | sum_a[256]
+    static __host__ __device__ int pgroups_for(int n_box) { return n_box <= 64 ? kMaxPGroups : 2; }
     static __host__ __device__ int tmem_a(int n_box) { return (n_box + 31) & ~31; }          // first column of the A slots
     static __host__ __device__ int slots_for(int n_box) {
         const int by_tmem = (kTmemCols - tmem_a(n_box)) / 32, by_smem = (kSmemBudget - pgroups_for(n_box) * kPGroup * kPBytes) / (n_box * kKc);
@@ -218,7 +221,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) tl1_umma_kernel(const UmmaLau
 
     const size_t blk_bytes = (size_t)(a.K / 2) * 32;
     const int n_groups = (n_chunks + kPGroup - 1) / kPGroup;
-    auto request_group = [&](int g) {                      // packed weights of chunks 8g .. 8g+7, both row blocks
+    auto request_group = [&](int g) {                      // packed weights of chunks kPGroup*g .. kPGroup*g + kPGroup-1, both row blocks
         const int slot = g % PG;
         const int chunks = min(kPGroup, n_chunks - g * kPGroup);
         const unsigned bytes = (unsigned)chunks * (kPBytes / 2);
@@ -229,20 +232,20 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) tl1_umma_kernel(const UmmaLau
         bulk_g2s(sP, a.w + (size_t)blk0 * blk_bytes + k_off, bytes, &bar_p[slot]);
         if (blk1 >= 0) bulk_g2s(sP + kPGroup * (kPBytes / 2), a.w + (size_t)blk1 * blk_bytes + k_off, bytes, &bar_p[slot]);
     };
-    if (tid == 0) {
+    if (warp == 0 && lane < PG) {
         // The weights depend on no earlier kernel and their latency is the longest in the prologue: ask for the first
-        // two groups before anything else (an mbarrier operation costs its thread about a hundred cycles, so the
-        // other barriers are initialised by other threads meanwhile).
-        for (int g = 0; g < PG; ++g) mbar_init(&bar_p[g], 1);
+        // groups before anything else, one lane per group (an mbarrier operation or a bulk-copy issue costs its thread
+        // over a hundred cycles; the other barriers are initialised by another warp meanwhile).
+        mbar_init(&bar_p[lane], 1);
         mbar_init_fence();
-        for (int g = 0; g < n_groups && g < PG; ++g) request_group(g);
-        UT(2);
+        if (lane < n_groups) request_group(lane);
+        if (lane == 0) UT(2);
     } else if (warp == 2) {
         if (lane < R) {
             mbar_init(&bar_full[lane], 5);             // four expanding warps + the expect_tx of the warp that requests the activation tile
             mbar_init(&bar_empty[lane], 1);
         } else if (lane >= 16 && lane < 16 + kMaxPGroups) {
-            mbar_init(&bar_pfree[lane - 16], 4 * kPGroup);
+            mbar_init(&bar_pfree[lane - 16], 4 * kExpandGroups * (R >= 8 ? 1 : 2));   // one arrival per expanding warp per iteration
         } else if (lane == 24) {
             mbar_init(bar_accum, kMmaThreads);
         } else if (lane == 25) {
@@ -292,9 +295,10 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) tl1_umma_kernel(const UmmaLau
             if (mma_t > 0 && mma_t < n_chunks && !mbar_spin_bounded(bar_first, 0u)) timed_out = true;
             for (int j = mma_t; j < n_chunks && !timed_out; j += kMmaThreads) {
                 const int s = j % R, use = j / R;
+                UC(j, 4);
                 if (!mbar_spin_bounded(&bar_full[s], (unsigned)use & 1u)) { timed_out = true; break; }
                 tc_fence_after();
-                if (j == 16) UT(5);
+                UC(j, 5);
                 const uint32_t ta = tmem_base + tmem_a0 + (uint32_t)(32 * s);
                 const uint64_t db = umma_desc_sw128(smem_addr(ring + (size_t)s * slot_bytes));
                 if (UCHK(tmem_a0 + 32 * s + 32 <= (uint32_t)kTmemCols && s < R && ring + (size_t)(s + 1) * slot_bytes <= pring, 5, s, j))
@@ -302,6 +306,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) tl1_umma_kernel(const UmmaLau
                 for (int k4 = 0; k4 < kKc / 32; ++k4)
                     umma_i8_ta(tmem_base, ta + (uint32_t)(8 * k4), db + (uint64_t)(2 * k4), idesc, (j > 0 || k4 > 0) ? 1u : 0u);
                 umma_commit(&bar_empty[s]);
+                UC(j, 6);
                 if (j == 0) umma_commit(bar_first);
             }
             umma_commit(bar_accum);
@@ -321,67 +326,94 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) tl1_umma_kernel(const UmmaLau
         int woff[4];                                           // word offsets of the four loads inside a 16-column-pair set
 #pragma unroll
         for (int u = 0; u < 4; ++u) woff[u] = (4 * t + (u ^ t)) * 8 + g;
+        // An iteration costs a warp about two thousand cycles whatever it expands (a poll of a barrier that has long
+        // completed is 300 cycles, a tensor-memory store 500 until it has landed), so with eight or more slots it takes
+        // two chunks, j and j + 4: one poll for both slots (the same thread issues both chunks' MMAs in order, so the
+        // later one's completion implies the earlier one's), one for the weights (both lie in the same group of eight),
+        // the two polls on different lanes, one wait for the four stores.
+        const int cpi = R >= 8 ? 2 : 1;
         int seen_group = -1;
-        for (int j = grp; j < n_chunks; j += kExpandGroups) {
-            const int s = j % R, use = j / R, ps = (j / kPGroup) % PG, puse = (j / kPGroup) / PG;
+        for (int it = 0, j0 = grp; j0 < n_chunks; ++it, j0 += kExpandGroups * cpi) {
+            const int n_here = (cpi == 2 && j0 + kExpandGroups < n_chunks) ? 2 : 1;
+            const int j_last = j0 + kExpandGroups * (n_here - 1);
+            const int pg = j0 / kPGroup, ps = pg % PG, puse = pg / PG;
             bool ok = true;
-            if (j == 16 && tid == 64) UT(3);
-            if (lane == 0) ok = (use == 0 || mbar_spin_bounded(&bar_empty[s], (unsigned)(use - 1) & 1u));
-            if (j == 16 && tid == 64) UT(12);
-            const int turn = j / kExpandGroups;
-            if (lane == 0 && ok && (turn & 3) == q) {           // the group's warps take turns requesting the activation tile
-                if (a.use_pdl && turn < 4) pdl_wait();          // it comes from the previous kernel (first turn of each warp)
-                if (UCHK(s < R && ring + (size_t)(s + 1) * slot_bytes <= pring, 2, s, j)) {
-                mbar_expect_tx(&bar_full[s], (unsigned)slot_bytes);
-                tma_load_2d(ring + (size_t)s * slot_bytes, &amap, (c_begin + j) * kKc, seq0, &bar_full[s]);
-                }
+            if (lane == 0 && q == 0) { UC(j0, 0); if (n_here == 2) UC(j0 + kExpandGroups, 0); }
+            if (lane == 0) {
+                const int s = j_last % R, use = j_last / R;
+                ok = use == 0 || mbar_spin_bounded(&bar_empty[s], (unsigned)(use - 1) & 1u);
+            } else if (lane == 1 && pg != seen_group) {
+                ok = mbar_spin_bounded(&bar_p[ps], (unsigned)puse & 1u);
             }
-            if (lane == 0 && ok && (j / kPGroup != seen_group)) ok = mbar_spin_bounded(&bar_p[ps], (unsigned)puse & 1u);
-            seen_group = j / kPGroup;
-            if (j == 0 && tid == 64) UT(6);
-            ok = __shfl_sync(0xffffffffu, ok, 0);
+            seen_group = pg;
+            ok = __all_sync(0xffffffffu, ok);
+            if (j0 == 0 && tid == 64) UT(6);
             if (!ok) { timed_out = true; break; }
             tc_fence_after();
-            if (j == 16 && tid == 64) UT(13);
-            const uint32_t* sP = reinterpret_cast<const uint32_t*>(pring + (size_t)ps * kPGroup * kPBytes + (size_t)blk * kPGroup * (kPBytes / 2) +
-                                                                   (size_t)(j % kPGroup) * (kPBytes / 2));
-            uint32_t W[16];
-            const bool sp_ok = UCHK(reinterpret_cast<const unsigned char*>(sP) >= pring && reinterpret_cast<const unsigned char*>(sP + 512) <= reinterpret_cast<unsigned char*>(bars), 3,
-                                    reinterpret_cast<const unsigned char*>(sP) - smem_raw, j);
+            if (lane == 0 && q == 0) { UC(j0, 1); if (n_here == 2) UC(j0 + kExpandGroups, 1); }
+            // The group's warps take turns requesting the activation tiles. They come from the previous kernel, so in the
+            // first iteration the request (and the wait for that kernel) is left until the chunks have been expanded:
+            // the weights depend on nothing, and the previous kernel runs about as long as the first round of expansion.
+            auto request_tiles = [&]() {
+                for (int c = 0; c < n_here; ++c) {
+                    const int j = j0 + kExpandGroups * c, s = j % R;
+                    if (lane == 0 && ((it * cpi + c) & 3) == q) {
+                        if (UCHK(s < R && ring + (size_t)(s + 1) * slot_bytes <= pring, 2, s, j)) {
+                            mbar_expect_tx(&bar_full[s], (unsigned)slot_bytes);
+                            tma_load_2d(ring + (size_t)s * slot_bytes, &amap, (c_begin + j) * kKc, seq0, &bar_full[s]);
+                        }
+                    }
+                }
+            };
+            const bool request_last = it == 0 && a.use_pdl;
+            if (!request_last) request_tiles();
+            for (int c = 0; c < n_here; ++c) {
+                const int j = j0 + kExpandGroups * c, s = j % R;
+                const uint32_t* sP = reinterpret_cast<const uint32_t*>(pring + (size_t)ps * kPGroup * kPBytes + (size_t)blk * kPGroup * (kPBytes / 2) +
+                                                                       (size_t)(j % kPGroup) * (kPBytes / 2));
+                uint32_t W[16];
+                const bool sp_ok = UCHK(reinterpret_cast<const unsigned char*>(sP) >= pring && reinterpret_cast<const unsigned char*>(sP + 512) <= reinterpret_cast<unsigned char*>(bars), 3,
+                                        reinterpret_cast<const unsigned char*>(sP) - smem_raw, j);
 #pragma unroll
-            for (int n = 0; n < 4; ++n)
+                for (int n = 0; n < 4; ++n)
 #pragma unroll
-                for (int u = 0; u < 4; ++u) W[4 * n + u] = (have && sp_ok) ? sP[n * 128 + woff[u]] : 0u;
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bar_pfree[ps]);   // the packed chunk has been consumed into registers
-            uint32_t lo[16], up[16];                       // registers of the two stores: lanes 0-15 (jj = 0, 1) and 16-31 (jj = 2, 3)
+                    for (int u = 0; u < 4; ++u) W[4 * n + u] = (have && sp_ok) ? sP[n * 128 + woff[u]] : 0u;
+                if (c == n_here - 1) {
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bar_pfree[ps]);   // the packed chunks have been consumed into registers
+                }
+                uint32_t lo[16], up[16];                       // registers of the two stores: lanes 0-15 (jj = 0, 1) and 16-31 (jj = 2, 3)
 #pragma unroll
-            for (int n = 0; n < 4; ++n) {
-                // 4x4 byte transpose: T[jj] = byte jj of the words of column pairs 16n + 4t + 0..3
-                const uint32_t p0 = prmt(W[4 * n], W[4 * n + 1], sel_a), p1 = prmt(W[4 * n + 2], W[4 * n + 3], sel_a);
-                const uint32_t p2 = prmt(W[4 * n], W[4 * n + 1], sel_b), p3 = prmt(W[4 * n + 2], W[4 * n + 3], sel_b);
-                const uint32_t T[4] = {prmt(p0, p1, sel_lo), prmt(p0, p1, sel_hi), prmt(p2, p3, sel_lo), prmt(p2, p3, sel_hi)};
+                for (int n = 0; n < 4; ++n) {
+                    // 4x4 byte transpose: T[jj] = byte jj of the words of column pairs 16n + 4t + 0..3
+                    const uint32_t p0 = prmt(W[4 * n], W[4 * n + 1], sel_a), p1 = prmt(W[4 * n + 2], W[4 * n + 3], sel_a);
+                    const uint32_t p2 = prmt(W[4 * n], W[4 * n + 1], sel_b), p3 = prmt(W[4 * n + 2], W[4 * n + 3], sel_b);
+                    const uint32_t T[4] = {prmt(p0, p1, sel_lo), prmt(p0, p1, sel_hi), prmt(p2, p3, sel_lo), prmt(p2, p3, sel_hi)};
 #pragma unroll
-                for (int jj = 0; jj < 4; ++jj) {
-                    const uint32_t nb = T[jj] >> (4 * hi);
-                    const uint32_t e = nb & 0x03030303u, o = (nb >> 2) & 0x03030303u;    // codes of the even / odd columns
-                    uint32_t* dst = (jj < 2 ? lo : up) + 4 * n + 2 * (jj & 1);
-                    dst[0] = prmt(e, o, 0x5140u);
-                    dst[1] = prmt(e, o, 0x7362u);
+                    for (int jj = 0; jj < 4; ++jj) {
+                        const uint32_t nb = T[jj] >> (4 * hi);
+                        const uint32_t e = nb & 0x03030303u, o = (nb >> 2) & 0x03030303u;    // codes of the even / odd columns
+                        uint32_t* dst = (jj < 2 ? lo : up) + 4 * n + 2 * (jj & 1);
+                        dst[0] = prmt(e, o, 0x5140u);
+                        dst[1] = prmt(e, o, 0x7362u);
+                    }
+                }
+                const uint32_t ta = tmem_base + tmem_a0 + (uint32_t)(32 * s) + ((uint32_t)(32 * q) << 16);
+                if (UCHK(tmem_a0 + 32 * s + 32 <= (uint32_t)kTmemCols && (tmem_base & 0xffffu) == 0u, 4, tmem_a0 + 32 * s, tmem_base)) {
+                    tmem_st_16x256b_x4(ta, lo);
+                    tmem_st_16x256b_x4(ta + (16u << 16), up);
                 }
             }
-            const uint32_t ta = tmem_base + tmem_a0 + (uint32_t)(32 * s) + ((uint32_t)(32 * q) << 16);
-            if (j == 16 && tid == 64) UT(14);
-            if (UCHK(tmem_a0 + 32 * s + 32 <= (uint32_t)kTmemCols && (tmem_base & 0xffffu) == 0u, 4, tmem_a0 + 32 * s, tmem_base)) {
-            tmem_st_16x256b_x4(ta, lo);
-            tmem_st_16x256b_x4(ta + (16u << 16), up);
+            if (lane == 0 && q == 0) { UC(j0, 2); if (n_here == 2) UC(j0 + kExpandGroups, 2); }
+            if (request_last) {
+                if (lane == 0) pdl_wait();
+                request_tiles();
             }
             tmem_wait_st();
-            if (j == 16 && tid == 64) UT(15);
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&bar_full[s]);
-            if (j == 12 && tid == 64) UT(4);
+            if (lane < n_here) mbar_arrive(&bar_full[(j0 + kExpandGroups * lane) % R]);
+            if (lane == 0 && q == 0) { UC(j0, 3); if (n_here == 2) UC(j0 + kExpandGroups, 3); }
         }
         // ---- all of this CTA's MMAs have completed; in a cluster it parks its partial tile [N][128 TMEM lanes] int32
         //      (the column blocks its peers will reduce) in the ring memory the pipeline no longer needs -----------------
@@ -592,6 +624,9 @@ extern "C" __attribute__((visibility("default"))) int tenzo_check_umma(unsigned 
 #ifdef TZ_UMMA_TRACE
 extern "C" __attribute__((visibility("default"))) int tenzo_trace_umma(long long* out) {
     return (int)cudaMemcpyFromSymbol(out, tz::g_umma_trace, sizeof(long long) * 160 * 16);
+}
+extern "C" __attribute__((visibility("default"))) int tenzo_trace_umma_chunks(long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, tz::g_umma_chunks, sizeof(long long) * 64 * 8);
 }
 #endif
 
