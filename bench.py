@@ -520,6 +520,9 @@ def main():
     ap.add_argument("--heads-per-cta", type=int, default=0)
     ap.add_argument("--gemm-rows", type=int, default=13824, help="gemm workload: output rows of the TL1 matrix (multiple of 128)")
     ap.add_argument("--gemm-k", type=int, default=2560, help="gemm workload: K of the TL1 matrix (multiple of 128)")
+    ap.add_argument("--gemm-epilogue", choices=["model", "store", "residual", "glu"], default="model",
+                    help="gemm workload: epilogue of the call; 'model' = what the 2B layer uses for the shape (13824 rows: ReLU^2*GLU of the "
+                         "gate|up halves; 2560 rows: + residual; else plain store)")
     ap.add_argument("--kv-mode", default="int8_fused", choices=["int8_fused", "paged_int8"], help="decode workloads: KV cache mode")
     ap.add_argument("--no-prefetch", action="store_true", help="gemv/gemm workloads: do not ask L2 for the next matrix (for DRAM-traffic captures)")
     args = ap.parse_args()

@@ -154,18 +154,27 @@ def run_gemm(args):
     N, K = args.gemm_rows, args.gemm_k
     n_mat = max(16, min(128, (160 << 20) // (N * K // 4) + 1))     # distinct matrices per step: more bytes than L2 holds
     B = args.batch
+    epi = getattr(args, "gemm_epilogue", "model")
+    if epi == "model":                                   # what the 2B layer does with a matrix of this height
+        epi = "glu" if N == 13824 else "residual" if N == 2560 else "store"
+    epilogue = {"store": kernels.EPI_STORE, "residual": kernels.EPI_RESIDUAL, "glu": kernels.EPI_RELU2_GLU}[epi]
     ws = [_random_tl1_device(N * K // 4, 200 + i) for i in range(n_mat)]
-    x = torch.randn(B, K, device="cuda", generator=torch.Generator(device="cuda").manual_seed(3))
-    out = torch.empty(B, N, device="cuda")
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn(B, K, device="cuda", generator=g)
+    norm_w = 1.0 + 0.1 * torch.randn(K, device="cuda", generator=g)      # every TL1 product of the layer has an RMSNorm in front
+    n_out = N // 2 if epi == "glu" else N
+    out = torch.empty(B, n_out, device="cuda")
+    resid = torch.randn(B, n_out, device="cuda", generator=g) if epi == "residual" else None
+    call = dict(epilogue=epilogue, resid=resid, norm_w=norm_w, do_norm=True, out=out, use_pdl=bool(args.pdl))
     stream = torch.cuda.Stream()
     with torch.cuda.stream(stream):
         for w in ws[:2]:
-            kernels.tl1_gemv(x, w, N // 64, K, [0.016], out=out, use_pdl=bool(args.pdl))
+            kernels.tl1_gemv(x, w, N // 64, K, [0.016], **call)
         stream.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
             for i, w in enumerate(ws):
-                kernels.tl1_gemv(x, w, N // 64, K, [0.016], out=out, use_pdl=bool(args.pdl), prefetch=None if args.no_prefetch else ws[(i + 1) % n_mat])
+                kernels.tl1_gemv(x, w, N // 64, K, [0.016], prefetch=None if args.no_prefetch else ws[(i + 1) % n_mat], **call)
         for _ in range(max(3, args.warmup)):
             graph.replay()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -185,7 +194,7 @@ def run_gemm(args):
     print(json.dumps({
         "metric": "tl1_gemm_tops", "value": tops, "unit": "TOP/s", "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup),
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8 x s8 -> s32",
-        "data": "synthetic", "config": {"workload": f"gemm: TL1 bitlinear {N}x{K} for {B} sequences (absmax quantiser + tcgen05 GEMM), "
+        "data": "synthetic", "config": {"workload": f"gemm: TL1 bitlinear {N}x{K} for {B} sequences (RMSNorm + absmax quantiser, tcgen05 GEMM, {epi} epilogue), "
                                                     f"{n_mat} distinct matrices per step ({n_mat * N * K // 4 / 1e6:.0f} MB > L2)", "pdl": int(args.pdl)},
         "gpu_launches": 2 * calls,
         "roofline": {"bound": "tensor", "kernel": "act_quant_kernel + tl1_umma_kernel", "achieved": tops, "peak": peak[0], "peak_source": peak[1],

@@ -26,6 +26,7 @@
 #include <cuda_fp16.h>
 
 #include <cstring>
+#include <utility>
 
 #include "attn_common.cuh"
 #include "common.cuh"
@@ -78,6 +79,10 @@ __device__ __forceinline__ void fa_mma_f16(float (&d)[4], uint32_t a0, uint32_t 
 // New token's K (rotated) and V rows: quantise and store at pos[seq] (:459-533), one warp per (sequence, kv head, K|V).
 __global__ void __launch_bounds__(64) fa_append_kernel(const tenzo_attention_args a) {
     const int seq = blockIdx.x, kvh = blockIdx.y, is_v = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (a.use_pdl) {                         // resident while the previous kernel drains; nothing is touched before it has completed
+        pdl_launch_dependents();
+        pdl_wait();
+    }
     const int pos = a.pos[seq];
     if (pos < 0 || pos >= a.max_seq) return;
     const float* src = (is_v ? a.v : a.k) + (size_t)seq * a.kv_stride + (size_t)kvh * kHd;
@@ -127,6 +132,10 @@ __global__ void __launch_bounds__(kFaThreads, 2) attn_fast_kernel(const FaLaunch
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t4 = lane & 3;
     const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
+    if (a.use_pdl) {
+        pdl_launch_dependents();
+        pdl_wait();
+    }
     const int pos = a.pos[seq];
     const int T = pos + 1;
     const int c_begin = split * L.split_keys, c_end = min(T, c_begin + L.split_keys);
@@ -334,6 +343,10 @@ __global__ void __launch_bounds__(128) attn_fast_merge_kernel(const FaLaunch L) 
     const tenzo_attention_args& a = L.a;
     const int G = L.group;
     const int kvh = blockIdx.x, seq = blockIdx.y;
+    if (a.use_pdl) {
+        pdl_launch_dependents();
+        pdl_wait();
+    }
     const size_t item0 = ((size_t)seq * a.n_kv + kvh) * L.n_splits;
     for (int idx = threadIdx.x; idx < G * kHd; idx += blockDim.x) {
         const int h = idx / kHd, d = idx % kHd;
@@ -392,13 +405,29 @@ static void fa_pick_split(int batch, int n_kv, int max_len, int* n_splits, int* 
     *n_splits = (max_len + keys - 1) / keys;
 }
 
+// Launch with (or without) the programmatic-serialisation attribute: the kernel may become resident while its
+// predecessor drains, and waits for it (griddepcontrol.wait) before its first global access.
+template <typename... KArgs, typename... Args>
+static cudaError_t fa_launch_ex(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
 template <int G>
 static int fa_launch(const FaLaunch& L, const CUtensorMap& km, const CUtensorMap& vm, cudaStream_t st) {
     const size_t smem = fa_smem_bytes();
     cudaError_t e = cudaFuncSetAttribute(attn_fast_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    attn_fast_kernel<G><<<dim3((unsigned)L.n_splits, (unsigned)L.a.n_kv, (unsigned)L.a.batch), kFaThreads, smem, st>>>(L, km, vm);
-    e = cudaGetLastError();
+    e = fa_launch_ex(attn_fast_kernel<G>, dim3((unsigned)L.n_splits, (unsigned)L.a.n_kv, (unsigned)L.a.batch), dim3(kFaThreads), smem, st, L.a.use_pdl != 0, L, km, vm);
     return e == cudaSuccess ? 0 : (int)e;
 }
 
@@ -429,8 +458,7 @@ int attn_fast_run(const tenzo_attention_args& a, cudaStream_t st) {
     L.part_o = static_cast<float*>(a.workspace);
     L.part_ml = L.part_o + items * L.group * kHd;
     if (a.append) {
-        fa_append_kernel<<<dim3((unsigned)a.batch, (unsigned)a.n_kv), 64, 0, st>>>(L.a);
-        if (cudaGetLastError() != cudaSuccess) return (int)cudaErrorLaunchFailure;
+        if (fa_launch_ex(fa_append_kernel, dim3((unsigned)a.batch, (unsigned)a.n_kv), dim3(64), 0, st, a.use_pdl != 0, L.a) != cudaSuccess) return (int)cudaErrorLaunchFailure;
     }
     CUtensorMap km, vm;
     std::memset(&km, 0, sizeof km);
@@ -446,8 +474,7 @@ int attn_fast_run(const tenzo_attention_args& a, cudaStream_t st) {
     }
     if (rc) return rc;
     if (L.n_splits > 1) {
-        attn_fast_merge_kernel<<<dim3((unsigned)a.n_kv, (unsigned)a.batch), 128, 0, st>>>(L);
-        if (cudaGetLastError() != cudaSuccess) return (int)cudaErrorLaunchFailure;
+        if (fa_launch_ex(attn_fast_merge_kernel, dim3((unsigned)a.n_kv, (unsigned)a.batch), dim3(128), 0, st, a.use_pdl != 0, L) != cudaSuccess) return (int)cudaErrorLaunchFailure;
     }
     return 0;
 }
