@@ -74,9 +74,9 @@ __global__ void __launch_bounds__(kNqThreads) act_quant_kernel(
     // it waits for this grid's completion before it touches the activations.
     if (use_pdl) pdl_launch_dependents();
     const float* xs = x + (size_t)seq * x_stride;
-    // The whole row in registers, every load in flight at once: a loop of load -> store to shared memory issues the
-    // loads one after the other (a later load may not pass an earlier store the compiler cannot tell apart), which made
-    // this kernel ten global-memory latencies long.
+    // The whole row in registers as 16-byte loads, all in flight at once; shared memory is only touched where another
+    // thread needs the value (the sum of squares in reference order, the packed fragments of the mma.sync path), instead
+    // of four passes over a staged copy.
     const bool vec = (K & 3) == 0 && K <= 4 * kAqVec * kNqThreads && (x_stride & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
                      (!norm_w || (reinterpret_cast<uintptr_t>(norm_w) & 15) == 0) && (!a_out || (reinterpret_cast<uintptr_t>(a_out) & 3) == 0);
     if (vec) {
