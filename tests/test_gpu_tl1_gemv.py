@@ -175,14 +175,16 @@ def test_tensor_core_path_bit_exact(cuda_lib, N, K, batch):
         assert np.array_equal(host(r["out"])[b], out), "fp32 outputs differ"
 
 
-@pytest.mark.parametrize("h", [512, 2048])
-def test_tensor_core_path_epilogues_match_single_sequence_path(cuda_lib, h):
-    """Segment scales + fused norm, residual and ReLU^2*GLU epilogues at 48 sequences against the same
-    launches made one sequence at a time (already pinned to the oracle above). At h = 2048 every one of them
-    splits K across a cluster of four CTAs."""
+@pytest.mark.parametrize("h,B", [(512, 48), (2048, 48), (2048, 144), (512, 240), (2048, 256)])
+def test_tensor_core_path_epilogues_match_single_sequence_path(cuda_lib, h, B):
+    """Segment scales + fused norm, residual and ReLU^2*GLU epilogues against the same launches made one sequence at a
+    time (already pinned to the oracle above). At h = 2048 every one of them splits K across a cluster of four CTAs.
+    48, 144 and 240 sequences leave an odd number of 16-sequence column blocks (a store unit of one block, ranks of a
+    cluster owning different numbers of blocks); above 128 sequences the kernel runs with four ring slots instead of
+    eight or twelve and one chunk per expand iteration."""
     from tenzo_b200 import kernels
-    f, B = 704, 48
-    rng = np.random.default_rng(46)
+    f = 704
+    rng = np.random.default_rng([46, h, B])
     x = rng.standard_normal((B, h)).astype(np.float32)
     res = rng.standard_normal((B, h)).astype(np.float32)
     nw = (1 + 0.1 * rng.standard_normal(h)).astype(np.float32)
@@ -199,9 +201,57 @@ def test_tensor_core_path_epilogues_match_single_sequence_path(cuda_lib, h):
 
     big = launches(dx, dres)
     torch.cuda.synchronize()
-    for b in [0, 7, 16, 33, 47]:
+    for b in sorted({0, 7, 16, 33, 47, B // 2, B - 17, B - 1}):
         one = launches(dx[b:b + 1].contiguous(), dres[b:b + 1].contiguous())
         torch.cuda.synchronize()
         for got, want, name in zip(big, one, ("residual", "glu", "qkv")):
             assert np.array_equal(host(got)[b], host(want)[0]), f"{name} epilogue differs at sequence {b}"
     assert cuda_lib.tenzo_cuda_tl1_gemv_take_timeouts() == 0
+
+
+def test_many_row_tiles_without_a_cluster_and_more_than_128_sequences(cuda_lib):
+    """150 row blocks (more tiles than half the SMs: one CTA per tile, no cluster) at 160 sequences: plain store and
+    GLU against the one-sequence path."""
+    from tenzo_b200 import kernels
+    N, K, B = 9600, 256, 160
+    rng = np.random.default_rng(48)
+    w = dev(synth.random_tl1_packed(rng, N, K))
+    x = dev(rng.standard_normal((B, K)).astype(np.float32))
+    assert cuda_lib.tenzo_cuda_tl1_gemm_ksplit(N // 64, K, B, kernels.EPI_STORE) == 1
+
+    def launches(xs):
+        s = kernels.tl1_gemv(xs, w, N // 64, K, [0.02])["out"]
+        g = kernels.tl1_gemv(xs, w, N // 64, K, [0.02, 0.03], [N // 128, N // 64, N // 64], epilogue=kernels.EPI_RELU2_GLU)["out"]
+        return s, g
+
+    big = launches(x)
+    torch.cuda.synchronize()
+    for b in [0, 15, 16, 127, 128, 143, 159]:
+        one = launches(x[b:b + 1].contiguous())
+        torch.cuda.synchronize()
+        for got, want, name in zip(big, one, ("store", "glu")):
+            assert np.array_equal(host(got)[b], host(want)[0]), f"{name} differs at sequence {b}"
+    assert cuda_lib.tenzo_cuda_tl1_gemv_take_timeouts() == 0
+
+
+@pytest.mark.parametrize("batch", [3, 17])
+def test_quantiser_paths_agree_on_misaligned_rows(cuda_lib, batch):
+    """The batched quantiser keeps 16-byte-aligned rows in registers and walks others element by element: the same
+    numbers through an aligned and a 4-byte-shifted buffer give the same quantised activations, scales and products
+    (3 sequences: packed mma.sync fragments; 17: the int8 matrix of the tcgen05 path)."""
+    from tenzo_b200 import kernels
+    N, K = 256, 384
+    rng = np.random.default_rng([49, batch])
+    w = dev(synth.random_tl1_packed(rng, N, K))
+    x = rng.standard_normal((batch, K)).astype(np.float32)
+    nw = dev((1 + 0.1 * rng.standard_normal(K)).astype(np.float32))
+    aligned = dev(x)
+    raw = torch.zeros(batch * K + 1, dtype=torch.float32, device="cuda")
+    shifted = raw[1:].view(batch, K)
+    shifted.copy_(aligned)
+    assert aligned.data_ptr() % 16 == 0 and shifted.data_ptr() % 16 == 4
+    a = kernels.tl1_gemv(aligned, w, N // 64, K, [0.02], norm_w=nw, do_norm=True, want_acc=True, want_act=True)
+    b = kernels.tl1_gemv(shifted, w, N // 64, K, [0.02], norm_w=nw, do_norm=True, want_acc=True, want_act=True)
+    torch.cuda.synchronize()
+    for k in ("a", "inv", "acc", "out"):
+        assert np.array_equal(host(a[k]), host(b[k])), f"{k} differs between the two quantiser paths"
