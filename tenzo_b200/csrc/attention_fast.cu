@@ -391,12 +391,15 @@ static size_t fa_smem_bytes() {
     return 1024 + (size_t)kFaWarps * kFaStages * 2 * kFaTile + (size_t)kFaWarps * kFaStages * 64 * 4 + 8 * kHd * 4 + kFaWarps * kFaStages * 8 + 64;
 }
 
-// Keys per CTA: enough CTAs for about six waves of two per SM, at least 256 keys each, a multiple of the 128 keys the
-// four warps take per round.
+// Keys per CTA: enough CTAs for about three waves of two per SM, at least 1024 keys each (a CTA's fixed cost - barriers,
+// query rotation, the first tiles' latency - is worth some 500 keys of streaming; measured at 32 x 4160: 93 us with 384
+// keys per CTA, 73 us with 1024) unless that leaves SMs without a CTA, then down to 256; a multiple of the 128 keys
+// the four warps take per round.
 static void fa_pick_split(int batch, int n_kv, int max_len, int* n_splits, int* split_keys) {
     const long long items = (long long)batch * n_kv;
-    long long want = (6LL * 2 * 148 + items - 1) / items;
-    const long long most = (max_len + 255) / 256;
+    long long want = (3LL * 2 * 148 + items - 1) / items;
+    long long most = (max_len + 1023) / 1024;
+    if (items * most < 2 * 148) most = (max_len + 255) / 256;
     if (want > most) want = most;
     if (want < 1) want = 1;
     int keys = (int)((max_len + want - 1) / want);
