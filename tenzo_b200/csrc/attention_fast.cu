@@ -348,18 +348,45 @@ __global__ void __launch_bounds__(128) attn_fast_merge_kernel(const FaLaunch L) 
         pdl_wait();
     }
     const size_t item0 = ((size_t)seq * a.n_kv + kvh) * L.n_splits;
-    for (int idx = threadIdx.x; idx < G * kHd; idx += blockDim.x) {
-        const int h = idx / kHd, d = idx % kHd;
+    // One thread per four adjacent dims of a head; the splits' (max, sum) pairs and partial rows are fetched eight splits
+    // at a time with every load in flight (a loop of dependent loads made this kernel ten L2 latencies long).
+    constexpr int kBatch = 8;
+    for (int idx4 = threadIdx.x; idx4 < G * kHd / 4; idx4 += blockDim.x) {
+        const int h = idx4 / (kHd / 4);
+        const float2* ml = reinterpret_cast<const float2*>(L.part_ml) + item0 * G + h;          // split s at ml[s * G]
+        const float4* po = reinterpret_cast<const float4*>(L.part_o) + item0 * G * (kHd / 4) + idx4;   // split s at po[s * G * kHd / 4]
         float m = -INFINITY;
-        for (int s = 0; s < L.n_splits; ++s) m = fmaxf(m, __ldcg(L.part_ml + ((item0 + s) * G + h) * 2));
-        const float m_use = m == -INFINITY ? 0.0f : m;
-        float o = 0.0f, l = 0.0f;
-        for (int s = 0; s < L.n_splits; ++s) {
-            const float f = fa_ex2(__ldcg(L.part_ml + ((item0 + s) * G + h) * 2) - m_use);
-            o += __ldcg(L.part_o + (item0 + s) * G * kHd + idx) * f;
-            l += __ldcg(L.part_ml + ((item0 + s) * G + h) * 2 + 1) * f;
+        for (int s0 = 0; s0 < L.n_splits; s0 += kBatch) {
+            float2 v[kBatch];
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) v[u] = s0 + u < L.n_splits ? __ldcg(ml + (size_t)(s0 + u) * G) : make_float2(-INFINITY, 0.0f);
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) m = fmaxf(m, v[u].x);
         }
-        a.out[(size_t)seq * a.n_q * kHd + (size_t)(kvh * G + h) * kHd + d] = o / (l * kFaPScale);
+        const float m_use = m == -INFINITY ? 0.0f : m;
+        float4 o = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        float l = 0.0f;
+        for (int s0 = 0; s0 < L.n_splits; s0 += kBatch) {
+            float2 v[kBatch];
+            float4 p[kBatch];
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                const bool in = s0 + u < L.n_splits;
+                v[u] = in ? __ldcg(ml + (size_t)(s0 + u) * G) : make_float2(-INFINITY, 0.0f);
+                p[u] = in ? __ldcg(po + (size_t)(s0 + u) * G * (kHd / 4)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {               // in split order, as the scalar form summed them
+                if (s0 + u < L.n_splits) {
+                    const float f = fa_ex2(v[u].x - m_use);
+                    o.x += p[u].x * f; o.y += p[u].y * f; o.z += p[u].z * f; o.w += p[u].w * f;
+                    l += v[u].y * f;
+                }
+            }
+        }
+        const float den = l * kFaPScale;
+        float4 r = make_float4(o.x / den, o.y / den, o.z / den, o.w / den);
+        reinterpret_cast<float4*>(a.out + (size_t)seq * a.n_q * kHd + (size_t)(kvh * G) * kHd)[idx4] = r;
     }
 }
 
@@ -440,6 +467,7 @@ bool attn_fast_applicable(const tenzo_attention_args& a) {
     if (group != 1 && group != 2 && group != 4 && group != 8) return false;
     if ((reinterpret_cast<uintptr_t>(a.cache_k) & 15) || (reinterpret_cast<uintptr_t>(a.cache_v) & 15)) return false;
     if ((reinterpret_cast<uintptr_t>(a.scale_k) & 15) || (reinterpret_cast<uintptr_t>(a.scale_v) & 15)) return false;
+    if (reinterpret_cast<uintptr_t>(a.out) & 15) return false;                    // the merge writes 16 bytes at a time
     if (a.max_seq % 4 || a.seq_stride_sc % 4 || a.seq_stride_kv % 16) return false;
     return true;
 }
