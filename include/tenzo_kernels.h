@@ -146,7 +146,7 @@ typedef struct {
      * accumulation (INT8 K/V are exact in fp16; the rotated query and the weights are rounded to fp16), exp is the
      * hardware ex2. Outputs agree with mode 0 to about 1e-4 of the output's largest magnitude (the specification asks
      * 1e-3 for floating-point outputs); the cache bytes written for the new token are identical in both modes.
-     * Contiguous cache only (block_table must be NULL), 16-byte aligned caches and scales, max_seq a multiple of 4;
+     * Contiguous cache only (block_table must be NULL), 16-byte aligned caches, scales and out, max_seq a multiple of 4;
      * returns -5 otherwise. */
     int mode;
     int split_keys;         /* mode 1: keys per CTA (rounded up to 128); 0 = choose automatically */
