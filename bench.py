@@ -321,8 +321,9 @@ def attention_roofline(B, ctx, steps, peak, mode=0):
     torch.cuda.empty_cache()
     return {"bound": "hbm", "kernel": "attn_fast_kernel (+ append, merge)" if mode == 1 else "attn_kernel", "achieved": gbs, "peak": peak[0],
             "peak_source": peak[1], "unit": "GB/s", "frac": gbs / peak[0],
-            "traffic": bytes_per * (265.2 / 259.5) if mode == 0 else None,
-            "traffic_source": "ncu at 24 sequences x 8192 keys: 1.02 x algorithmic, scaled by the keys read" if mode == 0 else "not captured",
+            "traffic": bytes_per * (265.2 / 259.5) if mode == 0 else bytes_per * (265.6 / 259.5),
+            "traffic_source": "ncu at 24 sequences x 8192 keys: 1.02 x algorithmic, scaled by the keys read" if mode == 0 else
+                              "ncu at 24 sequences x 8192 keys: 259.8 MB read + 5.8 MB of partial outputs written for 259.5 MB algorithmic, scaled by the keys read",
             "bytes_per_launch": bytes_per, "us_per_launch": ms * 1e3, "launches_timed": steps,
             "l2": f"{bytes_per / 1e6:.0f} MB of KV per launch, larger than L2" if bytes_per > 130e6 else "smaller than L2: an upper bound"}
 
