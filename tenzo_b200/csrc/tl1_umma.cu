@@ -9,11 +9,14 @@
 //   sum_k w*a = sum_k code*a - sum_k a          (w = code - 1; the per-sequence sum comes from the quantiser)
 //
 // One CTA per 128-row tile (two 64-row TL1 blocks; for the GLU epilogue the gate block and its up block, so the
-// activation is applied inside the CTA). K is walked in 128-byte chunks through a ring of 4 or 8 slots; per chunk
-//   warp 0 (lane 0)     bulk-copies the packed 2-bit weights eight chunks at a time (2 x 16 KB) into a two-group ring,
-//                       the first two groups first thing in the kernel (weights depend on no earlier kernel); lanes
-//                       1-31 fetch the per-sequence scale and sum for the epilogue;
-//   warps 2-5 / 6-9     (alternate chunks) expand the 2-bit codes to bytes in registers and write them straight into
+// activation is applied inside the CTA). K is walked in 128-byte chunks through a ring of 4, 8 or 12 slots (a multiple of
+// four: see UmmaSmem::slots_for); 21 warps per CTA:
+//   warp 0 (lane 0)     bulk-copies the packed 2-bit weights eight chunks at a time (2 x 16 KB) into a ring of two or
+//                       three groups; the first groups are requested by one lane each first thing in the kernel
+//                       (weights depend on no earlier kernel); lanes 1-31 fetch the per-sequence scale and sum for
+//                       the epilogue;
+//   warps 2-17          (four groups of four; group g takes chunks g, g + 4, ..., two per iteration when there are
+//                       eight or more slots) expand the 2-bit codes to bytes in registers and write them straight into
 //                       the slot's 32 columns of tensor memory (tcgen05.st 16x256b: no shared-memory A tile, no
 //                       proxy fence). Lane quarter q of a group takes one nibble half of one row block; a thread's
 //                       four TMEM lanes are the four rows of ONE packed word, so a thread loads sixteen words per
@@ -22,14 +25,14 @@
 //                       take turns TMA-loading the chunk's activation tile [N][128 B] (128-byte swizzle) into the
 //                       slot right after they have seen it free: a dedicated thread doing a poll, an expect_tx and
 //                       a TMA issue per chunk was the slowest role of the pipeline (about 800 cycles per chunk);
-//   warps 1, 10-12      (lane 0 each) take every fourth chunk: one poll of the slot's barrier (expand arrivals + the
+//   warps 1, 18-20      (lane 0 each) take every fourth chunk: one poll of the slot's barrier (expand arrivals + the
 //                       TMA's bytes), four tcgen05.mma (K = 32 each, A from tensor memory), one commit that frees the
 //                       slot. A poll costs the issuing thread about 180 cycles, a commit about 80 and the loop
 //                       another 270 (measured), more than the MMAs of a chunk take below 256 sequences, so one
 //                       issuing thread bounds the loop; four hide it. Integer accumulation is order-free, so the only
 //                       ordering needed between them is that chunk 0 (which overwrites) completes first.
-// After the last chunk every issuing thread commits to one barrier, which starts the epilogue on all eight expand
-// warps (two groups on alternate 32-sequence column units; TMEM lane = weight row, tcgen05.ld 16 sequences at a
+// After the last chunk every issuing thread commits to one barrier, which starts the epilogue on all sixteen expand
+// warps (the groups on alternate 32-sequence column units; TMEM lane = weight row, tcgen05.ld 16 sequences at a
 // time, scale / residual / ReLU^2*GLU, the unit assembled in shared memory and sent off by its own TMA store while
 // the next one is computed).
 // Few row tiles (the out, down and q|k|v projections have 20 to 30) would leave most SMs idle, so K is then split
