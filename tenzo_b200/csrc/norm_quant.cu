@@ -61,6 +61,12 @@ __global__ void __launch_bounds__(kNqThreads) rmsnorm_quant_kernel(
 // even columns of column pairs 16*set + 4*i + t (byte i = 0..3), words[seq][set][t][1] the odd
 // columns unscaled; columns beyond K are zero. inv[seq] = max|y|/31. `words` may be null (tensor-core GEMM
 // path: it takes the plain int8 matrix a_out [batch][K] and sum_out[seq] = sum_k a_k instead).
+#ifdef TZ_AQ_TRACE
+__device__ long long g_aq_trace[8];
+#define AQT(i) do { if (blockIdx.x == 0 && threadIdx.x == 0) g_aq_trace[i] = clock64(); } while (0)
+#else
+#define AQT(i) ((void)0)
+#endif
 constexpr int kAqVec = 7;     // float4 values a thread of act_quant_kernel holds: rows up to 7168 floats stay in registers
 
 __global__ void __launch_bounds__(kNqThreads) act_quant_kernel(
@@ -72,6 +78,7 @@ __global__ void __launch_bounds__(kNqThreads) act_quant_kernel(
     // Let the GEMM that consumes this kernel's output start at once: its prologue (tensor-memory allocation, the first
     // weight copies, expanding the first weight chunks) depends on nothing here and takes as long as this whole kernel;
     // it waits for this grid's completion before it touches the activations.
+    AQT(0);
     if (use_pdl) pdl_launch_dependents();
     const float* xs = x + (size_t)seq * x_stride;
     // The whole row in registers as 16-byte loads, all in flight at once; shared memory is only touched where another
@@ -91,6 +98,7 @@ __global__ void __launch_bounds__(kNqThreads) act_quant_kernel(
             }
         }
         if (use_pdl) pdl_wait();
+        AQT(1);
 #pragma unroll
         for (int r = 0; r < kAqVec; ++r) {
             const int i = tid + r * kNqThreads;
@@ -104,7 +112,9 @@ __global__ void __launch_bounds__(kNqThreads) act_quant_kernel(
                 if (i < k4) reinterpret_cast<float4*>(s_y)[i] = v[r];
             }
             __syncthreads();
+            AQT(2);
             const float ss = sumsq_reference_order(s_y, K, s_f);
+            AQT(3);
             const float inv_rms = rms_inv(ss, K, eps);
 #pragma unroll
             for (int r = 0; r < kAqVec; ++r) {          // y = (x * inv_rms) * w, left to right (rms_apply)
@@ -115,6 +125,7 @@ __global__ void __launch_bounds__(kNqThreads) act_quant_kernel(
 #pragma unroll
         for (int r = 0; r < kAqVec; ++r) m = fmaxf(fmaxf(m, fmaxf(fabsf(v[r].x), fabsf(v[r].y))), fmaxf(fabsf(v[r].z), fabsf(v[r].w)));
         m = fmaxf(block_max(m, s_f), 1e-6f);      // TenzoEngine.cpp:28-32
+        AQT(4);
         const float to_q = 31.0f / m;             // :34
         if (tid == 0) inv[seq] = m / 31.0f;       // :35
         if (words) {                              // the packed fragments gather arbitrary columns: through shared memory
@@ -162,6 +173,7 @@ __global__ void __launch_bounds__(kNqThreads) act_quant_kernel(
                 if (tid == 0) sum_out[seq] = s_i[0];
             }
         }
+        AQT(5);
         return;
     }
     // rows that are longer, or not aligned for 16-byte loads: element by element through shared memory
@@ -236,6 +248,12 @@ cudaError_t launch_act_quant(const float* x, const float* norm_w, int do_norm, f
 }
 
 }  // namespace tz
+
+#ifdef TZ_AQ_TRACE
+extern "C" __attribute__((visibility("default"))) int tenzo_trace_act_quant(long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, tz::g_aq_trace, sizeof(long long) * 8);
+}
+#endif
 
 extern "C" int tenzo_cuda_rmsnorm_quant(const float* x, const float* norm_w, int do_norm, float eps, int dim,
                                         int qmax, int batch, int x_stride, float* y_out, int8_t* q_out,
