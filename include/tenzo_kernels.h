@@ -77,6 +77,11 @@ TENZO_API int tenzo_cuda_tl1_gemv_ksplit(int n_blocks, int K, int epilogue);
  * (1, 2, 4 or 8; more than 1 when the row tiles alone would leave most SMs idle); 0 if that path does not take the
  * shape. Informational. */
 TENZO_API int tenzo_cuda_tl1_gemm_ksplit(int n_blocks, int K, int batch, int epilogue);
+/* The tensor-core path's per-CTA layout for `batch` sequences (what a CTA holds: min(batch, 256) padded to 16):
+ * ring slots (a multiple of four), groups of eight weight chunks in flight, dynamic shared memory in bytes, and the
+ * bytes the epilogue may need in the two rings. Host arithmetic only (no device call); returns 0, or -1 for
+ * batch < 16. Informational; no counterpart in the reference. */
+TENZO_API int tenzo_cuda_tl1_gemm_layout(int batch, int* slots, int* weight_groups, size_t* smem_bytes, size_t* epilogue_bytes);
 TENZO_API size_t tenzo_cuda_tl1_gemv_workspace_bytes(int batch, int K);
 /* The kernel's waits on asynchronous copies are bounded. Returns 1 (and clears the flag) if any launch
  * since the last call gave up waiting — its output is then invalid; 0 otherwise; -1 if the query failed.

@@ -83,7 +83,7 @@ EXT_SYMBOLS = [
     "tenzo_ext_persistent_phase_ns",
 ]
 KERNEL_SYMBOLS = [
-    "tenzo_cuda_tl1_gemv", "tenzo_cuda_tl1_gemv_ksplit", "tenzo_cuda_tl1_gemm_ksplit", "tenzo_cuda_tl1_gemv_workspace_bytes", "tenzo_cuda_tl1_gemv_take_timeouts", "tenzo_cuda_selftest_wait_expiry", "tenzo_cuda_rmsnorm_quant", "tenzo_cuda_attention_int8",
+    "tenzo_cuda_tl1_gemv", "tenzo_cuda_tl1_gemv_ksplit", "tenzo_cuda_tl1_gemm_ksplit", "tenzo_cuda_tl1_gemm_layout", "tenzo_cuda_tl1_gemv_workspace_bytes", "tenzo_cuda_tl1_gemv_take_timeouts", "tenzo_cuda_selftest_wait_expiry", "tenzo_cuda_rmsnorm_quant", "tenzo_cuda_attention_int8",
     "tenzo_cuda_attention_heads_per_cta", "tenzo_cuda_attention_take_timeouts", "tenzo_cuda_attention_workspace_bytes", "tenzo_cuda_lm_head_i8", "tenzo_cuda_lm_head_scratch_bytes",
     "tenzo_cuda_embedding_i8", "tenzo_cuda_tl1_pack_rows2bit", "tenzo_cuda_lm_head_i8_static",
     "tenzo_cuda_lm_head_static_max_batch", "tenzo_cuda_lm_head_take_timeouts", "tenzo_cuda_repetition_penalty",
@@ -153,6 +153,8 @@ def declare_kernel_abi(L):
     L.tenzo_cuda_tl1_gemv.restype, L.tenzo_cuda_tl1_gemv.argtypes = i32, [C.POINTER(Tl1GemvArgs), vp]
     L.tenzo_cuda_tl1_gemv_ksplit.restype, L.tenzo_cuda_tl1_gemv_ksplit.argtypes = i32, [i32, i32, i32]
     L.tenzo_cuda_tl1_gemm_ksplit.restype, L.tenzo_cuda_tl1_gemm_ksplit.argtypes = i32, [i32, i32, i32, i32]
+    L.tenzo_cuda_tl1_gemm_layout.restype = i32
+    L.tenzo_cuda_tl1_gemm_layout.argtypes = [i32, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]
     L.tenzo_cuda_tl1_gemv_workspace_bytes.restype, L.tenzo_cuda_tl1_gemv_workspace_bytes.argtypes = sz, [i32, i32]
     L.tenzo_cuda_tl1_gemv_take_timeouts.restype, L.tenzo_cuda_tl1_gemv_take_timeouts.argtypes = i32, []
     L.tenzo_cuda_rmsnorm_quant.restype = i32

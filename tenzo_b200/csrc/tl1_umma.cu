@@ -633,6 +633,18 @@ extern "C" __attribute__((visibility("default"))) int tenzo_trace_umma_chunks(lo
 }
 #endif
 
+extern "C" int tenzo_cuda_tl1_gemm_layout(int batch, int* slots, int* weight_groups, size_t* smem_bytes, size_t* epilogue_bytes) {
+    if (batch < 16) return -1;
+    const int per_cta = batch < tz::kMaxN ? batch : tz::kMaxN, n_box = (per_cta + 15) & ~15;
+    if (slots) *slots = tz::UmmaSmem::slots_for(n_box);
+    if (weight_groups) *weight_groups = tz::UmmaSmem::pgroups_for(n_box);
+    if (smem_bytes) *smem_bytes = tz::UmmaSmem::bytes(n_box);
+    // without a cluster: the output columns [n_box][128] fp32 (GLU: [n_box][64] twice); with one: behind the partial tile
+    // [n_box][128] int32, the columns of the blocks a rank owns (at most every other 16-sequence block)
+    if (epilogue_bytes) *epilogue_bytes = (size_t)n_box * 512 + (size_t)16 * ((n_box / 16 + 1) / 2) * 512;
+    return 0;
+}
+
 extern "C" int tenzo_cuda_tl1_gemm_ksplit(int n_blocks, int K, int batch, int epilogue) {
     if (n_blocks <= 0 || K < tz::kKc || K % tz::kKc || batch < 16) return 0;       // the tensor-core path does not apply
     const int units = epilogue == TENZO_EPI_RELU2_GLU ? n_blocks / 2 : (n_blocks + 1) / 2;

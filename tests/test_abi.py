@@ -108,6 +108,26 @@ def test_kernel_entry_points_reject_bad_arguments_without_a_device(lib):
     assert lib.tenzo_cuda_attention_heads_per_cta(1, 20, 5, 256) == 1 and lib.tenzo_cuda_attention_heads_per_cta(64, 20, 5, 8192) == 4
 
 
+def test_tensor_core_gemm_layout_invariants(lib):
+    """What the batched GEMM's hand-offs rely on, for every batch it can be given: the ring has a multiple of four slots
+    (slot s then always belongs to expand group s % 4 and issuing thread s % 4, so each barrier's phases are seen in order
+    by one waiter - a parity wait cannot tell phase k from phase k - 2), at least four of them, the A slots fit in tensor
+    memory beside the accumulators, everything fits in an SM's shared memory, and the two rings can hold what the
+    epilogue assembles in them."""
+    for batch in list(range(16, 273)) + [300, 1000, 4096]:
+        slots, groups, smem, epi = C.c_int(), C.c_int(), C.c_size_t(), C.c_size_t()
+        assert lib.tenzo_cuda_tl1_gemm_layout(batch, C.byref(slots), C.byref(groups), C.byref(smem), C.byref(epi)) == 0
+        n_box = (min(batch, 256) + 15) // 16 * 16
+        assert slots.value % 4 == 0 and 4 <= slots.value <= 16, (batch, slots.value)
+        assert (n_box + 31) // 32 * 32 + 32 * slots.value <= 512, "accumulators + A slots exceed tensor memory"
+        assert groups.value in (2, 3)
+        assert smem.value <= 227 * 1024, (batch, smem.value)
+        rings = slots.value * n_box * 128 + groups.value * 8 * 4096
+        assert rings + 1024 < smem.value                 # plus alignment slack, barriers, per-sequence operands
+        assert epi.value <= rings, (batch, epi.value, rings)
+    assert lib.tenzo_cuda_tl1_gemm_layout(15, None, None, None, None) == -1
+
+
 def test_engine_creation_fails_loudly_without_a_gpu(lib):
     import torch
     if torch.cuda.is_available():
