@@ -186,10 +186,9 @@ __global__ void __launch_bounds__((FUSED ? kFusedWarps : kBatchedWarps) * 32, FU
             wreg[r] = i < a.K ? __ldg(a.norm_w + i) : 0.0f;   // model constant: no need to wait for the previous kernel
         }
     }
-    if (L.ksplit > 1) {
-        __syncthreads();
-        cluster.barrier_arrive();                   // "my s_d is zeroed": peers may add into it after their wait
-    }
+    if (L.ksplit > 1 || !FUSED) __syncthreads();    // batched: the staging loop below adds into s_sa4 from every warp, so the
+                                                    // zeroes above must be in place first (one sequence: barriers follow anyway)
+    if (L.ksplit > 1) cluster.barrier_arrive();     // "my s_d is zeroed": peers may add into it after their wait
 
     TZ_STAMP(1);
     if (a.use_pdl) pdl_wait();

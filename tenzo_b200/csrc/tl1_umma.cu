@@ -76,7 +76,7 @@ struct UmmaLaunch {
     int n_slots;             // ring slots (A in tensor memory, activation tile in shared memory)
     int n_pgroups;           // groups of kPGroup chunks in the packed-weight ring
     int ksplit;              // CTAs of a cluster that share one tile's K range (1 = no cluster)
-    int store_cols;          // sequences per TMA store of the epilogue (32 without a cluster, 16 with one)
+    int store_cols;          // sequences per TMA store of the epilogue (32; 16 with a cluster or up to 64 sequences)
 };
 
 __device__ int g_umma_timeouts = 0;
@@ -156,14 +156,14 @@ __device__ __forceinline__ void umma_epilogue_block(const tenzo_tl1_gemv_args& a
             if (seq0 + c0 + i < a.batch) a.acc_out[(size_t)(seq0 + c0 + i) * a.n_blocks * 64 + block * 64 + rr] = (int)r[i];
     }
     if (EPI == TENZO_EPI_RELU2_GLU) {
-        if (up_half) {
+        if (up_half) {                                   // the up value, and ReLU(gate)^2: multiplied once both are in place
 #pragma unroll
             for (int i = 0; i < 16; ++i) s_glu_cols[i * 64 + rr] = v[i];
         } else {
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
                 const float rl = fmaxf(0.0f, v[i]);
-                s_out_cols[i * 64 + rr] = (rl * rl) * s_glu_cols[i * 64 + rr];   // :1618-1619
+                s_out_cols[i * 64 + rr] = rl * rl;                               // :1618
             }
         }
     } else if (EPI == TENZO_EPI_RESIDUAL) {
@@ -454,11 +454,11 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) tl1_umma_kernel(const UmmaLau
         // Output columns [sequences][128 rows] (GLU: [..][64]) are assembled in shared memory the pipeline no longer
         // needs - the rings, which are contiguous; with a cluster behind the partial tile the peers are reading - and
         // leave unit by unit through TMA stores: rows of 512 (256) contiguous bytes per sequence, clipped at the
-        // matrix edge by the tensor map. GLU: the up half goes through shared memory once for all columns, then the
-        // gate half computes and stores. Space: N*512 bytes without a cluster (at least four slots), N*512 plus 512 per
+        // matrix edge by the tensor map. GLU: the up half parks its values and the gate half its ReLU^2 side by side, then
+        // the group multiplies them in place. Space: N*512 bytes without a cluster (at least four slots), N*512 plus 512 per
         // own column with one (a rank owns at most every other block), which the two rings hold for every N.
         constexpr int row_floats = glu ? 64 : 128;
-        constexpr int SB = CLUSTER ? 1 : 2;                  // 16-sequence blocks per store unit
+        const int SB = L.store_cols >> 4;                    // 16-sequence blocks per store unit: 2, or 1 (a cluster; few sequences)
         float* s_out = reinterpret_cast<float*>(ring + (CLUSTER ? (size_t)N * 512 : 0));            // behind the partial tile [N][128] int32
         float* s_glu = s_out + (size_t)(CLUSTER ? 16 * ((N / 16 + 1) / 2) : N) * 64;                 // behind the GLU output columns (a rank owns at most every other block)
         const int n_blocks16 = N / 16;
@@ -467,54 +467,59 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) tl1_umma_kernel(const UmmaLau
         const bool leader = lane == 0 && q == 0;
         const uint32_t t_lane = tmem_base + ((uint32_t)(32 * q) << 16);
 #pragma unroll 1
-        for (int phase = glu ? 0 : 1; phase < 2; ++phase) {
-            const bool active = !glu || (phase == 0 ? rblk == 1 : rblk == 0);
-            if (active) {
-#pragma unroll 1
-                for (int un = grp; un < n_units; un += kExpandGroups) {
-                    const int ob0 = un * SB;
-                    const bool two = SB == 2 && ob0 + 1 < own_blocks;
-                    const int c0 = 16 * (CLUSTER ? split + ksplit * ob0 : ob0);
-                    uint32_t r0[16], r1[16];
+        for (int un = grp; un < n_units; un += kExpandGroups) {
+            const int ob0 = un * SB;
+            const bool two = SB == 2 && ob0 + 1 < own_blocks;
+            const int c0 = 16 * (CLUSTER ? split + ksplit * ob0 : ob0);
+            uint32_t r0[16], r1[16];
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) r0[i] = r1[i] = 0u;
-                    if (ok) {
-                        tmem_ld16_nowait(t_lane + (uint32_t)c0, r0);
-                        if (two) tmem_ld16_nowait(t_lane + (uint32_t)(c0 + 16), r1);
-                        tmem_wait_ld();
-                    }
-                    if (CLUSTER) {
-                        // the peers' partials over distributed shared memory: every load issued before the first is
-                        // used (ranks beyond the cluster and this CTA's own read its own tile and are masked out)
+            for (int i = 0; i < 16; ++i) r0[i] = r1[i] = 0u;
+            if (ok) {
+                tmem_ld16_nowait(t_lane + (uint32_t)c0, r0);
+                if (two) tmem_ld16_nowait(t_lane + (uint32_t)(c0 + 16), r1);
+                tmem_wait_ld();
+            }
+            if (CLUSTER) {
+                // the peers' partials over distributed shared memory: every load issued before the first is
+                // used (ranks beyond the cluster and this CTA's own read its own tile and are masked out)
 #pragma unroll
-                        for (int p = 0; p < 8; ++p) {
-                            const bool use_p = p < ksplit && p != split;
-                            const int* peer = cg::this_cluster().map_shared_rank(reinterpret_cast<int*>(ring), use_p ? p : split);
-                            const uint32_t mask = use_p ? 0xffffffffu : 0u;
+                for (int p = 0; p < 8; ++p) {
+                    const bool use_p = p < ksplit && p != split;
+                    const int* peer = cg::this_cluster().map_shared_rank(reinterpret_cast<int*>(ring), use_p ? p : split);
+                    const uint32_t mask = use_p ? 0xffffffffu : 0u;
 #pragma unroll
-                            for (int i = 0; i < 16; ++i) r0[i] += mask & (uint32_t)peer[(c0 + i) * 128 + m];
-                        }
-                    }
-                    umma_epilogue_block<EPI>(a, r0, s_inv, s_sum, wscale, c0, seq0, block, rr, row, phase == 0, s_out + (size_t)16 * ob0 * row_floats,
-                                             s_glu + (size_t)16 * ob0 * 64, ok);
-                    if (two)
-                        umma_epilogue_block<EPI>(a, r1, s_inv, s_sum, wscale, c0 + 16, seq0, block, rr, row, phase == 0,
-                                                 s_out + (size_t)16 * (ob0 + 1) * row_floats, s_glu + (size_t)16 * (ob0 + 1) * 64, ok);
-                    if (phase == 1) {
-                        // the unit is complete in shared memory: hand it to the TMA and go on with the next one
-                        fence_proxy_async_smem();
-                        named_barrier_sync(1 + grp, glu ? 64 : 128);
-                        if (leader && ok && seq0 + c0 < a.batch &&
-                            UCHK(reinterpret_cast<unsigned char*>(s_out + (size_t)16 * ob0 * row_floats) + 16 * SB * row_floats * 4 <= reinterpret_cast<unsigned char*>(bars), 6,
-                                 reinterpret_cast<unsigned char*>(s_out + (size_t)16 * ob0 * row_floats) - smem_raw, un)) {             // else nothing but padding
-                            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
-                                         ::"l"(&omap), "r"((glu ? tile : blk0) * 64), "r"(seq0 + c0), "r"(smem_addr(s_out + (size_t)16 * ob0 * row_floats)) : "memory");
-                            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                        }
-                    }
+                    for (int i = 0; i < 16; ++i) r0[i] += mask & (uint32_t)peer[(c0 + i) * 128 + m];
                 }
             }
-            if (phase == 0) named_barrier_sync(1 + kExpandGroups, 128 * kExpandGroups);      // every up value is in shared memory
+            float* unit_out = s_out + (size_t)16 * ob0 * row_floats;
+            float* unit_glu = s_glu + (size_t)16 * ob0 * 64;
+            umma_epilogue_block<EPI>(a, r0, s_inv, s_sum, wscale, c0, seq0, block, rr, row, rblk == 1, unit_out, unit_glu, ok);
+            if (two)
+                umma_epilogue_block<EPI>(a, r1, s_inv, s_sum, wscale, c0 + 16, seq0, block, rr, row, rblk == 1, unit_out + 16 * row_floats,
+                                         unit_glu + 16 * 64, ok);
+            if (glu) {
+                // gate and up halves of the unit are both in shared memory: out = ReLU(gate)^2 * up, four floats at a time
+                named_barrier_sync(1 + grp, 128);
+                const int n4 = (two ? 32 : 16) * 64 / 4;
+                float4* o4 = reinterpret_cast<float4*>(unit_out);
+                const float4* g4 = reinterpret_cast<const float4*>(unit_glu);
+                for (int i = 32 * q + lane; i < n4; i += 128) {
+                    float4 o = o4[i];
+                    const float4 u = g4[i];
+                    o.x *= u.x; o.y *= u.y; o.z *= u.z; o.w *= u.w;             // :1619
+                    o4[i] = o;
+                }
+            }
+            // the unit is complete in shared memory: hand it to the TMA and go on with the next one
+            fence_proxy_async_smem();
+            named_barrier_sync(1 + grp, 128);
+            if (leader && ok && seq0 + c0 < a.batch &&
+                UCHK(reinterpret_cast<unsigned char*>(unit_out) + 16 * SB * row_floats * 4 <= reinterpret_cast<unsigned char*>(bars), 6,
+                     reinterpret_cast<unsigned char*>(unit_out) - smem_raw, un)) {             // else nothing but padding
+                asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                             ::"l"(&omap), "r"((glu ? tile : blk0) * 64), "r"(seq0 + c0), "r"(smem_addr(unit_out)) : "memory");
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
         }
         if (tid == 64) UT(8);
         if (leader) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");     // the tiles have left shared memory
@@ -566,7 +571,7 @@ int launch_tl1_umma(const tenzo_tl1_gemv_args& a, const int8_t* a8, const float*
     L.n_pgroups = UmmaSmem::pgroups_for(L.n_box);
     const int seq_tiles = (a.batch + kMaxN - 1) / kMaxN;
     L.ksplit = pick_umma_ksplit(L.units * seq_tiles, a.K / kKc);
-    L.store_cols = L.ksplit > 1 ? 16 : 32;
+    L.store_cols = (L.ksplit > 1 || L.n_box <= 64) ? 16 : 32;      // few sequences: 16 per unit, so that every group gets one
     CUtensorMap amap, omap;
     // activations [batch][K] int8: B-operand tiles {128 bytes of K, n_box sequences}, 128-byte swizzle
     if (int rc = encode_2d(&amap, CU_TENSOR_MAP_DATA_TYPE_UINT8, a8, (uint64_t)a.K, (uint64_t)a.batch, (uint64_t)a.K, kKc, (uint32_t)L.n_box,
