@@ -350,6 +350,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) tl1_umma_kernel(const UmmaLau
             }
             seen_group = pg;
             ok = __all_sync(0xffffffffu, ok);
+            __syncwarp();                                   // what lanes 0 and 1 acquired is visible to the whole warp
             if (j0 == 0 && tid == 64) UT(6);
             if (!ok) { timed_out = true; break; }
             tc_fence_after();
@@ -381,10 +382,6 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) tl1_umma_kernel(const UmmaLau
                 for (int n = 0; n < 4; ++n)
 #pragma unroll
                     for (int u = 0; u < 4; ++u) W[4 * n + u] = (have && sp_ok) ? sP[n * 128 + woff[u]] : 0u;
-                if (c == n_here - 1) {
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&bar_pfree[ps]);   // the packed chunks have been consumed into registers
-                }
                 uint32_t lo[16], up[16];                       // registers of the two stores: lanes 0-15 (jj = 0, 1) and 16-31 (jj = 2, 3)
 #pragma unroll
                 for (int n = 0; n < 4; ++n) {
@@ -408,6 +405,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) tl1_umma_kernel(const UmmaLau
                 }
             }
             if (lane == 0 && q == 0) { UC(j0, 2); if (n_here == 2) UC(j0 + kExpandGroups, 2); }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar_pfree[ps]);       // every lane's packed words have been loaded and used
             if (request_last) {
                 if (lane == 0) pdl_wait();
                 request_tiles();
@@ -424,6 +423,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) tl1_umma_kernel(const UmmaLau
         bool ok = true;
         if (lane == 0) ok = !timed_out && mbar_spin_bounded(bar_meta, 0u) && mbar_spin_bounded(bar_accum, 0u);
         ok = __shfl_sync(0xffffffffu, ok, 0);
+        __syncwarp();
         if (!ok) timed_out = true;
         tc_fence_after();
         if (tid == 64) UT(7);
