@@ -7,6 +7,7 @@
 // The GEMV and LM-head kernels carry the same code in their prologues; this entry exists for the
 // backend class's executeRMSNorm and for checking the quantiser on its own.
 #include "common.cuh"
+#include "attn_common.cuh"
 #include "../../include/tenzo_kernels.h"
 
 namespace tz {
@@ -72,8 +73,8 @@ constexpr int kAqVec = 7;     // float4 values a thread of act_quant_kernel hold
 __global__ void __launch_bounds__(kNqThreads) act_quant_kernel(
     const float* x, const float* __restrict__ norm_w, int do_norm, float eps, int K, int x_stride,
     uint32_t* words, float* inv, int8_t* a_out, int* sum_out, int use_pdl) {
-    extern __shared__ float s_y[];            // K floats + 32 scratch
-    float* s_f = s_y + K;
+    extern __shared__ __align__(16) float s_y[];   // K floats (or eight padded rows of K/8 squares) + 32 scratch
+    float* s_f = s_y + K + 64;
     const int tid = threadIdx.x, seq = blockIdx.x;
     // Let the GEMM that consumes this kernel's output start at once: its prologue (tensor-memory allocation, the first
     // weight copies, expanding the first weight chunks) depends on nothing here and takes as long as this whole kernel;
@@ -106,14 +107,42 @@ __global__ void __launch_bounds__(kNqThreads) act_quant_kernel(
         }
         float m = 0.0f;
         if (do_norm) {
+            float ss;
+            if ((K & 7) == 0) {
+                // Squares from every thread, stored chain-major (lane j's x[j]^2, x[j+8]^2, ... contiguous, rows padded so
+                // that the eight lanes' 16-byte loads fall in different banks); the eight chains of the reference's order
+                // then cost one load per four adds and one add per element. The chain shares its SM with the
+                // consuming GEMM's first round of weight expansion, and every instruction it does not have to issue is
+                // one it does not have to queue for (load + square + add per element ran at 10.6 cycles per step there).
+                const int rows = K >> 3, stride = ((rows + 3) & ~3) + 4;
 #pragma unroll
-            for (int r = 0; r < kAqVec; ++r) {
-                const int i = tid + r * kNqThreads;
-                if (i < k4) reinterpret_cast<float4*>(s_y)[i] = v[r];
+                for (int r = 0; r < kAqVec; ++r) {
+                    const int i = tid + r * kNqThreads;
+                    if (i < k4) {
+                        float* d = s_y + (4 * (i & 1)) * stride + (i >> 1);      // element 4i + c: row (4i + c) & 7, column (4i + c) >> 3
+                        d[0] = __fmul_rn(v[r].x, v[r].x);
+                        d[stride] = __fmul_rn(v[r].y, v[r].y);
+                        d[2 * stride] = __fmul_rn(v[r].z, v[r].z);
+                        d[3 * stride] = __fmul_rn(v[r].w, v[r].w);
+                    }
+                }
+                __syncthreads();
+                AQT(2);
+                if (tid < 8) s_f[tid] = sequential_sum(s_y + tid * stride, rows);
+                __syncthreads();
+                ss = s_f[0];
+#pragma unroll
+                for (int j = 1; j < 8; ++j) ss = __fadd_rn(ss, s_f[j]);        // lanes added left to right, from lane 0
+            } else {
+#pragma unroll
+                for (int r = 0; r < kAqVec; ++r) {
+                    const int i = tid + r * kNqThreads;
+                    if (i < k4) reinterpret_cast<float4*>(s_y)[i] = v[r];
+                }
+                __syncthreads();
+                AQT(2);
+                ss = sumsq_reference_order(s_y, K, s_f);
             }
-            __syncthreads();
-            AQT(2);
-            const float ss = sumsq_reference_order(s_y, K, s_f);
             AQT(3);
             const float inv_rms = rms_inv(ss, K, eps);
 #pragma unroll
@@ -229,7 +258,7 @@ __global__ void __launch_bounds__(kNqThreads) act_quant_kernel(
 
 cudaError_t launch_act_quant(const float* x, const float* norm_w, int do_norm, float eps, int K, int batch, int x_stride,
                              uint32_t* words, float* inv, int8_t* a_out, int* sum_out, int use_pdl, cudaStream_t st) {
-    const size_t smem = (size_t)(K + 32) * sizeof(float);
+    const size_t smem = (size_t)(K + 96) * sizeof(float);
     if (smem > 48 * 1024) {
         cudaError_t ea = cudaFuncSetAttribute(act_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024);
         if (ea != cudaSuccess) return ea;
