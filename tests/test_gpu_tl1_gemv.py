@@ -255,3 +255,33 @@ def test_quantiser_paths_agree_on_misaligned_rows(cuda_lib, batch):
     torch.cuda.synchronize()
     for k in ("a", "inv", "acc", "out"):
         assert np.array_equal(host(a[k]), host(b[k])), f"{k} differs between the two quantiser paths"
+
+
+@pytest.mark.parametrize("world", [4, 8])
+def test_tensor_parallel_shard_shapes_match_the_single_sequence_path(cuda_lib, world):
+    """The row slices a rank of a 4- or 8-way tensor-parallel 8B-shaped layer multiplies (out, gate|up, down, q|k|v at 32
+    sequences: few row tiles, K split over clusters of up to eight CTAs, as few as four 128-byte chunks per CTA) against
+    the same launches made one sequence at a time."""
+    from tenzo_b200 import kernels
+    rng = np.random.default_rng([50, world])
+    B, h, f = 32, 4096, 14336
+    for name, N, K, epi in (("out", h // world, h, kernels.EPI_RESIDUAL), ("gate|up", 2 * f // world, h, kernels.EPI_RELU2_GLU),
+                            ("down", h // world, f, kernels.EPI_RESIDUAL), ("qkv", (32 + 8 + 8) * 128 // world, h, kernels.EPI_STORE)):
+        w = dev(synth.random_tl1_packed(rng, N, K))
+        x = dev(rng.standard_normal((B, K)).astype(np.float32))
+        nw = dev((1 + 0.1 * rng.standard_normal(K)).astype(np.float32))
+        n_out = N // 2 if epi == kernels.EPI_RELU2_GLU else N
+        res = dev(rng.standard_normal((B, n_out)).astype(np.float32)) if epi == kernels.EPI_RESIDUAL else None
+        nb = N // 64
+        seg = [nb // 2, nb, nb] if epi == kernels.EPI_RELU2_GLU else [nb, nb, nb]
+
+        def run(xs, rs):
+            return kernels.tl1_gemv(xs, w, nb, K, [0.02, 0.03], seg, epilogue=epi, resid=rs, norm_w=nw, do_norm=True)["out"]
+
+        big = run(x, res)
+        torch.cuda.synchronize()
+        for b in (0, 15, 16, 31):
+            one = run(x[b:b + 1].contiguous(), res[b:b + 1].contiguous() if res is not None else None)
+            torch.cuda.synchronize()
+            assert torch.equal(big[b], one[0]), f"{name} slice of a {world}-rank layer differs at sequence {b}"
+    assert cuda_lib.tenzo_cuda_tl1_gemv_take_timeouts() == 0
