@@ -528,7 +528,14 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) tl1_umma_kernel(const UmmaLau
     if (CLUSTER) cg::this_cluster().sync();                  // every peer has read this CTA's partial tile: it may exit
     if (timed_out) atomicExch(&g_umma_timeouts, 1);
     tc_fence_before();
-    __syncthreads();
+    if (__syncthreads_or(timed_out ? 1 : 0)) {
+        // A role gave up: copies it no longer waits for may still be on their way into this CTA's shared memory, and
+        // MMAs it issued may still be running. Give them a bounded time (about 100 us; a copy lands within a few) before
+        // the memory and the tensor-memory columns go back to the SM.
+        const long long t_end = clock64() + 200000;
+        while (clock64() < t_end) __nanosleep(1000);
+        __syncthreads();
+    }
     if (tid == 0) UTG(11);
     if (warp == 1) {
         tc_fence_after();
