@@ -128,7 +128,9 @@ typedef struct {
     int append;            /* 1: quantise and store the new k,v at pos (normal decode); 0: the
                               cache already holds pos[s]+1 keys, k/v are ignored */
     int heads_per_cta;     /* 0 = choose automatically; 1, 2, 4 or 8 forces the query heads one CTA processes */
-    int use_pdl;
+    int use_pdl;           /* launch with programmatic stream serialisation. The kernel launched immediately before must
+                              then write none of pos, rope_cos / rope_sin or the cache rows below pos[s]: with the contiguous
+                              cache and few items those are read before the wait for that kernel (q, k, v are read after) */
     int tiles;             /* 0 = choose automatically; 1 = force the variant whose scoring warps read K through TMA tiles
                               (two keys per lane; for many (sequence, kv head) items; returns -5 if it does not fit:
                               needs four 16 KB tile rings beside the weights, n_q/n_kv <= 4 heads per CTA, cache_k and

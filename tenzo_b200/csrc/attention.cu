@@ -130,9 +130,15 @@ __global__ void __launch_bounds__(TILED ? kTileThreads : kAttnThreads) attn_kern
     const int head0 = blockIdx.x * GH, kvh = head0 / G, seq = blockIdx.y;
     const bool stores_new_row = (head0 % G) == 0;
 
-    if (a.use_pdl) pdl_wait();
+    // Few items, contiguous cache (single-sequence decode, where a layer's attention is 6 us of dependent latencies): the
+    // position, the rotation coefficients, the rows of earlier keys and the first value chunks are inputs that no kernel
+    // of the same step writes before this one, so they are requested BEFORE waiting for the producer of q / k / v and
+    // their round trips overlap the producer's tail. (Callers that launch with use_pdl directly behind a kernel that
+    // writes the position, the tables or cache rows below it must not: include/tenzo_kernels.h says so.)
+    constexpr bool kEarly = !TILED && !PAGED;
+    if (!kEarly && a.use_pdl) pdl_wait();
     TZ_PH_DECL;
-    const int pos = a.pos[seq];
+    const int pos = __ldcg(a.pos + seq);
     // max_len sizes the score vectors and the staged block table: a position outside [0, max_len) would write past
     // them, so the CTA flags it (the host reads the flag like a give-up) and leaves without touching memory.
     if (pos < 0 || pos >= a.max_len) {
@@ -209,12 +215,21 @@ __global__ void __launch_bounds__(TILED ? kTileThreads : kAttnThreads) attn_kern
         }
     }
 
+    // rotation coefficients of this thread's pair index (the query loop below and the key row use i = tid mod 64)
+    float pre_c = 1.0f, pre_s = 0.0f;
+    if (kEarly && cs && tid < (GH > 1 ? GH : 1) * (kHd / 2)) {
+        pre_c = __ldg(cs + (tid & (kHd / 2 - 1)));
+        pre_s = __ldg(sn + (tid & (kHd / 2 - 1)));
+    }
+    if (kEarly && a.use_pdl) pdl_wait();
+
     // ---- RoPE on this CTA's query heads (pairs i, i+64; :459-480) ---------------------------------
     for (int idx = tid; idx < GH * (kHd / 2); idx += NT) {
         const int g = idx / (kHd / 2), i = idx % (kHd / 2);
         const float* qh = a.q + (size_t)seq * a.q_stride + (size_t)(head0 + g) * kHd;
         float r0, r1;
-        rope_pair(__ldcg(qh + i), __ldcg(qh + i + kHd / 2), cs, sn, i, r0, r1);
+        if constexpr (kEarly) rope_rotate(__ldcg(qh + i), __ldcg(qh + i + kHd / 2), cs != nullptr, pre_c, pre_s, r0, r1);   // NT > GH * 64: idx == tid
+        else rope_pair(__ldcg(qh + i), __ldcg(qh + i + kHd / 2), cs, sn, i, r0, r1);
         s_q[g * kHd + i] = r0;
         s_q[g * kHd + i + kHd / 2] = r1;
     }
@@ -224,7 +239,8 @@ __global__ void __launch_bounds__(TILED ? kTileThreads : kAttnThreads) attn_kern
         if (tid < kHd / 2) {
             const float* kh = a.k + (size_t)seq * a.kv_stride + (size_t)kvh * kHd;
             float r0, r1;
-            rope_pair(__ldcg(kh + tid), __ldcg(kh + tid + kHd / 2), cs, sn, tid, r0, r1);
+            if constexpr (kEarly) rope_rotate(__ldcg(kh + tid), __ldcg(kh + tid + kHd / 2), cs != nullptr, pre_c, pre_s, r0, r1);
+            else rope_pair(__ldcg(kh + tid), __ldcg(kh + tid + kHd / 2), cs, sn, tid, r0, r1);
             s_new[tid] = r0;
             s_new[tid + kHd / 2] = r1;
         } else if (tid < kHd) {

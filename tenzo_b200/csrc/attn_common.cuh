@@ -25,6 +25,16 @@ __device__ __forceinline__ void rope_pair(float x0, float x1, const float* cs, c
     }
 }
 
+// The same rotation with the coefficients already in registers.
+__device__ __forceinline__ void rope_rotate(float x0, float x1, bool rotate, float c, float s, float& r0, float& r1) {
+    r0 = x0;
+    r1 = x1;
+    if (rotate) {
+        r0 = __fmaf_rn(x0, c, -(x1 * s));
+        r1 = __fmaf_rn(x0, s, x1 * c);
+    }
+}
+
 // The scores / e_t / weights of one (sequence, kv-head group) live in shared memory head-major: w[g][t] at
 // base + g * tp + t, tp = max_len rounded up to 4. A head's values for consecutive keys are then contiguous: the
 // scoring lanes store without bank conflicts, the sequential softmax sum reads four keys per load, and the value sum
