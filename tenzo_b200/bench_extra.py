@@ -4,6 +4,8 @@
                 seeded matrices (283 MB, larger than L2) captured in one CUDA graph.
   gemm          its batched form: TL1 bitlinear GEMM 13824 x 2560 (gate|up of the 2B shape) for 256
                 sequences on tcgen05, cycled over 16 distinct matrices (141 MB, larger than L2).
+  lm_head       the INT8 LM head 128256 x 2560 + greedy argmax for one sequence (final RMSNorm + absmax quantiser fused),
+                alternating between two distinct tables (657 MB, larger than L2).
   attn          fused INT8-KV GQA decode attention alone, batch 64, 20/5 heads, ctx 8192.
   decode_batch  batched greedy decode of the BitNet-2B shape, KV prefilled on the device.
 
@@ -115,6 +117,85 @@ def _cpu_gemv_baseline(N, K):
     dt = time.perf_counter() - t0
     return {"value": n * (N * K // 4 + 4 * K + 4 * N) / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": "reference" if kind else "port",
             "sample": f"{n} calls of the reference's TL1 product {N}x{K} cycling over 32 distinct matrices, {dt:.1f} s; {dt / n * 1e6:.0f} us per call"}
+
+
+def run_lm_head(args):
+    """compute_logits' int8 branch + the greedy scan (src/runtime/TenzoEngine.cpp:1634-1638, :1661-1719, :1745-1755)."""
+    import torch
+    from . import kernels
+    V, H, n_mat, per_graph = 128256, 2560, 2, 8
+    g = torch.Generator(device="cuda").manual_seed(7)
+    ws = [torch.randint(-127, 128, (V, H), generator=g, device="cuda", dtype=torch.int8) for _ in range(n_mat)]
+    scales = (torch.rand(V, generator=g, device="cuda") * 0.01 + 0.001).contiguous()
+    norm_w = (1.0 + 0.1 * torch.randn(H, generator=g, device="cuda")).contiguous()
+    x = torch.randn(1, H, generator=g, device="cuda")
+    arg = torch.zeros(1, dtype=torch.int32, device="cuda")
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        for w in ws:
+            kernels.lm_head_i8_static(x, w, scales, norm_w=norm_w, argmax=arg, use_pdl=bool(args.pdl))
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for i in range(per_graph):
+                kernels.lm_head_i8_static(x, ws[i % n_mat], scales, norm_w=norm_w, argmax=arg, use_pdl=bool(args.pdl))
+        for _ in range(max(3, args.warmup)):
+            graph.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        stream.synchronize()
+        e0.record(stream)
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record(stream)
+        stream.synchronize()
+    ms = e0.elapsed_time(e1)
+    calls = args.steps * per_graph
+    bytes_per = V * H + 4 * V
+    gbs = bytes_per * calls / (ms * 1e-3) / 1e9
+    peak = _peak()
+    cpu = None if getattr(args, "no_cpu_baseline", False) else _cpu_lm_head_baseline(V, H)
+    print(json.dumps({
+        "cpu_baseline": cpu,
+        "metric": "lm_head_int8_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup),
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
+        "data": "synthetic", "config": {"workload": f"lm_head: INT8 LM head {V}x{H} + greedy argmax, one sequence, {per_graph} calls per step "
+                                                    f"alternating between {n_mat} tables ({n_mat * V * H / 1e6:.0f} MB > L2)", "pdl": int(args.pdl)},
+        "gpu_launches": 2 * calls,
+        "roofline": {"bound": "hbm", "kernel": "lm_head_kernel<1> (+ argmax_finish_kernel)", "achieved": gbs, "peak": peak[0], "peak_source": peak[1],
+                     "unit": "GB/s", "frac": gbs / peak[0], "traffic": 329044224.0,
+                     "traffic_source": "ncu dram__bytes_read.sum of one launch inside the decode step: 1.00 x algorithmic",
+                     "bytes_per_launch": bytes_per, "us_per_launch": ms * 1e3 / calls},
+    }), flush=True)
+
+
+def _cpu_lm_head_baseline(V, H):
+    """The restated int8 LM head (oracle: TenzoEngine.cpp:1688-1718) on the host cores, alternating between two tables
+    (more than the host's last-level cache), bounded sample. The reference has no kernel-level entry for it."""
+    import sys
+    import time
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[1]
+    for pth in (str(root), str(root / "tests")):
+        if pth not in sys.path:
+            sys.path.insert(0, pth)
+    import bench
+    from oracle import oracle_py as ora
+    threads = bench.use_host_threads()
+    rng = np.random.default_rng(5)
+    ws = [rng.integers(-127, 128, (V, H), dtype=np.int8) for _ in range(2)]
+    scales = (rng.random(V) * 0.01 + 0.001).astype(np.float32)
+    x8 = rng.integers(-127, 128, H, dtype=np.int8)
+    logits = np.zeros(V, np.float32)
+    O, P = ora.load_oracle(), ora.ptr
+    one = lambda w: O.ora_lm_head_i8(P(x8, ora.c_i8p), 0.01, P(w, ora.c_i8p), P(scales, ora.c_f32p), V, H, P(logits, ora.c_f32p), None)
+    one(ws[0])
+    n, t0 = 0, time.perf_counter()
+    while time.perf_counter() - t0 < 3.0:
+        one(ws[n % 2])
+        n += 1
+    dt = time.perf_counter() - t0
+    return {"value": n * (V * H + 4 * V) / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": f"{n} calls of the restated int8 LM head {V}x{H} alternating between 2 tables, {dt:.1f} s; {dt / n * 1e3:.1f} ms per call"}
 
 
 def _peak_tensor():
@@ -399,7 +480,7 @@ def run_decode_tp(args):
 
 
 def run(args):
-    fn = {"gemv": run_gemv, "gemm": run_gemm, "attn": run_attn, "decode_batch": run_decode_batch, "decode_tp": run_decode_tp}.get(args.workload)
+    fn = {"gemv": run_gemv, "lm_head": run_lm_head, "gemm": run_gemm, "attn": run_attn, "decode_batch": run_decode_batch, "decode_tp": run_decode_tp}.get(args.workload)
     if fn is None:
         raise SystemExit(f"unknown workload {args.workload!r}")
     return fn(args)

@@ -18,6 +18,7 @@ namespace tz {
 constexpr int kLmThreads = 256;
 constexpr int kLmWarps = kLmThreads / 32;
 constexpr int kLmCtas = 148 * 4;
+constexpr int kLmInFlight = 5;        // 16-byte loads per lane issued back to back
 
 
 // Sum of squares in the reference's order (see common.cuh) computed by ONE warp over a vector in
@@ -48,7 +49,7 @@ __device__ __forceinline__ float warp_sumsq_reference_order(const float* x, int 
 // NS sequences per CTA (1 or 8). With 8, warp n prepares sequence n (norm, quantise) and every
 // vocabulary row read from HBM is used for all eight sequences.
 template <int NS>
-__global__ void __launch_bounds__(kLmThreads) lm_head_kernel(
+__global__ void __launch_bounds__(kLmThreads, NS == 1 ? 4 : 0) lm_head_kernel(
     const float* __restrict__ x, const float* __restrict__ norm_w, int do_norm, float eps,
     const int8_t* __restrict__ w, const float* __restrict__ row_scales, int vocab, int hidden, int x_stride, int batch,
     float* logits, int32_t* acc_out, LmBest* cta_best, int use_pdl) {
@@ -112,15 +113,39 @@ __global__ void __launch_bounds__(kLmThreads) lm_head_kernel(
 #pragma unroll
         for (int n = 0; n < NS; ++n) acc[n] = 0;
         if (vec_ok) {
-            for (int p = lane; p < nvec; p += 32) {
-                const uint4 wv = ld_stream_u4(row + (size_t)p * 16);
+            if constexpr (NS == 1) {
+                // every load of a row leaves before the first is used (kLmInFlight x 512 bytes per warp: a 2560-byte row
+                // is five): with one 16-byte load per lane in flight the kernel moved 3.9 TB/s, bound by latency, not by HBM
+                for (int p0 = lane; p0 < nvec; p0 += 32 * kLmInFlight) {
+                    uint4 wv[kLmInFlight];
 #pragma unroll
-                for (int n = 0; n < NS; ++n) {
-                    const uint4 xv = reinterpret_cast<const uint4*>(s_x8 + (size_t)n * hpad)[p];
-                    acc[n] = dp4a_ss(wv.x, xv.x, acc[n]);
-                    acc[n] = dp4a_ss(wv.y, xv.y, acc[n]);
-                    acc[n] = dp4a_ss(wv.z, xv.z, acc[n]);
-                    acc[n] = dp4a_ss(wv.w, xv.w, acc[n]);
+                    for (int u = 0; u < kLmInFlight; ++u) {
+                        const int p = p0 + 32 * u;
+                        wv[u] = p < nvec ? ld_stream_u4(row + (size_t)p * 16) : make_uint4(0u, 0u, 0u, 0u);
+                    }
+#pragma unroll
+                    for (int u = 0; u < kLmInFlight; ++u) {
+                        const int p = p0 + 32 * u;
+                        if (p < nvec) {
+                            const uint4 xv = reinterpret_cast<const uint4*>(s_x8)[p];
+                            acc[0] = dp4a_ss(wv[u].x, xv.x, acc[0]);
+                            acc[0] = dp4a_ss(wv[u].y, xv.y, acc[0]);
+                            acc[0] = dp4a_ss(wv[u].z, xv.z, acc[0]);
+                            acc[0] = dp4a_ss(wv[u].w, xv.w, acc[0]);
+                        }
+                    }
+                }
+            } else {                                  // eight sequences per row: 32 dp4a per load
+                for (int p = lane; p < nvec; p += 32) {
+                    const uint4 wv = ld_stream_u4(row + (size_t)p * 16);
+#pragma unroll
+                    for (int n = 0; n < NS; ++n) {
+                        const uint4 xv = reinterpret_cast<const uint4*>(s_x8 + (size_t)n * hpad)[p];
+                        acc[n] = dp4a_ss(wv.x, xv.x, acc[n]);
+                        acc[n] = dp4a_ss(wv.y, xv.y, acc[n]);
+                        acc[n] = dp4a_ss(wv.z, xv.z, acc[n]);
+                        acc[n] = dp4a_ss(wv.w, xv.w, acc[n]);
+                    }
                 }
             }
         } else {
