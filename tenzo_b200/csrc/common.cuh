@@ -111,11 +111,7 @@ __device__ __forceinline__ float warp_max(float v) {
     for (int m = 16; m > 0; m >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, m));
     return v;
 }
-__device__ __forceinline__ int warp_sum_i(int v) {
-#pragma unroll
-    for (int m = 16; m > 0; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
-    return v;
-}
+__device__ __forceinline__ int warp_sum_i(int v) { return __reduce_add_sync(0xffffffffu, v); }   // one redux.sync
 
 // Block-wide reductions whose result is bit-identical in every thread and every CTA: warp
 // butterflies, then each thread adds the per-warp partials in index order. `scratch` holds at
@@ -136,9 +132,9 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
     __syncthreads();
     if (lane == 0) scratch[warp] = v;
     __syncthreads();
-    float t = scratch[0];
-    for (int i = 1; i < nw; ++i) t = fmaxf(t, scratch[i]);
-    return t;
+    // the per-warp maxima are reduced by a second butterfly (a maximum does not depend on the order; as a loop of
+    // dependent loads over up to 16 slots this step alone took some 500 cycles)
+    return warp_max(scratch[lane < nw ? lane : 0]);
 }
 
 // Sum of squares in the exact order of the reference's vectorised loop (TenzoEngine.cpp:149-153 as

@@ -41,6 +41,7 @@
 #include <cooperative_groups.h>
 
 #include "common.cuh"
+#include "attn_common.cuh"
 #include "../../include/tenzo_kernels.h"
 
 namespace tz {
@@ -78,17 +79,18 @@ __device__ __forceinline__ uint32_t ld_stream_u32(const void* p) {
     return v;
 }
 
-// Optional in-kernel timeline (compile with -DTZ_TRACE): first and last CTA record %globaltimer at
-// stage boundaries into g_trace; compiled out of the library build.
+// Optional in-kernel timeline (compile with -DTZ_TRACE): first and last CTA record their SM's cycle counter at
+// stage boundaries into g_trace (16 words per record; stamps 0-6 are the stages, 8-12 lie inside the prologue; word 15:
+// block index, grid size in the upper half), read and reset by tenzo_trace_gemv(); compiled out of the library build.
 #ifdef TZ_TRACE
-__device__ unsigned long long g_trace[4096 * 8];
+__device__ unsigned long long g_trace[4096 * 16];
 __device__ unsigned int g_trace_n;
-__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-#define TZ_TRACE_DECL unsigned long long tr[8] = {0, 0, 0, 0, 0, 0, 0, 0}
-#define TZ_STAMP(k) do { if (threadIdx.x == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)) tr[k] = gtime(); } while (0)
+#define TZ_TRACE_DECL unsigned long long tr[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}
+#define TZ_STAMP(k) do { if (threadIdx.x == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)) tr[k] = (unsigned long long)clock64(); } while (0)
 #define TZ_TRACE_FLUSH do { if (threadIdx.x == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)) { \
     const unsigned slot = atomicAdd(&g_trace_n, 1u); \
-    if (slot < 4096) { for (int k = 0; k < 7; ++k) g_trace[slot * 8 + k] = tr[k]; g_trace[slot * 8 + 7] = blockIdx.x; } } } while (0)
+    if (slot < 4096) { for (int k = 0; k < 15; ++k) g_trace[slot * 16 + k] = tr[k]; \
+                       g_trace[slot * 16 + 15] = blockIdx.x | ((unsigned long long)gridDim.x << 32); } } } while (0)
 #else
 #define TZ_TRACE_DECL do {} while (0)
 #define TZ_STAMP(k) do {} while (0)
@@ -112,7 +114,7 @@ struct GemvSmem {
     //               | s_b[sets*SL*8] | weights[nb_cta*sets*128] | (fused) x[K]
     static __host__ __device__ int head_words() { return (128 * SL + 2 * SL + 32 + 2 + 4 * kChunks + 3) & ~3; }
     static __host__ __device__ size_t bytes(int sets_per_cta, int K, int nb_cta) {
-        return (size_t)(head_words() + sets_per_cta * SL * 8 + nb_cta * sets_per_cta * 128 + (FUSED ? K + 8 : 0)) * 4;
+        return (size_t)(head_words() + sets_per_cta * SL * 8 + nb_cta * sets_per_cta * 128 + (FUSED ? K + 64 : 0)) * 4;   // x, or its squares in padded chain-major rows
     }
 };
 
@@ -179,7 +181,23 @@ __global__ void __launch_bounds__((FUSED ? kFusedWarps : kBatchedWarps) * 32, FU
     float wreg[kWRegs];
     const bool has_w = FUSED && a.do_norm && a.norm_w;
     const bool w_in_regs = has_w && a.K <= kWRegs * kGemvThreads;
-    if (w_in_regs) {
+    // Prologue form for K a multiple of 32 up to 4096 with 16-byte aligned vectors (two 16-byte pieces per thread: more
+    // would not fit the 64 registers that two CTAs per SM leave a thread): every thread OWNS the elements it loads
+    // (pieces f = tid, tid + threads; elements 4f..4f+3) and keeps them and their norm weights in registers from the
+    // load to the quantised bytes, which it stores straight into the packed activation words: no shared-memory round trip
+    // for the normalised vector and no second pass over it.
+    constexpr int kOwn = 2;
+    const int n_pieces = a.K >> 2;
+    const bool own = FUSED && (a.K & 31) == 0 && n_pieces <= kOwn * kGemvThreads &&
+                     ((reinterpret_cast<uintptr_t>(a.x + (size_t)seq0 * a.x_stride) | (has_w ? reinterpret_cast<uintptr_t>(a.norm_w) : 0)) & 15) == 0;
+    if (own && has_w) {
+#pragma unroll
+        for (int j = 0; j < kOwn; ++j) {
+            const int f = tid + j * kGemvThreads;
+            const float4 w4 = f < n_pieces ? __ldg(reinterpret_cast<const float4*>(a.norm_w) + f) : make_float4(0.f, 0.f, 0.f, 0.f);
+            wreg[4 * j] = w4.x; wreg[4 * j + 1] = w4.y; wreg[4 * j + 2] = w4.z; wreg[4 * j + 3] = w4.w;
+        }
+    } else if (w_in_regs) {
 #pragma unroll
         for (int r = 0; r < kWRegs; ++r) {
             const int i = tid + r * kGemvThreads;
@@ -198,8 +216,99 @@ __global__ void __launch_bounds__((FUSED ? kFusedWarps : kBatchedWarps) * 32, FU
     if (FUSED && a.epilogue == TENZO_EPI_RESIDUAL && split == 0 && tid < 64)
         resid_v = __ldcg(a.resid + (size_t)seq0 * a.out_stride + unit * 64 + tid);
 
-    if (FUSED) {
-        // ---- RMSNorm + absmax(31) quantiser, recomputed identically by every CTA --------------
+    if (FUSED && own) {
+        // ---- RMSNorm + absmax(31) quantiser, recomputed identically by every CTA; owned elements (see above) --------
+        const float4* x4 = reinterpret_cast<const float4*>(a.x + (size_t)seq0 * a.x_stride);
+        float xv[4 * kOwn];
+#pragma unroll
+        for (int j = 0; j < kOwn; ++j) {
+            const int f = tid + j * kGemvThreads;
+            const float4 v = f < n_pieces ? __ldcg(x4 + f) : make_float4(0.f, 0.f, 0.f, 0.f);
+            xv[4 * j] = v.x; xv[4 * j + 1] = v.y; xv[4 * j + 2] = v.z; xv[4 * j + 3] = v.w;
+        }
+        float m = 0.0f;
+        if (a.do_norm) {
+            // squares chain-major (element e in row e & 7, column e >> 3) in padded rows, 16-byte aligned and four banks
+            // apart: the lane of chain c then reads four of its elements per load
+            const int stride = (((a.K >> 3) + 3) & ~3) + 4;
+#pragma unroll
+            for (int j = 0; j < kOwn; ++j) {
+                const int f = tid + j * kGemvThreads;
+                if (f < n_pieces) {
+                    float* d = s_x + (4 * (f & 1)) * stride + (f >> 1);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) d[k * stride] = __fmul_rn(xv[4 * j + k], xv[4 * j + k]);
+                }
+            }
+            __syncthreads();
+            TZ_STAMP(8);
+            if (tid < 8) {
+                // eight elements requested while the previous eight are added (two registers sets of two loads)
+                const float4* p = reinterpret_cast<const float4*>(s_x + tid * stride);
+                const int n4 = a.K >> 5;                                  // 16-byte pieces per chain
+                float sum = 0.0f;
+                auto add4 = [&](const float4& v) {
+                    sum = __fadd_rn(sum, v.x); sum = __fadd_rn(sum, v.y); sum = __fadd_rn(sum, v.z); sum = __fadd_rn(sum, v.w);
+                };
+                float4 a0 = p[0], a1 = n4 > 1 ? p[1] : make_float4(0.f, 0.f, 0.f, 0.f), b0, b1;
+                int i = 0;
+                for (; i + 4 <= n4; i += 4) {
+                    b0 = p[i + 2]; b1 = p[i + 3];
+                    add4(a0); add4(a1);
+                    if (i + 6 <= n4) { a0 = p[i + 4]; a1 = p[i + 5]; } else if (i + 5 <= n4) { a0 = p[i + 4]; }
+                    add4(b0); add4(b1);
+                }
+                for (; i < n4; ++i) add4(p[i]);                           // at most three pieces (read again: rare shapes)
+                s_f[tid] = sum;
+            }
+            __syncthreads();
+            float ss = s_f[0];
+#pragma unroll
+            for (int j = 1; j < 8; ++j) ss = __fadd_rn(ss, s_f[j]);     // the eight lanes left to right (common.cuh)
+            TZ_STAMP(9);
+            const float inv_rms = rms_inv(ss, a.K, a.eps);
+#pragma unroll
+            for (int r = 0; r < 4 * kOwn; ++r) {
+                float y = xv[r] * inv_rms;                              // x * inv_rms * w, left to right (:158)
+                if (has_w) y = y * wreg[r];
+                xv[r] = y;
+                m = fmaxf(m, fabsf(y));                                 // slots beyond K hold zeros
+            }
+        } else {
+#pragma unroll
+            for (int r = 0; r < 4 * kOwn; ++r) m = fmaxf(m, fabsf(xv[r]));
+        }
+        TZ_STAMP(10);
+        m = fmaxf(block_max(m, s_f), 1e-6f);        // TenzoEngine.cpp:28-32
+        TZ_STAMP(11);
+        const float to_q = 31.0f / m;               // :34
+        if (tid == 0) s_inv[0] = m / 31.0f;         // :35
+        const bool parity_out = a.a_out && blockIdx.x == 0;
+        uint8_t* s_b8 = reinterpret_cast<uint8_t*>(s_b);
+        int sa = 0;
+#pragma unroll
+        for (int j = 0; j < kOwn; ++j) {
+            const int f = tid + j * kGemvThreads, s = f >> 3, i = (f >> 1) & 3;     // element 4f + k: set, byte of its word
+            if (f < n_pieces) {
+                const bool mine = s >= s_begin && s < s_end;                        // this CTA's K range
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int q = (int)roundf(xv[4 * j + k] * to_q);                // :41-42, half away from zero
+                    // word (set, column c = 4 (f & 1) + k) holds its elements 8 i + c, i = 0..3; even columns carry the factor 4
+                    if (mine) {
+                        s_b8[(((s - s_begin) * 8 + 4 * (f & 1) + k) << 2) + i] = (uint8_t)(int8_t)((k & 1) ? q : 4 * q);
+                        sa += q;
+                    }
+                    if (parity_out) a.a_out[(size_t)seq0 * a.K + 4 * f + k] = (int8_t)q;
+                }
+            }
+        }
+        sa = warp_sum_i(sa);
+        if (lane == 0 && sa) atomicAdd(&s_sa4[0], 4 * sa);
+        if (a.inv_out && blockIdx.x == 0 && tid == 0) a.inv_out[seq0] = m / 31.0f;
+        TZ_STAMP(12);
+    } else if (FUSED) {
+        // ---- the same for any other K: x staged in shared memory, two passes over it ----------------
         const float* x = a.x + (size_t)seq0 * a.x_stride;
         const bool vec = ((a.K & 3) == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
         if (vec) {
@@ -553,3 +662,19 @@ extern "C" int tenzo_cuda_tl1_gemv(const tenzo_tl1_gemv_args* args, void* stream
     }
     return e == cudaSuccess ? 0 : (int)e;
 }
+
+#ifdef TZ_TRACE
+// Measurement builds only: copies up to max_records timeline records (16 words each) to `out`, resets the buffer and
+// returns how many were copied.
+extern "C" __attribute__((visibility("default"))) int tenzo_trace_gemv(unsigned long long* out, int max_records) {
+    unsigned int n = 0;
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    if (cudaMemcpyFromSymbol(&n, tz::g_trace_n, sizeof n) != cudaSuccess) return -1;
+    if (n > 4096u) n = 4096u;
+    if ((int)n > max_records) n = (unsigned)max_records;
+    if (n && cudaMemcpyFromSymbol(out, tz::g_trace, (size_t)n * 16 * sizeof(unsigned long long)) != cudaSuccess) return -1;
+    const unsigned int zero = 0;
+    if (cudaMemcpyToSymbol(tz::g_trace_n, &zero, sizeof zero) != cudaSuccess) return -1;
+    return (int)n;
+}
+#endif
