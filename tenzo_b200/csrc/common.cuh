@@ -112,6 +112,11 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 __device__ __forceinline__ int warp_sum_i(int v) { return __reduce_add_sync(0xffffffffu, v); }   // one redux.sync
+// Maximum over the warp of values that are >= 0 and not NaN (running maxima of |x| that started at 0: fmaxf drops NaN):
+// for those the order of the floats is the order of their bit patterns, so one integer redux.sync replaces five shuffles.
+__device__ __forceinline__ float warp_max_nonneg(float v) {
+    return __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(v)));
+}
 
 // Block-wide reductions whose result is bit-identical in every thread and every CTA: warp
 // butterflies, then each thread adds the per-warp partials in index order. `scratch` holds at
@@ -125,6 +130,15 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     float t = 0.0f;
     for (int i = 0; i < nw; ++i) t += scratch[i];
     return t;
+}
+// The same for values >= 0 that are not NaN (see warp_max_nonneg).
+__device__ __forceinline__ float block_max_nonneg(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_max_nonneg(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    return warp_max_nonneg(scratch[lane < nw ? lane : 0]);
 }
 __device__ __forceinline__ float block_max(float v, float* scratch) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;

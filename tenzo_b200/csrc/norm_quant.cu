@@ -39,7 +39,7 @@ __global__ void __launch_bounds__(kNqThreads) rmsnorm_quant_kernel(
     if (y_out)
         for (int i = tid; i < dim; i += kNqThreads) y_out[(size_t)seq * dim + i] = s_y[i];
     if (!q_out && !scale_out) return;
-    m = block_max(m, s_f);
+    m = block_max_nonneg(m, s_f);      // m: running maximum of |y| from 0
     if (qmax == 31) {
         m = fmaxf(m, 1e-6f);
         const float to_q = 31.0f / m;
@@ -153,7 +153,7 @@ __global__ void __launch_bounds__(kNqThreads) act_quant_kernel(
         }
 #pragma unroll
         for (int r = 0; r < kAqVec; ++r) m = fmaxf(fmaxf(m, fmaxf(fabsf(v[r].x), fabsf(v[r].y))), fmaxf(fabsf(v[r].z), fabsf(v[r].w)));
-        m = fmaxf(block_max(m, s_f), 1e-6f);      // TenzoEngine.cpp:28-32
+        m = fmaxf(block_max_nonneg(m, s_f), 1e-6f);      // TenzoEngine.cpp:28-32
         AQT(4);
         const float to_q = 31.0f / m;             // :34
         if (tid == 0) inv[seq] = m / 31.0f;       // :35
@@ -221,7 +221,7 @@ __global__ void __launch_bounds__(kNqThreads) act_quant_kernel(
     } else {
         for (int i = tid; i < K; i += kNqThreads) m = fmaxf(m, fabsf(s_y[i]));
     }
-    m = fmaxf(block_max(m, s_f), 1e-6f);      // TenzoEngine.cpp:28-32
+    m = fmaxf(block_max_nonneg(m, s_f), 1e-6f);      // TenzoEngine.cpp:28-32
     const float to_q = 31.0f / m;             // :34
     const int nsets = ((K >> 1) + 15) / 16;
     for (int wd = tid; words && wd < nsets * 8; wd += kNqThreads) {

@@ -279,7 +279,7 @@ __global__ void __launch_bounds__((FUSED ? kFusedWarps : kBatchedWarps) * 32, FU
             for (int r = 0; r < 4 * kOwn; ++r) m = fmaxf(m, fabsf(xv[r]));
         }
         TZ_STAMP(10);
-        m = fmaxf(block_max(m, s_f), 1e-6f);        // TenzoEngine.cpp:28-32
+        m = fmaxf(block_max_nonneg(m, s_f), 1e-6f); // TenzoEngine.cpp:28-32 (m: running maximum of |y| from 0)
         TZ_STAMP(11);
         const float to_q = 31.0f / m;               // :34
         if (tid == 0) s_inv[0] = m / 31.0f;         // :35
@@ -342,7 +342,7 @@ __global__ void __launch_bounds__((FUSED ? kFusedWarps : kBatchedWarps) * 32, FU
         } else {
             for (int i = tid; i < a.K; i += kGemvThreads) m = fmaxf(m, fabsf(s_x[i]));
         }
-        m = fmaxf(block_max(m, s_f), 1e-6f);        // TenzoEngine.cpp:28-32
+        m = fmaxf(block_max_nonneg(m, s_f), 1e-6f); // TenzoEngine.cpp:28-32 (m: running maximum of |y| from 0)
         const float to_q = 31.0f / m;               // :34
         if (tid == 0) s_inv[0] = m / 31.0f;         // :35
         // pack only this CTA's columns: one 32-bit fragment word per (set, t, even/odd)
