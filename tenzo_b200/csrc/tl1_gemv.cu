@@ -39,6 +39,7 @@
 //     batch > 1: act_quant_kernel (norm_quant.cu) has written packed int8 activations to a
 //     workspace; CTAs stage their K range for 8 or 32 sequences and reuse every weight word for all.
 #include <cooperative_groups.h>
+#include <type_traits>
 
 #include "common.cuh"
 #include "attn_common.cuh"
@@ -107,6 +108,10 @@ constexpr int kChunks = TZ_GEMV_CHUNKS;
 
 __device__ int g_tl1_timeouts = 0; // set when a bounded mbarrier wait gave up (the result of that launch is invalid)
 
+// One sequence, 4096 < K <= 8192: a thread owns up to four 16-byte pieces of the input vector and parks their norm weights in
+// a private shared-memory slot while it waits (see the prologue): [4][threads] float4.
+__host__ __device__ constexpr int own_park_floats(int K) { return (K > 2 * 4 * kFusedWarps * 32 && K <= 4 * 4 * kFusedWarps * 32) ? 4 * kFusedWarps * 32 * 4 : 0; }
+
 template <int NT, bool FUSED>
 struct GemvSmem {
     static constexpr int SL = FUSED ? 1 : 8 * NT;                       // sequences per CTA
@@ -114,7 +119,7 @@ struct GemvSmem {
     //               | s_b[sets*SL*8] | weights[nb_cta*sets*128] | (fused) x[K]
     static __host__ __device__ int head_words() { return (128 * SL + 2 * SL + 32 + 2 + 4 * kChunks + 3) & ~3; }
     static __host__ __device__ size_t bytes(int sets_per_cta, int K, int nb_cta) {
-        return (size_t)(head_words() + sets_per_cta * SL * 8 + nb_cta * sets_per_cta * 128 + (FUSED ? K + 64 : 0)) * 4;   // x, or its squares in padded chain-major rows
+        return (size_t)(head_words() + sets_per_cta * SL * 8 + nb_cta * sets_per_cta * 128 + (FUSED ? K + 64 + own_park_floats(K) : 0)) * 4;   // x, or its squares in padded chain-major rows (+ parked norm weights)
     }
 };
 
@@ -181,23 +186,32 @@ __global__ void __launch_bounds__((FUSED ? kFusedWarps : kBatchedWarps) * 32, FU
     float wreg[kWRegs];
     const bool has_w = FUSED && a.do_norm && a.norm_w;
     const bool w_in_regs = has_w && a.K <= kWRegs * kGemvThreads;
-    // Prologue form for K a multiple of 32 up to 4096 with 16-byte aligned vectors (two 16-byte pieces per thread: more
-    // would not fit the 64 registers that two CTAs per SM leave a thread): every thread OWNS the elements it loads
-    // (pieces f = tid, tid + threads; elements 4f..4f+3) and keeps them and their norm weights in registers from the
-    // load to the quantised bytes, which it stores straight into the packed activation words: no shared-memory round trip
-    // for the normalised vector and no second pass over it.
-    constexpr int kOwn = 2;
+    // Prologue form for K a multiple of 32 up to 8192 with 16-byte aligned vectors: every thread OWNS the elements it loads
+    // (16-byte pieces f = tid, tid + threads, ...; elements 4f..4f+3) and keeps them in registers from the load to the
+    // quantised bytes, which it stores straight into the packed activation words: no shared-memory round trip for the
+    // normalised vector and no second pass over it. Up to two pieces per thread (K <= 4096) their norm weights wait in
+    // registers too; with up to four, the thread parks the weights in a shared-memory slot of its own before the wait and
+    // takes them back after the sum of squares (sixteen more live registers would not fit the 64 that two CTAs per SM
+    // leave a thread).
     const int n_pieces = a.K >> 2;
-    const bool own = FUSED && (a.K & 31) == 0 && n_pieces <= kOwn * kGemvThreads &&
-                     ((reinterpret_cast<uintptr_t>(a.x + (size_t)seq0 * a.x_stride) | (has_w ? reinterpret_cast<uintptr_t>(a.norm_w) : 0)) & 15) == 0;
-    if (own && has_w) {
+    const bool own_ok = FUSED && (a.K & 31) == 0 &&
+                        ((reinterpret_cast<uintptr_t>(a.x + (size_t)seq0 * a.x_stride) | (has_w ? reinterpret_cast<uintptr_t>(a.norm_w) : 0)) & 15) == 0;
+    const int own_p = !own_ok ? 0 : n_pieces <= 2 * kGemvThreads ? 2 : n_pieces <= 4 * kGemvThreads ? 4 : 0;
+    float4* s_w4 = reinterpret_cast<float4*>(s_x + a.K + 64);          // [4][threads], own_p == 4 only
+    if (own_p == 2 && has_w) {
 #pragma unroll
-        for (int j = 0; j < kOwn; ++j) {
+        for (int j = 0; j < 2; ++j) {
             const int f = tid + j * kGemvThreads;
             const float4 w4 = f < n_pieces ? __ldg(reinterpret_cast<const float4*>(a.norm_w) + f) : make_float4(0.f, 0.f, 0.f, 0.f);
             wreg[4 * j] = w4.x; wreg[4 * j + 1] = w4.y; wreg[4 * j + 2] = w4.z; wreg[4 * j + 3] = w4.w;
         }
-    } else if (w_in_regs) {
+    } else if (own_p == 4 && has_w) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int f = tid + j * kGemvThreads;
+            if (f < n_pieces) s_w4[j * kGemvThreads + tid] = __ldg(reinterpret_cast<const float4*>(a.norm_w) + f);
+        }
+    } else if (own_p == 0 && w_in_regs) {
 #pragma unroll
         for (int r = 0; r < kWRegs; ++r) {
             const int i = tid + r * kGemvThreads;
@@ -216,12 +230,13 @@ __global__ void __launch_bounds__((FUSED ? kFusedWarps : kBatchedWarps) * 32, FU
     if (FUSED && a.epilogue == TENZO_EPI_RESIDUAL && split == 0 && tid < 64)
         resid_v = __ldcg(a.resid + (size_t)seq0 * a.out_stride + unit * 64 + tid);
 
-    if (FUSED && own) {
+    auto own_prologue = [&](auto pieces_c) {
+        constexpr int P = decltype(pieces_c)::value;      // pieces per thread
         // ---- RMSNorm + absmax(31) quantiser, recomputed identically by every CTA; owned elements (see above) --------
         const float4* x4 = reinterpret_cast<const float4*>(a.x + (size_t)seq0 * a.x_stride);
-        float xv[4 * kOwn];
+        float xv[4 * P];
 #pragma unroll
-        for (int j = 0; j < kOwn; ++j) {
+        for (int j = 0; j < P; ++j) {
             const int f = tid + j * kGemvThreads;
             const float4 v = f < n_pieces ? __ldcg(x4 + f) : make_float4(0.f, 0.f, 0.f, 0.f);
             xv[4 * j] = v.x; xv[4 * j + 1] = v.y; xv[4 * j + 2] = v.z; xv[4 * j + 3] = v.w;
@@ -232,7 +247,7 @@ __global__ void __launch_bounds__((FUSED ? kFusedWarps : kBatchedWarps) * 32, FU
             // apart: the lane of chain c then reads four of its elements per load
             const int stride = (((a.K >> 3) + 3) & ~3) + 4;
 #pragma unroll
-            for (int j = 0; j < kOwn; ++j) {
+            for (int j = 0; j < P; ++j) {
                 const int f = tid + j * kGemvThreads;
                 if (f < n_pieces) {
                     float* d = s_x + (4 * (f & 1)) * stride + (f >> 1);
@@ -268,15 +283,22 @@ __global__ void __launch_bounds__((FUSED ? kFusedWarps : kBatchedWarps) * 32, FU
             TZ_STAMP(9);
             const float inv_rms = rms_inv(ss, a.K, a.eps);
 #pragma unroll
-            for (int r = 0; r < 4 * kOwn; ++r) {
+            for (int r = 0; r < 4 * P; ++r) {
                 float y = xv[r] * inv_rms;                              // x * inv_rms * w, left to right (:158)
-                if (has_w) y = y * wreg[r];
+                if (has_w) {
+                    if constexpr (P == 2) {
+                        y = y * wreg[r];
+                    } else {                                                // parked before the wait (same thread, same slot)
+                        const float* wp = reinterpret_cast<const float*>(s_w4 + (r >> 2) * kGemvThreads + tid);
+                        if (tid + (r >> 2) * kGemvThreads < n_pieces) y = y * wp[r & 3];
+                    }
+                }
                 xv[r] = y;
                 m = fmaxf(m, fabsf(y));                                 // slots beyond K hold zeros
             }
         } else {
 #pragma unroll
-            for (int r = 0; r < 4 * kOwn; ++r) m = fmaxf(m, fabsf(xv[r]));
+            for (int r = 0; r < 4 * P; ++r) m = fmaxf(m, fabsf(xv[r]));
         }
         TZ_STAMP(10);
         m = fmaxf(block_max_nonneg(m, s_f), 1e-6f); // TenzoEngine.cpp:28-32 (m: running maximum of |y| from 0)
@@ -287,7 +309,7 @@ __global__ void __launch_bounds__((FUSED ? kFusedWarps : kBatchedWarps) * 32, FU
         uint8_t* s_b8 = reinterpret_cast<uint8_t*>(s_b);
         int sa = 0;
 #pragma unroll
-        for (int j = 0; j < kOwn; ++j) {
+        for (int j = 0; j < P; ++j) {
             const int f = tid + j * kGemvThreads, s = f >> 3, i = (f >> 1) & 3;     // element 4f + k: set, byte of its word
             if (f < n_pieces) {
                 const bool mine = s >= s_begin && s < s_end;                        // this CTA's K range
@@ -307,6 +329,11 @@ __global__ void __launch_bounds__((FUSED ? kFusedWarps : kBatchedWarps) * 32, FU
         if (lane == 0 && sa) atomicAdd(&s_sa4[0], 4 * sa);
         if (a.inv_out && blockIdx.x == 0 && tid == 0) a.inv_out[seq0] = m / 31.0f;
         TZ_STAMP(12);
+    };
+    if (own_p == 2) {
+        own_prologue(std::integral_constant<int, 2>{});
+    } else if (own_p == 4) {
+        own_prologue(std::integral_constant<int, 4>{});
     } else if (FUSED) {
         // ---- the same for any other K: x staged in shared memory, two passes over it ----------------
         const float* x = a.x + (size_t)seq0 * a.x_stride;
