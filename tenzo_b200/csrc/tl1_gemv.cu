@@ -225,6 +225,7 @@ __global__ void __launch_bounds__((FUSED ? kFusedWarps : kBatchedWarps) * 32, FU
     TZ_STAMP(1);
     if (a.use_pdl) pdl_wait();
     TZ_STAMP(2);
+    if (FUSED && a.use_pdl) pdl_launch_dependents();   // one sequence: the next kernel's CTAs may come in and fetch their weights from here on
 
     float resid_v = 0.0f;                           // batch 1: fetched now so the epilogue does not wait on it
     if (FUSED && a.epilogue == TENZO_EPI_RESIDUAL && split == 0 && tid < 64)
@@ -411,7 +412,7 @@ __global__ void __launch_bounds__((FUSED ? kFusedWarps : kBatchedWarps) * 32, FU
     }
     __syncthreads();
     TZ_STAMP(3);
-    if (a.use_pdl) pdl_launch_dependents();
+    if (!FUSED && a.use_pdl) pdl_launch_dependents();
 
     // ---- main loop: weights from shared memory, four MMAs per set per 8 sequences -----------------
     int acc[NT][4][4];
